@@ -1,0 +1,163 @@
+"""Decoder-only GPT: token embedding -> `num_layer` pre-norm blocks (GQA
+attention with RoPE, SwiGLU MLP or top-k MoE) -> final norm -> (tied) LM head
+-> sequence-parallel-aware cross-entropy.
+
+Same modules, parameter names and FLOP model as the reference
+(`model/gpt.py:19-98`). The blocks hand the un-added branch output to the next
+norm so that `residual add + RMSNorm` is one pass, and in training the LM head
+and the loss are one fused op that never materialises `[B*T, V]` logits.
+
+Numerical conventions kept from the reference: fp32 residual stream, RMSNorm
+statistics in fp32, GEMM inputs in the compute dtype (bf16 on the GPU), fp32
+cross-entropy.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F_ops
+from ..parallel import parallel_state
+from ..parallel.flat import EXPERT_LOCAL_PARAM_SUFFIXES, flatten_model
+from ..training.config import ModelConfig
+from .modules.attn import Attention
+from .modules.emb import TextEmbedding
+from .modules.init import seeded_normal
+from .modules.loss import CrossEntropyLoss
+from .modules.mlp import MLP, MoE
+from .modules.norm import LayerNorm
+
+__all__ = ["GPT", "Block", "EXPERT_LOCAL_PARAM_SUFFIXES"]
+
+
+def _default_device():
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
+class Block(nn.Module):
+    def __init__(self, config: ModelConfig, use_moe: bool = True, top_k: int | None = None, device=None):
+        super().__init__()
+        self.use_moe = use_moe
+        self.ln_1 = LayerNorm(config, device)
+        self.attn = Attention(config, device)
+        self.ln_2 = LayerNorm(config, device)
+        self.mlp = MoE(config, top_k, device) if use_moe else MLP(config, device=device)
+
+    def forward(self, x: torch.Tensor, delta: torch.Tensor | None, B: int, T: int):
+        """x: fp32 residual `[B*T, D]`; delta: branch output not yet added.
+        Returns (residual, pending branch output)."""
+        x, h = self.ln_1.add_norm(x, delta)
+        a = self.attn(h, B, T)
+        x, h = self.ln_2.add_norm(x, a)
+        m = self.mlp(h)
+        if self.use_moe:
+            m = m[0]
+        return x, m
+
+
+class GPT(nn.Module):
+    def __init__(self, config: ModelConfig, device=None, compute_dtype: torch.dtype | None = None,
+                 flatten: bool = True, shard_world: int = 1):
+        super().__init__()
+        self.config = config
+        self.device = torch.device(device) if device is not None else _default_device()
+        if compute_dtype is None:
+            compute_dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.compute_dtype = compute_dtype
+        self.use_moe = config.use_moe
+        dev = self.device
+        self.wte = TextEmbedding(config.vocab_size, config.hidden_size, device=dev)
+        self.blocks = nn.ModuleList([Block(config, self.use_moe, device=dev) for _ in range(config.num_layer)])
+        self.lnf = LayerNorm(config, dev)
+        self.lm_head = nn.Module()
+        self.lm_head.weight = nn.Parameter(torch.empty(0, device=dev))
+        with torch.no_grad():
+            self.wte.weight.copy_(seeded_normal((config.vocab_size, config.hidden_size), config.init_std,
+                                                config.seed, dev, cache=not config.tied_lm_head))
+        if config.tied_lm_head:
+            self.lm_head.weight = self.wte.weight
+        else:
+            self.lm_head.weight = nn.Parameter(
+                seeded_normal((config.vocab_size, config.hidden_size), config.init_std, config.seed, dev))
+        self.loss_fn = CrossEntropyLoss()
+        self.dense_buf = self.expert_buf = None
+        if flatten:
+            pad = 1024 * max(1, shard_world)
+            self.dense_buf, self.expert_buf = flatten_model(self, compute_dtype, dev, pad, pad)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None, loss_scale: float = 1.0,
+                return_logits: bool | None = None):
+        """idx, targets: `[B, T_local]` (this SP rank's slice of the sequence).
+        Returns `(logits, loss, logging_loss)` like the reference
+        (`model/gpt.py:64-73`); both losses are multiplied by `loss_scale`
+        (pass `1 / grad_accum_steps`, then call `loss.backward()` directly).
+        Logits are only materialised when there are no targets or when
+        `return_logits=True`."""
+        B, T = idx.size()
+        sp = parallel_state.get_sp_world_size()
+        assert T * sp <= self.config.block_size * sp and T <= self.config.block_size, \
+            f"Cannot forward sequence of length {T}, block size is only {self.config.block_size}"
+        x = self.wte(idx)
+        delta = None
+        aux_total = None
+        for block in self.blocks:
+            x, delta = block(x, delta, B, T)
+            if self.use_moe and block.mlp.aux_loss is not None:
+                aux_total = block.mlp.aux_loss if aux_total is None else aux_total + block.mlp.aux_loss
+        _, h = self.lnf.add_norm(x, delta)
+        if return_logits is None:
+            return_logits = targets is None
+        logits = None
+        if return_logits:
+            logits = F_ops.linear(h, self.lm_head.weight).view(B, T, -1)
+        if targets is None:
+            return logits, None, None
+        if return_logits:
+            loss, logging_loss = self.loss_fn(logits, targets)
+            loss, logging_loss = loss * loss_scale, logging_loss * loss_scale
+        else:
+            loss, logging_loss = self.loss_fn.fused(h, self.lm_head.weight, targets, loss_scale)
+        if aux_total is not None:
+            loss = loss + aux_total * (loss_scale / sp)
+        return logits, loss, logging_loss
+
+    # ------------------------------------------------------------------ bookkeeping
+    def zero_grad_buffers(self) -> None:
+        for buf in (self.dense_buf, self.expert_buf):
+            if buf is not None:
+                buf.zero_grad()
+
+    def get_flops_per_fwd_bwd(self, batch_size: int, seq_len: int) -> float:
+        """Reference FLOP model (`model/gpt.py:75-98`), kept verbatim in meaning
+        so that MFU figures are comparable: 8BTD^2 for the four projections
+        (GQA ignored), 4BT^2D for attention (causality ignored), SwiGLU FFN, no
+        LM head; x3 for forward+backward; divided by the SP / EP sizes."""
+        c = self.config
+        sp, ep = parallel_state.get_sp_world_size(), parallel_state.get_ep_world_size()
+        B, T, D = batch_size, seq_len, c.hidden_size
+        attn = 8 * B * T * D * D + 4 * B * T * T * D
+        inter = c.moe_intermediate_size if self.use_moe else c.intermediate_size
+        ffn = 6 * B * T * D * inter + B * T * inter
+        if self.use_moe:
+            per_layer = (attn + 2 * B * T * D * c.num_experts) / sp + c.num_experts_per_tok * ffn / ep
+        else:
+            per_layer = (attn + ffn) / sp
+        return 3 * c.num_layer * per_layer
+
+    def get_exact_flops_per_fwd_bwd(self, batch_size: int, seq_len: int) -> float:
+        """Corrected count per device: GQA projection sizes, causal attention
+        (half the score matrix), LM head included."""
+        c = self.config
+        sp, ep = parallel_state.get_sp_world_size(), parallel_state.get_ep_world_size()
+        B, T, D = batch_size, seq_len, c.hidden_size
+        hd = D // c.num_attention_heads
+        proj = 2 * B * T * D * (c.num_attention_heads * hd + 2 * c.num_key_value_heads * hd + D)
+        attn = 4 * B * T * T * D / 2
+        if self.use_moe:
+            ffn = 2 * B * T * D * c.num_experts + c.num_experts_per_tok * 6 * B * T * D * c.moe_intermediate_size
+        else:
+            ffn = 6 * B * T * D * c.intermediate_size
+        head = 2 * B * T * D * c.vocab_size
+        # backward = 2x forward for GEMMs, 2.5x for attention (recomputed scores)
+        return (3 * c.num_layer * (proj + ffn) + 3.5 * c.num_layer * attn + 3 * head) / sp

@@ -1,0 +1,122 @@
+"""GQA causal self-attention with RoPE and optional Ulysses sequence parallelism.
+
+What the reference does in `model/modules/attn.py:126-176` with three GEMMs, a
+K/V expansion to Hq heads, a freshly built fp32 RoPE table per call, stack /
+transpose copies around two all-to-alls and a library SDPA call is done here as:
+
+  one GEMM against the fused `[Hq*hd + 2*Hkv*hd, D]` weight (q|k|v are adjacent
+  in the flat parameter buffer) -> RoPE on the q and k heads of the packed
+  `[B, T, Hq+2Hkv, hd]` tensor (table cached per position range) -> (SP only)
+  seq->head exchange of un-expanded heads -> flash attention that reads KV head
+  `h // (Hq/Hkv)` directly -> (SP only) head->seq exchange -> output GEMM.
+
+State-dict keys (`q_proj.weight`, `k_proj.weight`, `v_proj.weight`,
+`c_proj.weight`) and shapes equal the reference's.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ...ops import functional as F_ops
+from ...ops import oracle
+from ...parallel import parallel_state
+from ...parallel.flat import fuse_adjacent
+from ...parallel.sequence_parallel import ulysses
+from .init import seeded_normal
+
+
+def rope_impl(q: torch.Tensor, k: torch.Tensor, position_ids: torch.Tensor, rope_theta: float = 10000.0,
+              variant: str = "reference"):
+    """Functional RoPE on `[B, H, T, hd]` tensors (API of the reference's
+    `rope_impl`, `attn.py:12-68`); fp32 result."""
+    pos = position_ids[0] if position_ids.dim() > 1 else position_ids
+    cos, sin = oracle.rope_tables(pos, q.shape[-1], rope_theta, variant)
+    qe = oracle.rope(q.transpose(1, 2), cos, sin).transpose(1, 2)
+    ke = oracle.rope(k.transpose(1, 2), cos, sin).transpose(1, 2)
+    return qe, ke
+
+
+def gqa_impl(k: torch.Tensor, v: torch.Tensor, num_key_value_heads: int, num_attention_heads: int):
+    """Expand `[B, Hkv, T, hd]` to Hq heads. Provided for API parity
+    (`attn.py:71-88`); the attention op never needs it."""
+    if num_attention_heads % num_key_value_heads:
+        raise ValueError("num_attention_heads must be divisible by num_key_value_heads")
+    rep = num_attention_heads // num_key_value_heads
+    if rep == 1:
+        return k, v
+    return k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+
+
+class _Proj(nn.Module):
+    """Holder of one bias-free weight so that keys read `<name>.weight`."""
+
+    def __init__(self, out_features: int, in_features: int, std: float, seed: int, device):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(seeded_normal((out_features, in_features), std, seed, device))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        y = F_ops.linear(x.reshape(-1, shape[-1]).to(self.weight.dtype), self.weight)
+        return y.view(*shape[:-1], self.out_features)
+
+
+class Attention(nn.Module):
+    def __init__(self, config, device=None):
+        super().__init__()
+        assert config.hidden_size % config.num_attention_heads == 0
+        self.config = config
+        self.num_attention_heads = config.num_attention_heads
+        self.num_key_value_heads = config.num_key_value_heads
+        self.head_dim = config.hidden_size // config.num_attention_heads
+        self.n_embd = config.hidden_size
+        self.dropout = config.dropout
+        if self.dropout != 0.0:
+            raise NotImplementedError("attention dropout > 0 is not supported (the reference's scripts all use 0.0)")
+        hd, D = self.head_dim, config.hidden_size
+        self.q_proj = _Proj(self.num_attention_heads * hd, D, config.init_std, config.seed, device)
+        self.k_proj = _Proj(self.num_key_value_heads * hd, D, config.init_std, config.seed, device)
+        self.v_proj = _Proj(self.num_key_value_heads * hd, D, config.init_std, config.seed, device)
+        self.c_proj = _Proj(D, D, config.init_std, config.seed, device)
+        self._qkv_weight = None
+        self._rope_cache: dict = {}
+
+    def _post_flatten(self) -> None:
+        self._qkv_weight = fuse_adjacent([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
+
+    def _rope(self, T_local: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+        start = parallel_state.get_sep_rank() * T_local
+        key = (start, T_local, str(device))
+        if key not in self._rope_cache:
+            pos = torch.arange(start, start + T_local, device=device)
+            self._rope_cache = {key: oracle.rope_tables(pos, self.head_dim, self.config.rope_theta,
+                                                        self.config.rope_variant)}
+        return self._rope_cache[key]
+
+    def forward(self, h: torch.Tensor, B: int | None = None, T_local: int | None = None) -> torch.Tensor:
+        """h: `[B*T_local, D]` (or `[B, T_local, D]`) in the compute dtype -> same shape."""
+        shape = h.shape
+        if h.dim() == 3:
+            B, T_local = shape[0], shape[1]
+            h = h.reshape(-1, shape[-1])
+        Hq, Hkv, hd = self.num_attention_heads, self.num_key_value_heads, self.head_dim
+        h = h.to(self.q_proj.weight.dtype)
+        if self._qkv_weight is not None:
+            qkv = F_ops.linear(h, self._qkv_weight)
+        else:
+            qkv = torch.cat([F_ops.linear(h, self.q_proj.weight), F_ops.linear(h, self.k_proj.weight),
+                             F_ops.linear(h, self.v_proj.weight)], dim=-1)
+        qkv = qkv.view(B, T_local, Hq + 2 * Hkv, hd)
+        cos, sin = self._rope(T_local, h.device)
+        qkv = F_ops.rope_qk(qkv, cos, sin, Hq + Hkv)
+        sp = parallel_state.get_sep_world_size()
+        if sp > 1:
+            group = parallel_state.get_sep_group()
+            qkv_l, q_l, kv_l = ulysses.seq_to_head(qkv, Hq, Hkv, group)
+            o = F_ops.attention_packed(qkv_l.contiguous(), q_l, kv_l, True)
+            o = ulysses.head_to_seq(o, group)
+        else:
+            o = F_ops.attention_packed(qkv, Hq, Hkv, True)
+        y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
+        return y.view(shape)

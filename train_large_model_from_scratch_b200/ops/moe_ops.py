@@ -1,0 +1,151 @@
+"""Mixture-of-experts data path: routing, dispatch, grouped expert MLP, combine.
+
+The routing/dispatch bookkeeping is expressed once here in terms of small
+building blocks; the CUDA path swaps the heavy blocks (grouped GEMM, SwiGLU,
+gather/scatter) for kernels while the control flow stays the same.
+
+Data flow for `M` local tokens, top-`k`, `E` experts over `ep` ranks
+(reference: `model/modules/mlp.py:95-169`):
+
+  1. `weights, experts = softmax(topk(logits))`                     [M, k]
+  2. sort the M*k (token, slot) pairs by global expert id (stable); because
+     experts are laid out rank-major this is also sorted by destination rank
+  3. exchange per-(destination, local expert) counts; exchange rows
+  4. receiver regroups rows from (source, expert) order to expert order using
+     the counts only
+  5. per-expert `down(silu(gate x) * up x)` as grouped GEMMs
+  6. inverse regroup, rows travel back, un-sort, weighted sum over the k slots
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import functional as F_ops
+from . import native
+from . import oracle
+from ..parallel.expert_parallel.comm import ep_all_to_all, exchange_counts
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """rows of `x` are grouped by expert: rows [offs[e-1], offs[e]) use `weight[e]`
+    (`[E, N, K]`, `y = x @ weight[e]^T`). `counts` is a host list."""
+
+    @staticmethod
+    def forward(ctx, x, weight, counts):
+        ctx.counts = counts
+        ctx.weight = weight
+        ctx.save_for_backward(x)
+        if F_ops._use_native(x, weight):
+            return native.grouped_gemm_nt(x, weight, counts)
+        out = x.new_empty((x.shape[0], weight.shape[1]), dtype=weight.dtype)
+        r = 0
+        for e, c in enumerate(counts):
+            if c:
+                out[r:r + c] = x[r:r + c].to(weight.dtype) @ weight[e].t()
+            r += c
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        w, counts = ctx.weight, ctx.counts
+        mg = F_ops._main_grad(w)
+        dy = dy.contiguous()
+        if F_ops._use_native(x, w):
+            native.grouped_gemm_tn_accum(dy, x, mg, counts)
+            return native.grouped_gemm_nn(dy, w, counts), None, None
+        dx = torch.empty_like(x)
+        r = 0
+        for e, c in enumerate(counts):
+            if c:
+                dx[r:r + c] = (dy[r:r + c].to(w.dtype) @ w[e]).to(x.dtype)
+                mg[e].add_(dy[r:r + c].float().t() @ x[r:r + c].float())
+            r += c
+        return dx, None, None
+
+
+def grouped_linear(x: torch.Tensor, weight: torch.Tensor, counts: list[int]) -> torch.Tensor:
+    return _GroupedLinear.apply(x, weight, counts)
+
+
+def route(logits: torch.Tensor, k: int):
+    """(weights [M,k] fp32, experts [M,k] int64); differentiable w.r.t. logits."""
+    vals, experts = torch.topk(logits.float(), k, dim=-1)
+    return torch.softmax(vals, dim=-1), experts
+
+
+def aux_loss(logits: torch.Tensor, experts: torch.Tensor, num_experts: int) -> torch.Tensor:
+    probs = torch.softmax(logits.float(), dim=-1).mean(0)
+    frac = torch.bincount(experts.reshape(-1), minlength=num_experts).float() / experts.numel()
+    return num_experts * (frac.detach() * probs).sum()
+
+
+def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_group, ep_size: int,
+                aux_coef: float = 0.0, capacity_factor: float = 0.0):
+    """x `[M, D]`, logits `[M, E]` -> (out `[M, D]`, aux loss or None)."""
+    M, D = x.shape
+    E_local = num_experts // ep_size
+    weights, experts = route(logits, k)                                    # [M,k]
+    aux = aux_loss(logits, experts, num_experts) * aux_coef if aux_coef > 0.0 else None
+
+    flat_e = experts.reshape(-1)                                           # [M*k], pair p = token p//k, slot p%k
+    order = torch.sort(flat_e, stable=True).indices                        # pairs sorted by expert id
+    keep = None
+    if capacity_factor > 0.0:
+        # position of each pair inside its expert's queue; drop what exceeds the capacity
+        cap = max(1, int(capacity_factor * M * k / num_experts))
+        sorted_e = flat_e[order]
+        start = torch.searchsorted(sorted_e, torch.arange(num_experts, device=x.device))
+        pos = torch.arange(M * k, device=x.device) - start[sorted_e]
+        keep = pos < cap
+        order = order[keep]
+    token_of = torch.div(order, k, rounding_mode="floor")
+    sorted_x = x.index_select(0, token_of)                                 # gather (bwd: index_add)
+    counts = torch.bincount(flat_e[order], minlength=num_experts).view(ep_size, E_local)
+
+    if ep_size > 1:
+        recv_counts = exchange_counts(counts, ep_group)                    # [src, E_local]
+        both = torch.stack([counts, recv_counts]).tolist()                 # one host sync for both
+        send_c, recv_c = both
+        send_splits = [sum(r) for r in send_c]
+        recv_splits = [sum(r) for r in recv_c]
+        recv_x = ep_all_to_all(sorted_x, send_splits, recv_splits, ep_group)
+        # rows arrive ordered (src, expert); regroup to (expert, src)
+        regroup = _regroup_index(recv_c, x.device)
+        local_x = recv_x.index_select(0, regroup)
+        per_expert = [sum(recv_c[s][e] for s in range(ep_size)) for e in range(E_local)]
+    else:
+        local_x = sorted_x
+        per_expert = counts.view(-1).tolist()
+
+    gate = grouped_linear(local_x, w_gate, per_expert)
+    up = grouped_linear(local_x, w_up, per_expert)
+    act = F_ops.swiglu(torch.cat([gate, up], dim=-1))
+    y = grouped_linear(act, w_down, per_expert)
+
+    if ep_size > 1:
+        inv = torch.empty_like(regroup)
+        inv[regroup] = torch.arange(regroup.numel(), device=x.device)
+        y = ep_all_to_all(y.index_select(0, inv), recv_splits, send_splits, ep_group)
+
+    w_sorted = weights.reshape(-1)[order]                                  # weight of each sorted pair
+    contrib = y.float() * w_sorted[:, None]
+    out = torch.zeros(M, D, dtype=torch.float32, device=x.device).index_add(0, token_of, contrib)
+    return out.to(x.dtype), aux
+
+
+def _regroup_index(recv_counts: list[list[int]], device) -> torch.Tensor:
+    """Index that reorders rows received as (src-major, expert-minor) blocks
+    into (expert-major, src-minor) order. Pure function of the counts."""
+    ep, E_local = len(recv_counts), len(recv_counts[0])
+    starts, r = [[0] * E_local for _ in range(ep)], 0
+    for s in range(ep):
+        for e in range(E_local):
+            starts[s][e] = r
+            r += recv_counts[s][e]
+    idx = []
+    for e in range(E_local):
+        for s in range(ep):
+            idx.extend(range(starts[s][e], starts[s][e] + recv_counts[s][e]))
+    return torch.tensor(idx, dtype=torch.long, device=device)

@@ -1,0 +1,264 @@
+"""AdamW on flat buffers with ZeRO-1 sharding of optimizer state.
+
+Reference: `distributed/zero1/distributed_optimizer.py:1-185` wraps a
+`torch.optim.AdamW`, assigns WHOLE tensors to ranks with a greedy
+longest-processing-time heuristic, steps the owned tensors and then broadcasts
+every tensor from its owner; gradients reach it through DDP's all-reduce plus a
+per-tensor SP all-reduce and a separate `clip_grad_norm_` pass.
+
+Here the step is one pipeline over each flat buffer (see `parallel.flat`):
+
+    reduce-scatter(main_grad) -> |g|^2 partial -> one scalar all-reduce ->
+    fused clip + AdamW on this rank's even 1/n slice (fp32 master, exp_avg,
+    exp_avg_sq) -> all-gather of the updated compute-dtype parameters
+
+so every rank holds exactly 1/n of the optimizer state regardless of tensor
+sizes (the reference's owner of the embedding holds 1.4-2.5x the ideal share),
+and gradients cross the wire once as a reduce-scatter instead of twice as an
+all-reduce. On CUDA the stages run as kernels of this package over NVLink peer
+memory (`parallel.symm`); on CPU/Gloo they are `torch.distributed` calls.
+
+The reference's public names are kept: `DistributedOptimizer(optimizer,
+process_group, ranks_map, num_parts, verbose)`, `.part_assignment`,
+`partition_tensors`, attribute forwarding to the wrapped optimizer, and a
+`state_dict()` in `torch.optim.AdamW` layout restricted to the tensors this
+rank owns under the whole-tensor assignment (that is the on-disk format).
+"""
+from __future__ import annotations
+
+import heapq
+import math
+from collections import OrderedDict
+
+import torch
+import torch.distributed as dist
+
+from ...ops import native, oracle
+from ..flat import FlatBuffer
+
+
+def partition_tensors(tensor_dict: "OrderedDict[tuple[int, int], torch.Tensor]", ranks_map: list | None = None,
+                      num_parts: int | None = None, verbose: bool = False, deterministic: bool = True):
+    """Greedy balanced assignment of tensors to parts: biggest tensor first,
+    always to the currently lightest part; ties resolved by key (and by part
+    id) so that every rank computes the same answer.
+    Returns `(assignment: key -> owner, tensor_dict)`."""
+    if ranks_map is not None:
+        num_parts = len(ranks_map)
+    assert num_parts and num_parts > 0, "num_parts must be a positive integer"
+    items = [(k, t.numel()) for k, t in tensor_dict.items()]
+    items.sort(key=(lambda kv: (-kv[1], kv[0])) if deterministic else (lambda kv: -kv[1]))
+    heap = [(0, part) for part in range(num_parts)]
+    heapq.heapify(heap)
+    loads = [0] * num_parts
+    assignment = {k: None for k in tensor_dict}
+    for key, n in items:
+        load, part = heapq.heappop(heap)
+        assignment[key] = ranks_map[part] if ranks_map is not None else part
+        loads[part] = load + n
+        heapq.heappush(heap, (load + n, part))
+    if verbose:
+        for part, load in enumerate(loads):
+            if load == 0:
+                print(f"[ZeRO-1] Warning: partition {part} is empty.")
+        mean = sum(loads) / num_parts + 1e-6
+        print(f"[ZeRO-1] Partition load imbalance: {(max(loads) - min(loads)) / mean:.2%}")
+    return assignment, tensor_dict
+
+
+class _Shard:
+    """Optimizer state of one flat buffer on this rank."""
+
+    def __init__(self, buf: FlatBuffer, group, sharded: bool):
+        self.buf, self.group = buf, group
+        self.n = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.sharded = sharded and self.n > 1
+        parts = self.n if self.sharded else 1
+        assert buf.padded % parts == 0, "flat buffer must be padded to a multiple of the shard count"
+        self.len = buf.padded // parts
+        self.lo = (self.rank if self.sharded else 0) * self.len
+        self.hi = self.lo + self.len
+        self.master = buf.init_fp32[self.lo:self.hi].clone()
+        buf.init_fp32 = None                                    # full fp32 copy no longer needed
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.grad_shard = None if not self.sharded else torch.zeros_like(self.master)
+        # slice of the buffer whose |g|^2 this rank contributes to the global norm
+        vlen = buf.padded // self.n
+        self.norm_lo, self.norm_hi = ((self.lo, self.hi) if self.sharded
+                                      else (self.rank * vlen, (self.rank + 1) * vlen))
+
+
+class FusedAdamW:
+    """AdamW (decoupled weight decay on every tensor, like the reference's
+    single param group, `training/trainer.py:137-143`) over flat buffers."""
+
+    def __init__(self, buffers: list[FlatBuffer], lr: float = 1e-3, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, groups: list | None = None, grad_divisor: float = 1.0,
+                 sharded: bool = False, norm_group=None):
+        self.buffers = [b for b in buffers if b is not None]
+        groups = groups if groups is not None else [None] * len(self.buffers)
+        self.param_groups = [dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
+                                  amsgrad=False, maximize=False, params=[])]
+        self.grad_divisor = float(grad_divisor)
+        self.norm_group = norm_group
+        self.shards = [_Shard(b, g, sharded) for b, g in zip(self.buffers, groups)]
+        self.step_count = 0
+        self.grad_norm = None
+        self._comm = None              # optional peer-memory collective engine (CUDA)
+
+    # -- the reference-style surface ------------------------------------------------
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for b in self.buffers:
+            b.zero_grad()
+
+    @torch.no_grad()
+    def step(self, grad_clip_value: float | None = None):
+        """Reduce gradients, clip by global norm, update, re-assemble parameters.
+        Returns the global gradient norm (0-d tensor, before clipping)."""
+        g = self.param_groups[0]
+        self.step_count += 1
+        inv = 1.0 / self.grad_divisor
+        norm_sq = None
+        for s in self.shards:
+            grad = self._reduce(s)
+            part = self._sumsq(grad if s.sharded else s.buf.main_grad[s.norm_lo:s.norm_hi])
+            norm_sq = part if norm_sq is None else norm_sq + part
+        norm_sq = norm_sq * (inv * inv)
+        if self.norm_group is not None and dist.get_world_size(self.norm_group) > 1:
+            dist.all_reduce(norm_sq, op=dist.ReduceOp.SUM, group=self.norm_group)
+        norm = norm_sq.sqrt()
+        if grad_clip_value is not None and grad_clip_value > 0:
+            scale = torch.clamp(grad_clip_value / (norm + 1e-6), max=1.0) * inv
+        else:
+            scale = torch.full_like(norm, inv)
+        for s in self.shards:
+            grad = s.grad_shard if s.sharded else s.buf.main_grad
+            self._update(s, grad, scale, g)
+            self._gather(s)
+        self.grad_norm = norm
+        return norm
+
+    # -- stages -----------------------------------------------------------------------
+    def _reduce(self, s: _Shard) -> torch.Tensor:
+        mg = s.buf.main_grad
+        if s.n == 1:
+            return mg
+        if self._comm is not None:
+            return self._comm.reduce_grads(s)
+        if s.sharded:
+            if mg.is_cuda:
+                dist.reduce_scatter_tensor(s.grad_shard, mg, op=dist.ReduceOp.SUM, group=s.group)
+            else:                                   # Gloo has no reduce-scatter
+                dist.all_reduce(mg, op=dist.ReduceOp.SUM, group=s.group)
+                s.grad_shard.copy_(mg[s.lo:s.hi])
+            return s.grad_shard
+        dist.all_reduce(mg, op=dist.ReduceOp.SUM, group=s.group)
+        return mg
+
+    @staticmethod
+    def _sumsq(x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            return native.sumsq(x)
+        return x.double().pow(2).sum().float()
+
+    def _update(self, s: _Shard, grad: torch.Tensor, scale: torch.Tensor, g: dict) -> None:
+        b1, b2 = g["betas"]
+        out = s.buf.params[s.lo:s.hi]
+        if grad.is_cuda:
+            native.adamw_step(s.master, s.exp_avg, s.exp_avg_sq, grad, out, scale, self.step_count,
+                              g["lr"], b1, b2, g["eps"], g["weight_decay"])
+        else:
+            oracle.adamw_step(s.master, grad, s.exp_avg, s.exp_avg_sq, self.step_count, g["lr"], b1, b2,
+                              g["eps"], g["weight_decay"], grad_scale=float(scale))
+            out.copy_(s.master.to(out.dtype))
+
+    def _gather(self, s: _Shard) -> None:
+        if not s.sharded:
+            return
+        if self._comm is not None:
+            return self._comm.gather_params(s)
+        p = s.buf.params
+        if p.is_cuda:
+            dist.all_gather_into_tensor(p, p[s.lo:s.hi].clone(), group=s.group)
+        else:
+            chunks = list(p.view(s.n, s.len).unbind(0))
+            dist.all_gather(chunks, p[s.lo:s.hi].clone(), group=s.group)
+
+    # -- full-buffer views of sharded state (checkpointing) -----------------------------
+    def gather_full(self, s: _Shard, which: str) -> torch.Tensor:
+        """fp32 tensor of the whole buffer for `which` in {master, exp_avg, exp_avg_sq}."""
+        local = getattr(s, which)
+        if not s.sharded:
+            return local.clone()
+        full = torch.empty(s.buf.padded, dtype=torch.float32, device=local.device)
+        chunks = list(full.view(s.n, s.len).unbind(0))
+        dist.all_gather(chunks, local.contiguous(), group=s.group)
+        return full
+
+    def scatter_full(self, s: _Shard, which: str, full: torch.Tensor) -> None:
+        getattr(s, which).copy_(full[s.lo:s.hi])
+
+    def sync_params_from_master(self) -> None:
+        """Rewrite the compute-dtype parameters from the fp32 master shards."""
+        for s in self.shards:
+            s.buf.params[s.lo:s.hi].copy_(s.master.to(s.buf.params.dtype))
+            self._gather(s)
+
+
+class DistributedOptimizer:
+    """ZeRO-1 front end with the reference's constructor and attribute
+    forwarding. `optimizer` is a `FusedAdamW` built with `sharded=True`."""
+
+    _OWN = {"optimizer", "process_group", "ranks_map", "num_parts", "verbose", "part_assignment",
+            "tensor_dict", "rank", "world_size", "named_tensors"}
+
+    def __init__(self, optimizer: FusedAdamW, process_group, ranks_map=None, num_parts=None, verbose=False,
+                 named_tensors: "OrderedDict[str, torch.Tensor] | None" = None):
+        object.__setattr__(self, "optimizer", optimizer)
+        object.__setattr__(self, "process_group", process_group)
+        object.__setattr__(self, "ranks_map", ranks_map)
+        object.__setattr__(self, "verbose", verbose)
+        self.rank = dist.get_rank(process_group) if process_group is not None else 0
+        self.world_size = dist.get_world_size(process_group) if process_group is not None else 1
+        self.num_parts = num_parts if num_parts is not None else self.world_size
+        assert 1 <= self.num_parts <= self.world_size
+        self.named_tensors = named_tensors if named_tensors is not None else OrderedDict()
+        self.apply_zero1()
+
+    def apply_zero1(self, part_assignment=None) -> None:
+        """Whole-tensor ownership table keyed `(group_idx, param_idx)`; it only
+        decides which rank WRITES which tensor's state into a checkpoint."""
+        self.tensor_dict = OrderedDict(((0, i), t) for i, t in enumerate(self.named_tensors.values()))
+        if part_assignment is None:
+            if self.ranks_map is None:
+                owners = list(range(self.num_parts))
+            else:
+                owners = [dist.get_group_rank(self.process_group, r) for r in self.ranks_map]
+                assert len(set(owners)) == len(owners), f"Duplicate owners in ranks_map: {self.ranks_map}"
+                self.num_parts = len(owners)
+            part_assignment, _ = partition_tensors(self.tensor_dict, ranks_map=owners, verbose=self.verbose)
+        self.part_assignment = part_assignment
+
+    def owned_names(self) -> list[str]:
+        names = list(self.named_tensors.keys())
+        return [names[i] for (g, i), owner in self.part_assignment.items() if owner == self.rank]
+
+    def __getattr__(self, name):
+        return getattr(object.__getattribute__(self, "optimizer"), name)
+
+    def __setattr__(self, name, value):
+        if name in self._OWN or name.startswith("_"):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self.optimizer, name, value)
+
+    def __dir__(self):
+        return sorted(set(dir(type(self)) + list(self.__dict__.keys()) + dir(self.optimizer)))
+
+    def step(self, *args, **kwargs):
+        return self.optimizer.step(*args, **kwargs)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.optimizer.zero_grad(set_to_none)

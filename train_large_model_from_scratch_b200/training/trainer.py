@@ -1,0 +1,459 @@
+"""Training runtime: distributed init, data, model, optimizer, step loop,
+evaluation, checkpointing, profiling and throughput/MFU reporting.
+
+Public surface and overridable hooks follow the reference's `Trainer`
+(`training/trainer.py:37-408`): `Trainer(config).train()`, `.eval()`,
+`.save(step)`, `_init_distributed/_init_dataset/_init_model/_init_optimizer/
+_init_profiler/_init_logging`, `_lr_scheduler`, `_one_training_micro_step`,
+`_one_training_step`, `_resume_from_checkpoint`. Console line, `log.txt`
+grammar (`"{step} train {loss:.6f}"`, `"{step} val {loss:.4f}"`), log-directory
+name and checkpoint files are the same.
+
+What is different underneath: there is no DDP wrapper and no autocast. The
+model's parameters and gradients live in flat buffers; the optimizer step is
+reduce-scatter -> global-norm clip -> fused AdamW -> all-gather over those
+buffers (one pass for DP averaging, SP summation and ZeRO-1), and step time is
+also measured on the device with CUDA events.
+"""
+from __future__ import annotations
+
+import math
+import os
+import socket
+import time
+from collections import OrderedDict
+from contextlib import contextmanager, nullcontext
+from itertools import islice
+
+import torch
+import torch.distributed as dist
+
+from ..models import GPT
+from ..models.gpt import EXPERT_LOCAL_PARAM_SUFFIXES
+from ..parallel import parallel_state
+from ..parallel.zero1.distributed_optimizer import DistributedOptimizer, FusedAdamW
+from ..utils import compute_mfu, get_model_params, get_training_info, set_seed
+from ..utils.profile import get_measured_peak_flops
+from ..utils.training import lr_schedule
+from . import checkpoint as ckpt
+from .config import Config
+from .data import MockDataset, build_loader
+
+try:
+    from tqdm.auto import tqdm
+except Exception:                                           # pragma: no cover
+    tqdm = None
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class Trainer:
+    def __init__(self, config: Config):
+        self.config = config
+        self._init_distributed(config)
+        t = config.train
+        micro_tokens = t.batch_size * t.seq_len * self.dp_world_size
+        assert t.total_batch_size % micro_tokens == 0, (
+            f"make sure total_batch_size {t.total_batch_size} is divisible by batch_size {t.batch_size} * "
+            f"seq_len {t.seq_len} * dp_world_size {self.dp_world_size}")
+        if self.master_process:
+            print(f"Training config: {config.as_dict()}")
+        self._init_dataset(config)
+        self.training_info = get_training_info(
+            len(self.train_dataset), t.seq_len, t.total_batch_size, t.batch_size, self.dp_world_size,
+            t.max_steps, t.max_epochs)
+        if config.optim.warmup_steps >= self.training_info["max_steps"]:
+            raise ValueError(f"warmup_steps must be < max_steps. Got warmup_steps={config.optim.warmup_steps}, "
+                             f"max_steps={self.training_info['max_steps']}.")
+        if self.master_process:
+            print(f"The training process will train {self.training_info['epochs']} epochs, "
+                  f"{self.training_info['max_steps']} steps.")
+            print(f"=> calculated gradient accumulation steps: {self.training_info['grad_accum_steps']}")
+            print(f"=> calculated tokens per step: {self.training_info['total_tokens_per_step']}")
+        self._init_model(config)
+        self._init_optimizer(config)
+        self._init_logging(config)
+        self.start_step = 0
+        self.results = {}
+        self.one_step_results = {}
+        self.train_loader_iter = None
+        self.profiler = None
+        self.profiler_record_fn = self._null_record
+        self.step_ms_device = None
+
+    # ------------------------------------------------------------------ init hooks
+    def _init_distributed(self, config: Config) -> None:
+        self.rank = int(os.environ.get("RANK", 0))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", 0))
+        self.world_size = int(os.environ.get("WORLD_SIZE", 1))
+        self.use_cuda = torch.cuda.is_available()
+        backend = config.parallel.backend
+        if backend == "nccl" and not self.use_cuda:
+            backend = "gloo"
+        self.backend = backend
+        self._owns_pg = False
+        if not dist.is_initialized():
+            if config.parallel.init_method == "env://":
+                os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+                os.environ.setdefault("MASTER_PORT", str(_free_port()))
+                os.environ.setdefault("RANK", "0")
+                os.environ.setdefault("WORLD_SIZE", "1")
+            kwargs = {}
+            if self.use_cuda and backend == "nccl":
+                kwargs["device_id"] = torch.device("cuda", self.local_rank)
+            dist.init_process_group(backend=backend, init_method=config.parallel.init_method, **kwargs)
+            self._owns_pg = True
+        if self.use_cuda:
+            torch.cuda.set_device(self.local_rank)
+            self.device = torch.device("cuda", self.local_rank)
+        else:
+            self.device = torch.device("cpu")
+        set_seed(config.seed.seed + self.rank, deterministic=config.seed.deterministic)
+        self.master_process = self.rank == 0
+        if not parallel_state.is_initialized():
+            parallel_state.initialize_model_parallel(config=config.parallel)
+        ps = parallel_state
+        self.dp_group, self.dp_rank, self.dp_world_size = ps.get_dp_group(), ps.get_dp_rank(), ps.get_dp_world_size()
+        self.sp_group, self.sp_rank, self.sp_world_size = ps.get_sp_group(), ps.get_sp_rank(), ps.get_sp_world_size()
+        self.dp_sp_group, self.dp_sp_rank, self.dp_sp_world_size = (
+            ps.get_dp_sp_group(), ps.get_dp_sp_rank(), ps.get_dp_sp_world_size())
+
+    def _init_dataset(self, config: Config) -> None:
+        d, t = config.data, config.train
+        if d.use_mock_data:
+            self.train_dataset = MockDataset(d.mock_data_num_samples, t.seq_len, base_seed=config.seed.seed)
+            self.val_dataset = (MockDataset(d.mock_data_num_samples // 10, t.seq_len, base_seed=config.seed.seed,
+                                            seed_offset=1_000_000_000) if t.do_val else None)
+        else:
+            raise NotImplementedError(
+                "no built-in on-disk dataset: pass --use_mock_data or subclass Trainer and override "
+                "_init_dataset (see pretrain_example.py)")
+        self._build_loaders(config)
+
+    def _build_loaders(self, config: Config) -> None:
+        d, t = config.data, config.train
+        self.train_sampler, self.train_loader = build_loader(
+            self.train_dataset, t.batch_size, self.dp_world_size, self.dp_rank, True, d.num_workers, d.pin_memory)
+        if getattr(self, "val_dataset", None) is not None:
+            self.val_sampler, self.val_loader = build_loader(
+                self.val_dataset, t.batch_size, self.dp_world_size, self.dp_rank, False, d.num_workers, d.pin_memory)
+        else:
+            self.val_dataset = self.val_loader = None
+
+    def _compute_dtype(self, precision: str) -> torch.dtype:
+        if precision == "fp16":
+            raise NotImplementedError("FP16 precision is not supported yet")
+        if precision == "fp32" or not self.use_cuda:
+            return torch.float32
+        if precision == "bf16":
+            return torch.bfloat16
+        raise ValueError(f"Unsupported precision: {precision}. Supported precisions are: bf16, fp32.")
+
+    def _init_model(self, config: Config) -> None:
+        self.model_config = config.model
+        if self.master_process:
+            print(f"Params config: {get_model_params(self.model_config)}")
+        self.model = GPT(self.model_config, device=self.device,
+                         compute_dtype=self._compute_dtype(config.train.precision),
+                         shard_world=self.dp_sp_world_size)
+        self.raw_model = self.model
+
+    def _init_optimizer(self, config: Config) -> None:
+        o = config.optim
+        zero1 = config.parallel.use_distributed_optimizer
+        m = self.raw_model
+        # dense parameters are replicated over the whole world (their gradients are
+        # summed over SP and averaged over DP); expert parameters only over DP.
+        buffers = [m.dense_buf] + ([m.expert_buf] if m.expert_buf is not None else [])
+        groups = [self.dp_sp_group] + ([self.dp_group] if m.expert_buf is not None else [])
+        fused = FusedAdamW(buffers, lr=o.max_lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
+                           weight_decay=o.weight_decay, groups=groups, grad_divisor=self.dp_world_size,
+                           sharded=zero1, norm_group=self.dp_sp_group)
+        if self.use_cuda and self.world_size > 1 and os.environ.get("TLM_COMM", "symm") == "symm":
+            from ..parallel.symm import PeerCollectives
+            fused._comm = PeerCollectives.create(fused, wire_dtype=config.parallel.grad_wire_dtype)
+        if zero1:
+            named = OrderedDict((n, p) for n, p in m.named_parameters())
+            self.optimizer = DistributedOptimizer(optimizer=fused, process_group=self.dp_group, named_tensors=named)
+            self.raw_optimizer = self.optimizer.optimizer
+        else:
+            self.optimizer = self.raw_optimizer = fused
+
+    @staticmethod
+    @contextmanager
+    def _null_record(name: str):
+        yield
+
+    def _init_profiler(self, config: Config) -> None:
+        t = config.train
+        if t.use_profiler:
+            assert t.steps_to_profile[0] >= 1, "steps_to_profile[0] should be >= 1"
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if self.use_cuda:
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+
+            def on_ready(prof):
+                if self.master_process:
+                    prof.export_chrome_trace(f"{self.log_dir}/rank{self.rank}_trace.json")
+            self.profiler = torch.profiler.profile(
+                schedule=torch.profiler.schedule(wait=t.steps_to_profile[0] - 1, warmup=1,
+                                                 active=t.steps_to_profile[1] + 1 - t.steps_to_profile[0], repeat=1),
+                on_trace_ready=on_ready, record_shapes=True, with_stack=True, with_flops=True, activities=acts)
+            self.profiler_record_fn = torch.profiler.record_function
+        else:
+            self.profiler = None
+            self.profiler_record_fn = self._null_record
+
+    def _init_logging(self, config: Config) -> None:
+        n_params = sum(p.numel() for p in self.raw_model.parameters())
+        self.log_dir = os.path.join(
+            config.logging.log_dir,
+            f"{config.logging.exp_name}_modelsize_{n_params}_lr{config.optim.max_lr}_BS{config.train.batch_size}_"
+            f"SL{config.train.seq_len}_DP{self.dp_world_size}_SEP{parallel_state.get_sep_world_size()}_")
+        self.log_file = os.path.join(self.log_dir, "log.txt")
+        if self.master_process:
+            os.makedirs(self.log_dir, exist_ok=True)
+            resuming = ckpt.find_latest_complete(config.ckpt.resume_path or self.log_dir, self.rank) is not None
+            if not resuming:
+                open(self.log_file, "w").close()
+        if self.world_size > 1:
+            dist.barrier()
+
+    # ------------------------------------------------------------------ schedule / precision
+    def _lr_scheduler(self, it: int, max_steps: int, warmup_steps: int, max_lr: float, min_lr: float) -> float:
+        return lr_schedule(it, max_steps, warmup_steps, max_lr, min_lr)
+
+    def _autocast_context(self, precision: str):
+        """Kept for API parity. Mixed precision is built into the ops (bf16
+        GEMM inputs, fp32 residual/norm/loss), so no autocast is needed."""
+        if precision == "fp16":
+            raise NotImplementedError("FP16 precision is not supported yet")
+        if precision not in ("bf16", "fp32"):
+            raise ValueError(f"Unsupported precision: {precision}. Supported precisions are: bf16, fp32.")
+        return nullcontext()
+
+    # ------------------------------------------------------------------ steps
+    def _sp_slice(self, x: torch.Tensor) -> torch.Tensor:
+        T = x.shape[1]
+        assert T % self.sp_world_size == 0, "sequence length must be divisible by sp_world_size"
+        c = T // self.sp_world_size
+        return x[:, self.sp_rank * c:(self.sp_rank + 1) * c]
+
+    def _to_device(self, x: torch.Tensor) -> torch.Tensor:
+        x = self._sp_slice(x)
+        if not self.use_cuda:
+            return x.contiguous()
+        if x.is_pinned() and self.sp_world_size == 1:
+            return x.to(self.device, non_blocking=True)
+        x = x.contiguous()
+        if self.config.data.pin_memory:
+            x = x.pin_memory()
+        return x.to(self.device, non_blocking=True)
+
+    def _one_training_micro_step(self, config: Config, micro_step: int, data_batch: dict):
+        x, y = self._to_device(data_batch["input_ids"]), self._to_device(data_batch["labels"])
+        ga = self.training_info["grad_accum_steps"]
+        with self.profiler_record_fn("forward"):
+            _, loss, logging_loss = self.model(x, y, loss_scale=1.0 / ga)
+        with self.profiler_record_fn("backward"):
+            loss.backward()
+        return logging_loss.detach()
+
+    def _next_batch(self) -> dict:
+        if self.train_loader_iter is None:
+            self.train_loader_iter = enumerate(self.train_loader)
+        try:
+            _, batch = next(self.train_loader_iter)
+        except StopIteration:
+            self._epoch = getattr(self, "_epoch", 0) + 1
+            self.train_sampler.set_epoch(self._epoch)
+            self.train_loader_iter = enumerate(self.train_loader)
+            _, batch = next(self.train_loader_iter)
+        return batch
+
+    def _one_training_step(self, config: Config, step: int) -> None:
+        self.model.train()
+        self.optimizer.zero_grad()
+        loss_accum = None
+        for micro_step in range(self.training_info["grad_accum_steps"]):
+            l = self._one_training_micro_step(config, micro_step, self._next_batch())
+            loss_accum = l if loss_accum is None else loss_accum + l
+        lr = self._lr_scheduler(step, self.training_info["max_steps"], config.optim.warmup_steps,
+                                config.optim.max_lr, config.optim.min_lr)
+        for group in self.optimizer.param_groups:
+            group["lr"] = lr
+        norm = self.optimizer.step(grad_clip_value=config.train.grad_clip_value)
+        if self.dp_world_size > 1:
+            dist.all_reduce(loss_accum, op=dist.ReduceOp.SUM, group=self.dp_group)
+            loss_accum = loss_accum / self.dp_world_size
+        self.one_step_results["lr"] = lr
+        self.one_step_results["loss"] = loss_accum
+        self.one_step_results["grad_norm"] = norm
+
+    def train_step(self, step: int) -> dict:
+        """One optimizer step (all micro-steps). Public entry for callers that
+        drive the loop themselves; returns `{lr, loss, grad_norm}` with `loss`
+        and `grad_norm` as 0-d tensors on the training device."""
+        self.one_step_results = {}
+        self._one_training_step(self.config, step)
+        return self.one_step_results
+
+    # ------------------------------------------------------------------ resume / save
+    def _steps_per_epoch(self) -> int:
+        return max(1, len(self.train_loader) // self.training_info["grad_accum_steps"])
+
+    def _resume_from_checkpoint(self, steps_per_epoch: int | None = None) -> None:
+        ckpt_dir = self.config.ckpt.resume_path or self.log_dir
+        prefix = ckpt.find_latest_complete(ckpt_dir, self.rank)
+        if self.world_size > 1:                         # all ranks must agree
+            objs = [prefix]
+            dist.broadcast_object_list(objs, src=0)
+            prefix = objs[0]
+        if prefix is None:
+            self.start_step = 0
+            return
+        meta = torch.load(f"{prefix}_meta.pt", map_location="cpu", weights_only=False)
+        state = torch.load(f"{prefix}_model.pt", map_location="cpu", weights_only=True)
+        ckpt.load_model_state_dict(self.raw_model, self.optimizer, state)
+        key = f"optimizer/rank{self.rank}"
+        placeholder = {key: ckpt.optimizer_state_dict(self.raw_model, self.optimizer)}
+        ckpt.dcp_load(placeholder, f"{prefix}_opt")
+        ckpt.load_optimizer_state_dict(self.raw_model, self.optimizer, placeholder[key])
+        sampler_state = meta.get("sampler_state", {})
+        epoch, iter_idx = sampler_state.get("epoch", 0), sampler_state.get("iter_idx", 0)
+        self._epoch = epoch
+        self.train_sampler.set_epoch(epoch)
+        self.train_loader_iter = enumerate(islice(self.train_loader, iter_idx, None), start=iter_idx)
+        step = meta.get("step")
+        self.start_step = step + 1 if step is not None else 0
+        if self.master_process:
+            print(f"=> Resumed from {ckpt_dir} | next_step={self.start_step}, sampler_epoch={epoch}, "
+                  f"dataloader_iter_idx={iter_idx}")
+        rng_path = f"{prefix}_rng_rank{self.rank}.pt"
+        if os.path.exists(rng_path):
+            ckpt.set_rng_state(torch.load(rng_path, map_location="cpu", weights_only=False), self.local_rank)
+        if self.world_size > 1:
+            dist.barrier()
+        if self.use_cuda:
+            torch.cuda.synchronize()
+
+    def save(self, step: int | None = None) -> None:
+        step = 0 if step is None else step
+        os.makedirs(self.log_dir, exist_ok=True)
+        prefix = os.path.join(self.log_dir, f"{step:05d}")
+        spe = self._steps_per_epoch()
+        ga = self.training_info["grad_accum_steps"]
+        nxt = step + 1
+        sampler_state = {"epoch": nxt // spe, "iter_idx": (nxt % spe) * ga}
+        model_state = ckpt.full_model_state_dict(self.raw_model, self.optimizer)        # collective
+        opt_state = ckpt.optimizer_state_dict(self.raw_model, self.optimizer)           # collective
+        ckpt.dcp_save({f"optimizer/rank{self.rank}": opt_state}, f"{prefix}_opt")
+        rng = ckpt.rng_state(self.local_rank)
+        ckpt._atomic_save(rng, f"{prefix}_rng_rank{self.rank}.pt")
+        if self.world_size > 1:
+            dist.barrier()
+        if self.master_process:
+            ckpt._atomic_save(model_state, f"{prefix}_model.pt")
+            results = {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in self.one_step_results.items()}
+            meta = {
+                "trainer_config": self.config.as_dict(),
+                "model_config": self.raw_model.config.as_dict(),
+                "step": step,
+                "this_step_results": results,
+                "opt_part_assignment": getattr(self.optimizer, "part_assignment", None),
+                "sampler_state": sampler_state,
+                "rng_state": rng,
+            }
+            ckpt._atomic_save(meta, f"{prefix}_meta.pt")                               # commit marker, last
+        if self.world_size > 1:
+            dist.barrier()
+
+    # ------------------------------------------------------------------ loops
+    def train(self) -> None:
+        cfg = self.config
+        self.results = {}
+        self.train_loader_iter = enumerate(self.train_loader)
+        self._resume_from_checkpoint(self._steps_per_epoch())
+        self._init_profiler(cfg)
+        if self.profiler:
+            self.profiler.start()
+        max_steps = self.training_info["max_steps"]
+        ga = self.training_info["grad_accum_steps"]
+        steps = range(self.start_step, max_steps)
+        bar = tqdm(steps, initial=self.start_step, total=max_steps, desc="Train",
+                   disable=not self.master_process) if tqdm is not None else steps
+        write = tqdm.write if tqdm is not None else print
+        measured_peak = get_measured_peak_flops()
+        for step in bar:
+            self.one_step_results = {}
+            t0 = time.time()
+            last_step = step == max_steps - 1
+            if self.use_cuda:
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+            with self.profiler_record_fn("training_step"):
+                self._one_training_step(cfg, step)
+            if self.use_cuda:
+                ev1.record()
+                torch.cuda.synchronize()
+                self.step_ms_device = ev0.elapsed_time(ev1)
+            if self.profiler:
+                self.profiler.step()
+            if not cfg.train.debug and cfg.train.do_val and (step % cfg.train.val_every_steps == 0 or last_step):
+                self.eval()
+                if self.master_process:
+                    write(f"validation loss: {self.one_step_results['val_loss'].item():.4f}")
+                    with open(self.log_file, "a") as f:
+                        f.write(f"{step} val {self.one_step_results['val_loss'].item():.4f}\n")
+            if cfg.ckpt.do_save and not cfg.train.debug and step > 0 and (
+                    step % cfg.ckpt.save_every_steps == 0 or last_step):
+                self.save(step)
+            dt = time.time() - t0
+            tokens = cfg.train.batch_size * cfg.train.seq_len * ga * self.dp_world_size
+            mfu, _, _ = compute_mfu(self.raw_model, cfg.train.batch_size, cfg.train.seq_len, dt, ga, dtype="bf16") \
+                if self.use_cuda else (0.0, 0.0, 0.0)
+            if self.master_process:
+                loss_v = float(self.one_step_results["loss"])
+                extra = ""
+                if self.use_cuda and measured_peak:
+                    m2, _, _ = compute_mfu(self.raw_model, cfg.train.batch_size, cfg.train.seq_len, dt, ga,
+                                           peak_flops=measured_peak)
+                    extra = f" | MFU(measured peak): {m2 * 100:.2f}% | dt(device): {self.step_ms_device:.2f}ms"
+                write(f"step {step:5d} | loss: {loss_v:.6f} | lr {self.one_step_results['lr']:.4e} | "
+                      f"grad norm: {float(self.one_step_results['grad_norm']):.4f} | dt: {dt * 1000:.2f}ms | "
+                      f"tok/sec: {tokens / dt:.2f} | MFU: {mfu * 100:.2f}%{extra}")
+                with open(self.log_file, "a") as f:
+                    f.write(f"{step} train {loss_v:.6f}\n")
+            self.results[step] = self.one_step_results
+        if self.profiler:
+            self.profiler.stop()
+        self.close()
+
+    def close(self) -> None:
+        if self._owns_pg and dist.is_initialized():
+            parallel_state.destroy_model_parallel()
+            dist.destroy_process_group()
+            self._owns_pg = False
+
+    @torch.no_grad()
+    def eval(self) -> None:
+        self.model.eval()
+        n = len(self.val_loader)
+        acc = None
+        it = self.val_loader
+        if tqdm is not None:
+            it = tqdm(it, desc="Val", disable=not self.master_process)
+        for batch in it:
+            x, y = self._to_device(batch["input_ids"]), self._to_device(batch["labels"])
+            _, _, logging_loss = self.model(x, y, loss_scale=1.0 / n)
+            acc = logging_loss if acc is None else acc + logging_loss
+        if self.use_cuda:
+            torch.cuda.synchronize()
+        if self.dp_world_size > 1:
+            dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.dp_group)
+            acc = acc / self.dp_world_size
+        self.one_step_results["val_loss"] = acc
