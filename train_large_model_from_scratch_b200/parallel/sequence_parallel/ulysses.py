@@ -26,14 +26,16 @@ class _AllToAllEqual(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
+        x = x.contiguous()
         out = torch.empty_like(x)
-        dist.all_to_all_single(out, x.contiguous(), group=group)
+        dist.all_to_all_single(out, x, group=group)
         return out
 
     @staticmethod
     def backward(ctx, g):
+        g = g.contiguous()          # empty_like of a permuted grad would keep its strides
         out = torch.empty_like(g)
-        dist.all_to_all_single(out, g.contiguous(), group=ctx.group)
+        dist.all_to_all_single(out, g, group=ctx.group)
         return out, None
 
 

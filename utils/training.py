@@ -1,0 +1,1 @@
+from train_large_model_from_scratch_b200.utils.training import *  # noqa: F401,F403
