@@ -1,0 +1,301 @@
+"""Headline benchmark: training throughput (tokens/s, whole job) of the
+0.25B-class dense GPT (16 layers, hidden 1024, 16 query / 8 KV heads, SwiGLU
+4096, vocab 50304, tied embeddings, RoPE), bf16, sequence length 4096,
+micro-batch 8 per GPU, 2 gradient-accumulation micro-steps per optimizer step,
+ZeRO-1 over DP = N, grad-clip 1.0, synthetic uniform-random tokens, random-init
+weights.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+For N > 1 launch with torchrun (one rank per GPU). Rank 0 prints ONE JSON line.
+
+`value`  : device-timed (CUDA events, max over ranks) tokens/s with the step's
+           batches already resident on the device.
+`e2e`    : the same metric through the public `Trainer.train_step` API with the
+           trainer's own data loader: every step copies its input ids / labels
+           from pinned host memory and reads the loss back to the host.
+`--impl reference` runs the unmodified reference from `baseline/_ref` through
+its own `Trainer` for the same model and batch shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+MODEL = dict(num_layer=16, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+             intermediate_size=4096, vocab_size=50304, block_size=4096)
+SEQ_LEN, MICRO_BATCH, GRAD_ACCUM = 4096, 8, 2
+BASELINE_TOKENS_PER_S = None          # the reference publishes no number
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock / throttle reasons of this rank's GPU with nvidia-smi
+    (read-only queries) while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1])); mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        os.remove(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _visible_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            pass
+    return local_rank
+
+
+def _dist_env():
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("LOCAL_RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    return int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+
+
+def _timed(torch, dist, world, fn, steps):
+    """barrier + sync, K steps between CUDA events, sync + barrier; max over ranks (ms)."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = (time.time() - t0) * 1e3
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item()), wall
+
+
+def _flags(n_gpus: int, steps_total: int, log_dir: str) -> list[str]:
+    tokens = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n_gpus
+    samples = MICRO_BATCH * GRAD_ACCUM * n_gpus * (steps_total + 4)
+    f = ["--use_mock_data", "--mock_data_num_samples", str(samples), "--total_batch_size", str(tokens),
+         "--batch_size", str(MICRO_BATCH), "--seq_len", str(SEQ_LEN), "--max_steps", str(steps_total + 4),
+         "--warmup_steps", "2", "--max_lr", "6e-4", "--min_lr", "6e-5", "--weight_decay", "0.1",
+         "--grad_clip_value", "1.0", "--debug", "--sep_size", "1", "--use_distributed_optimizer", "--tied_lm_head",
+         "--pin_memory", "--precision", "bf16", "--log_dir", log_dir, "--exp_name", "bench"]
+    for k, v in MODEL.items():
+        f += [f"--{k}", str(v)]
+    return f
+
+
+def _result(impl, n, steps, warmup, ms_total, tokens_per_step, clocks, extra):
+    ms_step = ms_total / steps
+    value = tokens_per_step / (ms_step / 1e3)
+    out = {
+        "metric": "training throughput, 0.25B-class dense GPT (tokens/s, whole job, max over ranks)",
+        "value": value, "unit": "tokens/s", "n_gpus": n, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+        "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": impl,
+        "config": {"model": "dense GPT 16L/1024/16q-8kv/SwiGLU-4096/vocab 50304 tied (0.30B params)",
+                   "global_batch": tokens_per_step, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
+                   "grad_accum": GRAD_ACCUM, "parallelism": f"dp{n} zero1",
+                   "l2": "per-step working set (~20 GB of activations) far exceeds the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+    }
+    out.update(extra)
+    return out
+
+
+# --------------------------------------------------------------------------- our implementation
+def run_ours(args) -> dict:
+    rank, local_rank, world = _dist_env()
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from train_large_model_from_scratch_b200.ops import native
+    from train_large_model_from_scratch_b200.training import Trainer, build_config, parse_args
+
+    n, K, W = args.gpus, args.steps, args.warmup
+    assert world == n, f"--gpus {n} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {n}"
+    log_dir = tempfile.mkdtemp(prefix="tlm_bench_")
+    cfg = build_config(parse_args(_flags(n, 2 * (K + W), log_dir)))
+    trainer = Trainer(cfg)
+    dev = trainer.device
+    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n
+
+    # ---- device-resident batches (kernel-side number) ----
+    gen = torch.Generator().manual_seed(1234 + rank)
+    pool = []
+    for _ in range(4):
+        step_batches = []
+        for _ in range(GRAD_ACCUM):
+            d = torch.randint(0, MODEL["vocab_size"], (MICRO_BATCH, SEQ_LEN + 1), generator=gen)
+            step_batches.append({"input_ids": d[:, :-1].to(dev), "labels": d[:, 1:].to(dev)})
+        pool.append(step_batches)
+    counter = {"i": 0}
+
+    def step_device(i):
+        trainer.train_step(counter["i"], batches=pool[counter["i"] % len(pool)])
+        counter["i"] += 1
+
+    for i in range(W):
+        step_device(i)
+    native.raise_on_device_status()
+    sampler = ClockSampler(_visible_gpu_index(local_rank))
+    sampler.start()
+    native.reset_launch_count()
+    ms_dev, _ = _timed(torch, dist, world, step_device, K)
+    launches = native.launch_count()
+    clocks = sampler.stop()
+    native.raise_on_device_status()
+
+    # ---- end to end through the public API: loader -> pinned H2D -> step -> loss D2H ----
+    losses = []
+
+    def step_e2e(i):
+        r = trainer.train_step(counter["i"])
+        counter["i"] += 1
+        losses.append(float(r["loss"]))            # device -> host read of the step's result
+
+    for i in range(max(1, W // 2)):
+        step_e2e(i)
+    ms_e2e, _ = _timed(torch, dist, world, step_e2e, K)
+    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * SEQ_LEN * 8       # ids + labels, int64, per rank
+    extra = {
+        "e2e": {"value": tokens_per_step / (ms_e2e / K / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
+                "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
+        "gpu_launches": launches,
+        "final_loss": losses[-1] if losses else None,
+    }
+    out = _result("ours", n, K, W, ms_dev, tokens_per_step, clocks, extra)
+    trainer.close()
+    return out if rank == 0 else None
+
+
+# --------------------------------------------------------------------------- the reference, unmodified
+def run_reference(args) -> dict:
+    rank, local_rank, world = _dist_env()
+    if not os.path.isdir(os.path.join(REF_DIR, "training")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is missing (reference tree not installed)"} \
+            if rank == 0 else None
+    sys.path[:] = [REF_DIR] + [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    import torch
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "the reference requires CUDA (model/gpt.py:42)"} if rank == 0 else None
+    import torch.distributed as dist
+    from training import Trainer, build_config, parse_args                    # the reference's own modules
+
+    n, K, W = args.gpus, args.steps, args.warmup
+    log_dir = tempfile.mkdtemp(prefix="ref_bench_")
+    flags = [f for f in _flags(n, 2 * (K + W), log_dir)]
+    if args.ref_compile:
+        flags.append("--use_compile")
+    cfg = build_config(parse_args(flags))
+    trainer = Trainer(cfg)
+    # what Trainer.train() does before and inside its loop (training/trainer.py:308-351)
+    trainer.results = {}
+    trainer.train_loader_iter = enumerate(trainer.train_loader)
+    trainer.start_step = 0
+    trainer._init_profiler(cfg)
+    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n
+    counter = {"i": 0}
+    losses = []
+
+    def step(i):
+        trainer.one_step_results = {}
+        trainer._one_training_step(cfg, counter["i"])
+        torch.cuda.synchronize()
+        losses.append(trainer.one_step_results["loss"].item())
+        counter["i"] += 1
+
+    for i in range(W):
+        step(i)
+    sampler = ClockSampler(_visible_gpu_index(local_rank))
+    sampler.start()
+    ms, _ = _timed(torch, dist, world, step, K)
+    clocks = sampler.stop()
+    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * SEQ_LEN * 8
+    extra = {"e2e": {"value": tokens_per_step / (ms / K / 1e3), "unit": "tokens/s", "ms_per_step": ms / K,
+                     "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
+             "gpu_launches": None, "final_loss": losses[-1], "use_compile": bool(args.ref_compile)}
+    out = _result("reference", n, K, W, ms, tokens_per_step, clocks, extra)
+    dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-compile", type=int, default=0,
+                    help="reference arm: pass --use_compile to the reference (its CLI default is off)")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        try:
+            out = run_reference(args)
+        except Exception as e:                                       # report, never crash the driver
+            out = {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"} \
+                if int(os.environ.get("RANK", 0)) == 0 else None
+    else:
+        out = run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

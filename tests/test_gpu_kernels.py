@@ -1,0 +1,183 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from train_large_model_from_scratch_b200.ops import native
+    native.lib()                      # a missing library is an error on a GPU machine
+    yield native
+    torch.cuda.synchronize()
+    assert native.take_device_status() == 0
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 192), (200, 264, 72), (1000, 1096, 520),
+               (4096, 2048, 1024), (64, 8, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nt(nat, M, N, K):
+    x, w = _rand(M, K, seed=1), _rand(N, K, seed=2)
+    y = nat.gemm_nt(x, w)
+    ref = x.float() @ w.float().t()
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert _rel_err(y, ref) < 6e-3
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nn(nat, M, N, K):
+    dy, w = _rand(M, N, seed=3), _rand(N, K, seed=4)
+    dx = nat.gemm_nn(dy, w)
+    ref = dy.float() @ w.float()
+    assert _rel_err(dx, ref) < 6e-3
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_tn_accum(nat, M, N, K):
+    dy, x = _rand(M, N, seed=5), _rand(M, K, seed=6)
+    acc = torch.ones(N, K, device="cuda")
+    nat.gemm_tn_accum(dy, x, acc)
+    ref = 1.0 + dy.float().t() @ x.float()
+    assert _rel_err(acc, ref) < 1e-4
+    nat.gemm_tn_accum(dy, x, acc)                       # accumulates
+    assert _rel_err(acc, 2 * ref - 1.0) < 1e-4
+
+
+def test_gemm_strided_output_and_guard_rows(nat):
+    """Output written into a slice of a larger buffer must not touch its neighbours."""
+    M, N, K = 200, 264, 72
+    x, w = _rand(M, K, seed=7), _rand(N, K, seed=8)
+    big = torch.full((M + 16, N + 24), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = big[8:8 + M, 8:8 + N]
+    nat.gemm_raw(x, w, out, M, N, K, x.stride(0), w.stride(0), big.stride(0), 0, 0, 0)
+    assert _rel_err(out, x.float() @ w.float().t()) < 6e-3
+    mask = torch.ones_like(big, dtype=torch.bool)
+    mask[8:8 + M, 8:8 + N] = False
+    assert (big[mask] == 7.0).all()
+
+
+def test_embedding(nat):
+    w = _rand(1000, 256, seed=9)
+    idx = torch.randint(0, 1000, (3, 50), device="cuda")
+    out = nat.embedding_fwd(idx, w)
+    torch.testing.assert_close(out, w[idx.reshape(-1)].float())
+    dx = torch.randn(150, 256, device="cuda")
+    g = torch.zeros(1000, 256, device="cuda")
+    nat.embedding_bwd(idx, dx, g)
+    ref = torch.zeros_like(g).index_add_(0, idx.reshape(-1), dx)
+    torch.testing.assert_close(g, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("rows,D,has_delta", [(37, 256, True), (64, 1024, True), (5, 3072, False), (130, 64, True)])
+def test_add_rmsnorm(nat, rows, D, has_delta):
+    x = torch.randn(rows, D, device="cuda")
+    delta = _rand(rows, D, seed=10) if has_delta else None
+    w = (1.0 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    x_new, h, rstd = nat.add_rmsnorm_fwd(x, delta, w, 1e-6)
+    xr = x + (delta.float() if has_delta else 0.0)
+    rr = torch.rsqrt(xr.pow(2).mean(-1) + 1e-6)
+    torch.testing.assert_close(x_new, xr)
+    torch.testing.assert_close(rstd, rr, rtol=1e-5, atol=1e-6)
+    assert _rel_err(h, xr * rr[:, None] * w.float()) < 4e-3
+    g_xnew = torch.randn(rows, D, device="cuda")
+    g_h = _rand(rows, D, seed=11)
+    mg = torch.zeros(D, device="cuda")
+    g_x, g_delta = nat.add_rmsnorm_bwd(g_xnew, g_h, x_new, rstd, w, mg, has_delta)
+    xhat = xr * rr[:, None]
+    gxh = g_h.float() * w.float()
+    ref = g_xnew + rr[:, None] * (gxh - xhat * (gxh * xhat).mean(-1, keepdim=True))
+    torch.testing.assert_close(g_x, ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(mg, (g_h.float() * xhat).sum(0), rtol=1e-3, atol=1e-3)
+    if has_delta:
+        assert _rel_err(g_delta, ref) < 4e-3
+    g_x2, _ = nat.add_rmsnorm_bwd(None, g_h, x_new, rstd, w, mg, False)
+    torch.testing.assert_close(g_x2, ref - g_xnew, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("hd,variant", [(64, "reference"), (128, "standard"), (32, "reference")])
+def test_rope(nat, hd, variant):
+    from train_large_model_from_scratch_b200.ops import oracle
+    B, T, Hq, Hkv = 2, 24, 4, 2
+    qkv = _rand(B, T, Hq + 2 * Hkv, hd, seed=12)
+    cos, sin = oracle.rope_tables(torch.arange(5, 5 + T, device="cuda"), hd, 10000.0, variant)
+    ref = qkv.clone().float()
+    ref[:, :, :Hq + Hkv] = oracle.rope(qkv[:, :, :Hq + Hkv], cos, sin)
+    got = nat.rope_qk(qkv.clone(), cos.contiguous(), sin.contiguous(), Hq + Hkv, False)
+    assert _rel_err(got, ref) < 4e-3
+    torch.testing.assert_close(got[:, :, Hq + Hkv:], qkv[:, :, Hq + Hkv:])
+    refb = qkv.clone().float()
+    refb[:, :, :Hq + Hkv] = oracle.rope_bwd(qkv[:, :, :Hq + Hkv], cos, sin)
+    gotb = nat.rope_qk(qkv.clone(), cos.contiguous(), sin.contiguous(), Hq + Hkv, True)
+    assert _rel_err(gotb, refb) < 4e-3
+
+
+def test_swiglu(nat):
+    gu = _rand(77, 2 * 384, seed=13)
+    act = nat.swiglu_fwd(gu)
+    g, u = gu.float().chunk(2, -1)
+    assert _rel_err(act, torch.nn.functional.silu(g) * u) < 4e-3
+    dact = _rand(77, 384, seed=14)
+    dgu = nat.swiglu_bwd(dact, gu)
+    sig = torch.sigmoid(g)
+    ref = torch.cat([dact.float() * u * sig * (1 + g * (1 - sig)), dact.float() * g * sig], -1)
+    assert _rel_err(dgu, ref) < 4e-3
+
+
+@pytest.mark.parametrize("V", [50304, 2048])
+def test_ce_inplace(nat, V):
+    rows = 33
+    logits = _rand(rows, V, scale=2.0, seed=15)
+    t = torch.randint(0, V, (rows,), device="cuda")
+    t[3] = -100
+    scale = torch.tensor(0.37, device="cuda")
+    loss = torch.zeros((), device="cuda")
+    work = logits.clone()
+    nat.ce_fwd_bwd_inplace(work, t, scale, loss, -100, True)
+    lf = logits.float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lf, t, ignore_index=-100, reduction="sum")
+    (ref * 0.37).backward()
+    torch.testing.assert_close(loss, ref.detach(), rtol=1e-4, atol=1e-3)
+    assert _rel_err(work, lf.grad) < 6e-3
+    assert (work[3] == 0).all()
+    loss2 = torch.zeros((), device="cuda")
+    keep = logits.clone()
+    nat.ce_fwd_bwd_inplace(keep, t, scale, loss2, -100, False)
+    torch.testing.assert_close(keep, logits)
+    torch.testing.assert_close(loss2, loss)
+
+
+def test_sumsq(nat):
+    for n in (1024, 1 << 20, (1 << 22) + 4):
+        x = torch.randn(n, device="cuda")
+        torch.testing.assert_close(nat.sumsq(x), x.double().pow(2).sum().float(), rtol=1e-5, atol=1e-3)
+
+
+def test_adamw_matches_torch(nat):
+    n = 1 << 16
+    p = torch.randn(n, device="cuda")
+    ref = p.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    scale = torch.tensor(0.5, device="cuda")
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda")
+        ref.grad = g * 0.5
+        opt.step()
+        nat.adamw_step(p, m, v, g, out, scale, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
+    torch.testing.assert_close(p, ref.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(out, p.to(torch.bfloat16))

@@ -1,0 +1,478 @@
+// Bandwidth-bound kernels of the model: embedding gather / scatter-add, fused
+// residual-add + RMSNorm (forward, backward), RoPE on the packed qkv tensor,
+// SwiGLU (forward, backward), in-place softmax-cross-entropy gradient, sum of
+// squares, fused clipped AdamW. All use 16-byte accesses on rows whose length
+// is a multiple of 8 elements; statistics are fp32.
+#include "common.cuh"
+
+namespace tlm {
+
+// ------------------------------------------------------------------ embedding
+__global__ void embedding_fwd_kernel(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__ w,
+                                     float* __restrict__ out, int rows, int D) {
+  const int vec_per_row = D / 8;
+  const long long total = (long long)rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 8;
+    const uint4 v = *reinterpret_cast<const uint4*>(w + idx[r] * (long long)D + c);
+    const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), d = unpack_bf16(v.w);
+    float4* o = reinterpret_cast<float4*>(out + (long long)r * D + c);
+    o[0] = make_float4(a.x, a.y, b.x, b.y);
+    o[1] = make_float4(cc.x, cc.y, d.x, d.y);
+  }
+}
+
+__global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const float* __restrict__ dx,
+                                     float* __restrict__ grad, int rows, int D) {
+  const int vec_per_row = D / 4;
+  const long long total = (long long)rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(dx + (long long)r * D + c);
+    atomicAdd(reinterpret_cast<float4*>(grad + idx[r] * (long long)D + c), v);
+  }
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// One warp per row; the row is staged in the warp's slice of shared memory so
+// global memory is read once. x_new = x + delta; h = x_new * rstd * w.
+__global__ void add_rmsnorm_fwd_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                                       const __nv_bfloat16* __restrict__ w, float* __restrict__ x_new,
+                                       __nv_bfloat16* __restrict__ h, float* __restrict__ rstd_out, int rows, int D,
+                                       float eps) {
+  extern __shared__ float smem_f[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* row_buf = smem_f + (size_t)warp * D;
+  const int nvec = D / 8;
+  for (int r = blockIdx.x * warps + warp; r < rows; r += gridDim.x * warps) {
+    const float* xr = x + (long long)r * D;
+    float ss = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float4 a = *reinterpret_cast<const float4*>(xr + v * 8), b = *reinterpret_cast<const float4*>(xr + v * 8 + 4);
+      if (delta != nullptr) {
+        const uint4 d = *reinterpret_cast<const uint4*>(delta + (long long)r * D + v * 8);
+        const float2 d0 = unpack_bf16(d.x), d1 = unpack_bf16(d.y), d2 = unpack_bf16(d.z), d3 = unpack_bf16(d.w);
+        a.x += d0.x; a.y += d0.y; a.z += d1.x; a.w += d1.y;
+        b.x += d2.x; b.y += d2.y; b.z += d3.x; b.w += d3.y;
+        float4* o = reinterpret_cast<float4*>(x_new + (long long)r * D + v * 8);
+        o[0] = a; o[1] = b;
+      }
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+      *reinterpret_cast<float4*>(row_buf + v * 8) = a;
+      *reinterpret_cast<float4*>(row_buf + v * 8 + 4) = b;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    if (lane == 0) rstd_out[r] = rstd;
+    __syncwarp();
+    for (int v = lane; v < nvec; v += 32) {
+      const float4 a = *reinterpret_cast<const float4*>(row_buf + v * 8), b = *reinterpret_cast<const float4*>(row_buf + v * 8 + 4);
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
+      const float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+      uint4 o;
+      o.x = pack_bf16(a.x * rstd * w0.x, a.y * rstd * w0.y);
+      o.y = pack_bf16(a.z * rstd * w1.x, a.w * rstd * w1.y);
+      o.z = pack_bf16(b.x * rstd * w2.x, b.y * rstd * w2.y);
+      o.w = pack_bf16(b.z * rstd * w3.x, b.w * rstd * w3.y);
+      *reinterpret_cast<uint4*>(h + (long long)r * D + v * 8) = o;
+    }
+    __syncwarp();
+  }
+}
+
+// g_x = g_xnew + rstd * (gh*w - xhat * mean(gh*w*xhat)); g_delta = bf16(g_x);
+// dw[c] += sum_rows gh*xhat. Each warp keeps a private dw row in shared memory;
+// the block folds them and issues one atomicAdd per column.
+__global__ void add_rmsnorm_bwd_kernel(const float* __restrict__ g_xnew, const __nv_bfloat16* __restrict__ g_h,
+                                       const float* __restrict__ x_new, const float* __restrict__ rstd_in,
+                                       const __nv_bfloat16* __restrict__ w, float* __restrict__ g_x,
+                                       __nv_bfloat16* __restrict__ g_delta, float* __restrict__ dw_out, int rows,
+                                       int D) {
+  extern __shared__ float smem_f[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* dw = smem_f + (size_t)warp * 2 * D;        // [D] partial dweight
+  float* buf = dw + D;                               // [D] staged gh*w
+  const int nvec = D / 8;
+  for (int c = lane; c < D; c += 32) dw[c] = 0.f;
+  __syncwarp();
+  for (int r = blockIdx.x * warps + warp; r < rows; r += gridDim.x * warps) {
+    const float rstd = rstd_in[r];
+    const float* xr = x_new + (long long)r * D;
+    float dot = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const float4 a = *reinterpret_cast<const float4*>(xr + v * 8), b = *reinterpret_cast<const float4*>(xr + v * 8 + 4);
+      const uint4 gv = *reinterpret_cast<const uint4*>(g_h + (long long)r * D + v * 8);
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
+      const float xs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      const float2 g0 = unpack_bf16(gv.x), g1 = unpack_bf16(gv.y), g2 = unpack_bf16(gv.z), g3 = unpack_bf16(gv.w);
+      const float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+      const float gs[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+      const float ws[8] = {w0.x, w0.y, w1.x, w1.y, w2.x, w2.y, w3.x, w3.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = xs[j] * rstd;
+        dw[v * 8 + j] += gs[j] * xhat;
+        const float gw = gs[j] * ws[j];
+        buf[v * 8 + j] = gw;
+        dot += gw * xhat;
+      }
+    }
+    dot = warp_sum(dot) / (float)D;
+    __syncwarp();
+    for (int v = lane; v < nvec; v += 32) {
+      const float4 a = *reinterpret_cast<const float4*>(xr + v * 8), b = *reinterpret_cast<const float4*>(xr + v * 8 + 4);
+      const float xs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (buf[v * 8 + j] - xs[j] * rstd * dot);
+      if (g_xnew != nullptr) {
+        const float4 ga = *reinterpret_cast<const float4*>(g_xnew + (long long)r * D + v * 8);
+        const float4 gb = *reinterpret_cast<const float4*>(g_xnew + (long long)r * D + v * 8 + 4);
+        o[0] += ga.x; o[1] += ga.y; o[2] += ga.z; o[3] += ga.w; o[4] += gb.x; o[5] += gb.y; o[6] += gb.z; o[7] += gb.w;
+      }
+      float4* out = reinterpret_cast<float4*>(g_x + (long long)r * D + v * 8);
+      out[0] = make_float4(o[0], o[1], o[2], o[3]);
+      out[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (g_delta != nullptr) {
+        uint4 d;
+        d.x = pack_bf16(o[0], o[1]); d.y = pack_bf16(o[2], o[3]); d.z = pack_bf16(o[4], o[5]); d.w = pack_bf16(o[6], o[7]);
+        *reinterpret_cast<uint4*>(g_delta + (long long)r * D + v * 8) = d;
+      }
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float s = 0.f;
+    for (int wi = 0; wi < warps; ++wi) s += smem_f[(size_t)wi * 2 * D + c];
+    atomicAdd(dw_out + c, s);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (in place)
+// qkv: [rows = B*T, heads_total, hd]; the first n_rot heads are rotated with
+// tables cos/sin [T, hd] (row t = r % T). Pairing is (j, j + hd/2) with an
+// independent table entry per slot, which covers both table layouts.
+// inverse = apply the transposed map (backward).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                            const float* __restrict__ sinT, long long rows, int T, int heads_total, int n_rot, int hd,
+                            int inverse) {
+  const int half = hd / 2, vec_per_head = half / 8;
+  const long long total = rows * n_rot * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    const long long rh = i / vec_per_head;
+    const int head = (int)(rh % n_rot);
+    const long long r = rh / n_rot;
+    const int t = (int)(r % T), j = v * 8;
+    __nv_bfloat16* p = qkv + (r * heads_total + head) * (long long)hd + j;
+    const uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + half);
+    const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+    const float* c = cosT + (long long)t * hd + j;
+    const float* s = sinT + (long long)t * hd + j;
+    uint32_t ol[4], oh[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16(lw[k]), b = unpack_bf16(hw[k]);
+      const float cl0 = c[2 * k], cl1 = c[2 * k + 1], ch0 = c[half + 2 * k], ch1 = c[half + 2 * k + 1];
+      const float sl0 = s[2 * k], sl1 = s[2 * k + 1], sh0 = s[half + 2 * k], sh1 = s[half + 2 * k + 1];
+      float y0, y1, z0, z1;
+      if (!inverse) {          // y[j] = x[j] c[j] - x[j+h] s[j];  y[j+h] = x[j+h] c[j+h] + x[j] s[j+h]
+        y0 = a.x * cl0 - b.x * sl0; y1 = a.y * cl1 - b.y * sl1;
+        z0 = b.x * ch0 + a.x * sh0; z1 = b.y * ch1 + a.y * sh1;
+      } else {                 // dx[j] = dy[j] c[j] + dy[j+h] s[j+h];  dx[j+h] = dy[j+h] c[j+h] - dy[j] s[j]
+        y0 = a.x * cl0 + b.x * sh0; y1 = a.y * cl1 + b.y * sh1;
+        z0 = b.x * ch0 - a.x * sl0; z1 = b.y * ch1 - a.y * sl1;
+      }
+      ol[k] = pack_bf16(y0, y1); oh[k] = pack_bf16(z0, z1);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+    *reinterpret_cast<uint4*>(p + half) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long rows,
+                                  int I) {
+  const int vec = I / 8;
+  const long long total = rows * vec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec; const int c = (int)(i % vec) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * 2 * I + c), u = *reinterpret_cast<const uint4*>(gu + r * 2 * I + I + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16(gw[k]), b = unpack_bf16(uw[k]);
+      o[k] = pack_bf16(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    *reinterpret_cast<uint4*>(act + r * I + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, long long rows, int I) {
+  const int vec = I / 8;
+  const long long total = rows * vec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec; const int c = (int)(i % vec) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * 2 * I + c), u = *reinterpret_cast<const uint4*>(gu + r * 2 * I + I + c);
+    const uint4 d = *reinterpret_cast<const uint4*>(dact + r * I + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w}, dw[4] = {d.x, d.y, d.z, d.w};
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16(gw[k]), b = unpack_bf16(uw[k]), dd = unpack_bf16(dw[k]);
+      const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
+      og[k] = pack_bf16(dd.x * b.x * s0 * (1.f + a.x * (1.f - s0)), dd.y * b.y * s1 * (1.f + a.y * (1.f - s1)));
+      ou[k] = pack_bf16(dd.x * a.x * s0, dd.y * a.y * s1);
+    }
+    *reinterpret_cast<uint4*>(dgu + r * 2 * I + c) = make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(dgu + r * 2 * I + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy, gradient written in place
+// One block per row of bf16 logits [rows, V] (row pitch ld). Pass 1: online
+// max / sum-exp. Pass 2 (if write_grad): logits <- scale * (softmax - onehot).
+// loss_sum += lse - logit[target]. Rows whose target == ignore_index
+// contribute nothing and get a zero gradient.
+__global__ void ce_inplace_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                                  const float* __restrict__ scale_ptr, float* __restrict__ loss_sum, int V,
+                                  long long ld, long long ignore_index, int write_grad) {
+  __shared__ float red_m[32], red_s[32];
+  __shared__ float row_m, row_l;
+  const int r = blockIdx.x;
+  __nv_bfloat16* row = logits + (long long)r * ld;
+  const long long tgt = targets[r];
+  const int nvec = V / 8, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (tgt == ignore_index) {
+    if (write_grad) for (int v = threadIdx.x; v < nvec; v += blockDim.x) *reinterpret_cast<uint4*>(row + v * 8) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  float m = -INFINITY, s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 a = unpack_bf16(w[k]); f[2 * k] = a.x; f[2 * k + 1] = a.y; }
+    float lm = f[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) lm = fmaxf(lm, f[k]);
+    const float nm = fmaxf(m, lm);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += __expf(f[k] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  const float wm = warp_max(m);
+  s = warp_sum(s * __expf(m - wm));
+  if (lane == 0) { red_m[warp] = wm; red_s[warp] = s; }
+  __syncthreads();
+  if (warp == 0) {
+    float mm = lane < nwarps ? red_m[lane] : -INFINITY, ss = lane < nwarps ? red_s[lane] : 0.f;
+    const float gm = warp_max(mm);
+    ss = warp_sum(ss * __expf(mm - gm));
+    if (lane == 0) {
+      row_m = gm; row_l = ss;
+      atomicAdd(loss_sum, gm + __logf(ss) - __bfloat162float(row[tgt]));
+    }
+  }
+  __syncthreads();
+  if (!write_grad) return;
+  const float gm = row_m, inv = 1.f / row_l, scale = *scale_ptr;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 q = *reinterpret_cast<const uint4*>(row + v * 8);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 a = unpack_bf16(w[k]); f[2 * k] = a.x; f[2 * k + 1] = a.y; }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float p = __expf(f[k] - gm) * inv;
+      if ((long long)(v * 8 + k) == tgt) p -= 1.f;
+      f[k] = p * scale;
+    }
+    *reinterpret_cast<uint4*>(row + v * 8) =
+        make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+  }
+}
+
+// ------------------------------------------------------------------ sum of squares (two stages, deterministic)
+constexpr int SUMSQ_BLOCKS = 1024, SUMSQ_THREADS = 256;
+
+__global__ void sumsq_partial_kernel(const float* __restrict__ x, long long n, float* __restrict__ partials) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long long nvec = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nvec * 4)) { const float t = x[nvec * 4 + threadIdx.x]; acc += t * t; }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) partials[blockIdx.x] = v;
+  }
+}
+
+__global__ void sumsq_final_kernel(const float* __restrict__ partials, int n, float* __restrict__ out) {
+  __shared__ double red[32];
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)partials[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+    out[0] = (float)t;
+  }
+}
+
+// ------------------------------------------------------------------ fused AdamW
+// p (fp32 master), m, v updated in place from g * (*scale_ptr); the new value
+// is also written as bf16 to `p_out`. Decoupled weight decay, bias-corrected,
+// same update order as torch.optim.AdamW.
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ g, __nv_bfloat16* __restrict__ p_out,
+                             const float* __restrict__ scale_ptr, long long n, float lr, float beta1, float beta2,
+                             float eps, float wd, float inv_bc1, float inv_sqrt_bc2) {
+  const float scale = *scale_ptr;
+  const long long nvec = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i], mm = reinterpret_cast<float4*>(m)[i], vv = reinterpret_cast<float4*>(v)[i];
+    const float4 gg = reinterpret_cast<const float4*>(g)[i];
+    float* pa = &pp.x; float* ma = &mm.x; float* va = &vv.x; const float* ga = &gg.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gr = ga[k] * scale;
+      float x = pa[k] * (1.f - lr * wd);
+      ma[k] = beta1 * ma[k] + (1.f - beta1) * gr;
+      va[k] = beta2 * va[k] + (1.f - beta2) * gr * gr;
+      const float denom = sqrtf(va[k]) * inv_sqrt_bc2 + eps;
+      x -= lr * inv_bc1 * ma[k] / denom;
+      pa[k] = x;
+    }
+    reinterpret_cast<float4*>(p)[i] = pp; reinterpret_cast<float4*>(m)[i] = mm; reinterpret_cast<float4*>(v)[i] = vv;
+    reinterpret_cast<uint2*>(p_out)[i] = make_uint2(pack_bf16(pp.x, pp.y), pack_bf16(pp.z, pp.w));
+  }
+}
+
+static inline int grid_for(long long work_items, int threads, int max_blocks_per_sm = 8) {
+  long long b = (work_items + threads - 1) / threads;
+  long long cap = (long long)num_sms() * max_blocks_per_sm;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace tlm
+
+using namespace tlm;
+
+TLM_API int tlm_embedding_fwd(const long long* idx, const void* w, float* out, int rows, int D, cudaStream_t st) {
+  embedding_fwd_kernel<<<grid_for((long long)rows * D / 8, 256), 256, 0, st>>>(idx, (const __nv_bfloat16*)w, out, rows, D);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_embedding_bwd(const long long* idx, const float* dx, float* grad, int rows, int D, cudaStream_t st) {
+  embedding_bwd_kernel<<<grid_for((long long)rows * D / 4, 256), 256, 0, st>>>(idx, dx, grad, rows, D);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_add_rmsnorm_fwd(const float* x, const void* delta, const void* w, float* x_new, void* h, float* rstd,
+                                int rows, int D, float eps, cudaStream_t st) {
+  int warps = 8;
+  while (warps > 1 && (size_t)warps * D * 4 > 200 * 1024) warps >>= 1;
+  size_t smem = (size_t)warps * D * 4;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  int grid = grid_for((rows + warps - 1) / warps, 1, 8);
+  add_rmsnorm_fwd_kernel<<<grid, warps * 32, smem, st>>>(x, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w, x_new,
+                                                         (__nv_bfloat16*)h, rstd, rows, D, eps);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_add_rmsnorm_bwd(const float* g_xnew, const void* g_h, const float* x_new, const float* rstd,
+                                const void* w, float* g_x, void* g_delta, float* dw, int rows, int D,
+                                cudaStream_t st) {
+  int warps = 8;
+  while (warps > 1 && (size_t)warps * 2 * D * 4 > 200 * 1024) warps >>= 1;
+  size_t smem = (size_t)warps * 2 * D * 4;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  int grid = grid_for((rows + warps - 1) / warps, 1, 2);
+  add_rmsnorm_bwd_kernel<<<grid, warps * 32, smem, st>>>(g_xnew, (const __nv_bfloat16*)g_h, x_new, rstd,
+                                                         (const __nv_bfloat16*)w, g_x, (__nv_bfloat16*)g_delta, dw, rows, D);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_rope(void* qkv, const float* cosT, const float* sinT, long long rows, int T, int heads_total, int n_rot,
+                     int hd, int inverse, cudaStream_t st) {
+  if (hd % 16 != 0) return -3;
+  long long items = rows * n_rot * (hd / 16);
+  rope_kernel<<<grid_for(items, 256), 256, 0, st>>>((__nv_bfloat16*)qkv, cosT, sinT, rows, T, heads_total, n_rot, hd, inverse);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_swiglu_fwd(const void* gu, void* act, long long rows, int I, cudaStream_t st) {
+  swiglu_fwd_kernel<<<grid_for(rows * I / 8, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, rows, I);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long rows, int I, cudaStream_t st) {
+  swiglu_bwd_kernel<<<grid_for(rows * I / 8, 256), 256, 0, st>>>((const __nv_bfloat16*)dact, (const __nv_bfloat16*)gu,
+                                                                 (__nv_bfloat16*)dgu, rows, I);
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_ce_inplace(void* logits, const long long* targets, const float* scale, float* loss_sum, int rows, int V,
+                           long long ld, long long ignore_index, int write_grad, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  ce_inplace_kernel<<<rows, 512, 0, st>>>((__nv_bfloat16*)logits, targets, scale, loss_sum, V, ld, ignore_index, write_grad);
+  count_launch();
+  return launch_status();
+}
+
+// scratch: at least tlm_sumsq_scratch_floats() floats of device memory.
+TLM_API int tlm_sumsq_scratch_floats() { return SUMSQ_BLOCKS; }
+
+TLM_API int tlm_sumsq(const float* x, long long n, float* scratch, float* out, cudaStream_t st) {
+  int blocks = grid_for(n / 4 + 1, SUMSQ_THREADS, 4);
+  if (blocks > SUMSQ_BLOCKS) blocks = SUMSQ_BLOCKS;
+  sumsq_partial_kernel<<<blocks, SUMSQ_THREADS, 0, st>>>(x, n, scratch);
+  sumsq_final_kernel<<<1, 256, 0, st>>>(scratch, blocks, out);
+  count_launch(2);
+  return launch_status();
+}
+
+TLM_API int tlm_adamw(float* p, float* m, float* v, const float* g, void* p_out, const float* scale, long long n,
+                      float lr, float beta1, float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2,
+                      cudaStream_t st) {
+  if (n % 4 != 0) return -3;
+  adamw_kernel<<<grid_for(n / 4, 256), 256, 0, st>>>(p, m, v, g, (__nv_bfloat16*)p_out, scale, n, lr, beta1, beta2, eps, wd,
+                                                     inv_bc1, inv_sqrt_bc2);
+  count_launch();
+  return launch_status();
+}

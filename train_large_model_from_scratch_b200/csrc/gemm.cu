@@ -1,0 +1,386 @@
+// Persistent, warp-specialised bf16 GEMM on the 5th-generation tensor cores.
+//
+//   C[M,N] (=|+=) A[M,K] * B[N,K]^T      fp32 accumulation in tensor memory
+//
+// One CTA per SM walks over 128x256 output tiles. Roles inside the CTA:
+//   warp 0      : TMA producer - fills a 4-deep ring of (A 128x64, B 256x64) bf16
+//                 stages in 128B-swizzled shared memory
+//   warp 1      : allocates 512 TMEM columns (two 128x256 fp32 accumulators) and,
+//                 through one elected lane, issues tcgen05.mma (M128 N256 K16)
+//   warps 2..5  : epilogue - tcgen05.ld the finished accumulator (each warp owns
+//                 the 32 TMEM lanes its rank allows), convert, store to global
+// The two accumulators let the MMA warp start tile i+1 while the epilogue
+// drains tile i.
+//
+// Either operand may be "K-major" (reduction index contiguous in memory:
+// A stored [M,K], B stored [N,K]) or "MN-major" (output index contiguous:
+// A stored [K,M], B stored [K,N]). The major-ness only changes the TMA boxes
+// and two descriptor fields, so forward (x W^T), dgrad (dy W) and wgrad
+// (dy^T x, accumulated into the fp32 gradient buffer) all run on this kernel
+// without transposed copies.
+//
+// Every mbarrier wait is bounded; on a timeout the CTA records a status code,
+// every role leaves its loop, and the CTA still frees its tensor memory.
+#include "common.cuh"
+
+namespace tlm {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
+constexpr int B_BYTES = BN * BK * 2;                 // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BOX_MN_BYTES = 64 * BK * 2;            // one 64(mn) x 64(k) MN-major box = 8 KB
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;            // elements
+  unsigned int* status;
+  // grouped mode (MoE): problem g covers rows [row_start[g], row_start[g+1]) of a
+  // row-grouped operand; see grouped launchers. groups == 0 -> plain GEMM.
+  int groups;
+  const int* row_start;     // device, groups + 1 entries
+  int group_mode;           // 1: rows of A/C grouped, B per group (3-D map); 2: K grouped (wgrad), C per group
+  long long c_group_stride; // elements between per-group C matrices (mode 2)
+  int max_tiles_m;          // upper bound of m-tiles per group (mode 1)
+};
+
+struct TileCoord {
+  int m0, n0;       // output tile origin (row within C / column)
+  int a_row0;       // row coordinate for the A operand
+  int b_grp;        // third coordinate of the B map (grouped) or 0
+  int k_lo, k_hi;   // reduction range
+  int m_end;        // exclusive row bound for stores
+  long long c_off;  // element offset added to C
+  bool valid;
+};
+
+__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile, int tiles_m, int tiles_n) {
+  // bands of 16 row-tiles, column-tiles fastest inside a band -> the CTAs that
+  // run together share a handful of A and B tiles in L2
+  constexpr int GROUP_M = 16;
+  int band = tile / (GROUP_M * tiles_n);
+  int first_m = band * GROUP_M;
+  int gm = min(GROUP_M, tiles_m - first_m);
+  int r = tile - band * GROUP_M * tiles_n;
+  int tm = first_m + r % gm, tn = r / gm;
+  TileCoord t;
+  t.m0 = tm * BM; t.n0 = tn * BN; t.a_row0 = t.m0; t.b_grp = 0;
+  t.k_lo = 0; t.k_hi = p.K; t.m_end = p.M; t.c_off = 0; t.valid = true;
+  return t;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  // barrier slots: full[0..S), empty[S..2S), acc_full[2S..2S+2), acc_empty[2S+2..2S+4)
+  const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto accf_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto acce_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_n = (p.N + BN - 1) / BN;
+  int tiles_m, total_tiles;
+  if (p.groups == 0) { tiles_m = (p.M + BM - 1) / BM; total_tiles = tiles_m * tiles_n; }
+  else if (p.group_mode == 1) { tiles_m = p.max_tiles_m; total_tiles = p.groups * tiles_m * tiles_n; }
+  else { tiles_m = (p.M + BM - 1) / BM; total_tiles = p.groups * tiles_m * tiles_n; }
+
+  auto get_tile = [&](int tile) -> TileCoord {
+    if (p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n);
+    TileCoord t;
+    int per = tiles_m * tiles_n;
+    int g = tile / per, r = tile - g * per;
+    int tm = r % tiles_m, tn = r / tiles_m;
+    int lo = p.row_start[g], hi = p.row_start[g + 1];
+    if (p.group_mode == 1) {            // rows grouped: A rows [lo,hi), B = weight[g]
+      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = g;
+      t.k_lo = 0; t.k_hi = p.K; t.m_end = hi; t.c_off = 0; t.valid = t.m0 < hi;
+    } else {                            // reduction grouped: K range [lo,hi), C = C_base + g * stride
+      t.m0 = tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = 0;
+      t.k_lo = lo; t.k_hi = hi; t.m_end = p.M; t.c_off = (long long)g * p.c_group_stride; t.valid = hi > lo;
+    }
+    return t;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileCoord t = get_tile(tile);
+        if (!t.valid) continue;
+        for (int k0 = t.k_lo; k0 < t.k_hi; k0 += BK) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, abort_flag, p.status)) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * BOX_MN_BYTES, &tmA, full_bar(stage), t.a_row0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sa, &tmA, full_bar(stage), k0, t.a_row0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * BOX_MN_BYTES, &tmB, full_bar(stage), t.n0 + 64 * j, k0, t.b_grp);
+          } else {
+            tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, t.b_grp);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileCoord t = get_tile(tile);
+        if (!t.valid) continue;
+        if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, 2, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
+        for (int k0 = t.k_lo; k0 < t.k_hi; k0 += BK) {
+          if (!mbar_wait(full_bar(stage), phase, 3, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // K-major: 16 bf16 = 32 B further along the 128 B row;
+            // MN-major: 16 k-rows = two 8-row groups = 2048 B further.
+            const uint64_t ad = A_MN ? umma_smem_desc(sa + kk * 2048, BOX_MN_BYTES, 1024)
+                                     : umma_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t bd = B_MN ? umma_smem_desc(sb + kk * 2048, BOX_MN_BYTES, 1024)
+                                     : umma_smem_desc(sb + kk * 32, 16, 1024);
+            umma_bf16(tmem_d, ad, bd, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(empty_bar(stage));          // stage reusable once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(accf_bar(acc));               // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                        // TMEM lane quarter this warp may read
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      TileCoord t = get_tile(tile);
+      if (!t.valid) continue;
+      if (!mbar_wait(accf_bar(acc), acc_phase, 4, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const int row = t.m0 + q * 32 + lane;
+      const bool row_ok = row < t.m_end;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = t.n0 + c;
+        if (row_ok && col < p.N) {
+          if (EPI == EPI_BF16) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                v.y = pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                v.z = pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                v.w = pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(p.C) + t.c_off + (long long)row * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                       __uint_as_float(r[j + 3]));
+                if (EPI == EPI_F32_ACC) {
+                  const float4 o = *reinterpret_cast<const float4*>(out + j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(out + j) = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+// Operand description: `ptr` points at element (0,0); K-major operands are
+// [rows, K] with leading dimension `ld`; MN-major operands are [K, rows] with
+// leading dimension `ld`. `groups`/`group_stride` add an outer dimension (B only).
+struct Operand {
+  const void* ptr;
+  long long rows, k, ld;
+  bool mn_major;
+  long long groups, group_stride;
+};
+
+static int build_map(CUtensorMap* map, const Operand& o, int box_rows) {
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  if (o.mn_major) {            // memory [k][rows]: inner = rows
+    dims[0] = (uint64_t)o.rows; dims[1] = (uint64_t)o.k;
+    box[0] = 64; box[1] = BK;
+  } else {                     // memory [rows][k]: inner = k
+    dims[0] = (uint64_t)o.k; dims[1] = (uint64_t)o.rows;
+    box[0] = BK; box[1] = (uint32_t)box_rows;
+  }
+  strides[0] = (uint64_t)o.ld * 2;
+  int rank = 2;
+  if (o.groups > 0) {
+    dims[2] = (uint64_t)o.groups; strides[1] = (uint64_t)o.group_stride * 2; box[2] = 1; rank = 3;
+  }
+  return make_tmap_bf16(map, o.ptr, rank, dims, strides, box);
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
+  count_launch();
+  return launch_status();
+}
+
+static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                    int tiles, cudaStream_t st) {
+#define TLM_CASE(A, B, E) if (a_mn == A && b_mn == B && epi == E) return launch_t<A, B, E>(ma, mb, p, tiles, st);
+  TLM_CASE(false, false, EPI_BF16) TLM_CASE(false, true, EPI_BF16) TLM_CASE(true, true, EPI_F32_ACC)
+  TLM_CASE(false, false, EPI_F32) TLM_CASE(true, true, EPI_F32) TLM_CASE(false, false, EPI_F32_ACC)
+  TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32)
+#undef TLM_CASE
+  return -2;
+}
+
+}  // namespace tlm
+
+using namespace tlm;
+
+// C[M,N] = A * B^T with arbitrary operand majors.
+//   a_mn = 0: A is [M,K] (lda); a_mn = 1: A is [K,M] (lda)
+//   b_mn = 0: B is [N,K] (ldb); b_mn = 1: B is [K,N] (ldb)
+//   epi: 0 bf16 store, 1 fp32 accumulate (C += ...), 2 fp32 store
+TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int a_mn, int b_mn, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  Operand oa{A, M, K, lda, a_mn != 0, 0, 0}, ob{B, N, K, ldb, b_mn != 0, 1, (long long)N * K};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
+  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return dispatch(a_mn != 0, b_mn != 0, epi, ma, mb, p, tiles, stream);
+}
+
+// Grouped forward / dgrad: rows of A and C are grouped (`row_start`, device,
+// groups+1 ints, ascending, row_start[groups] == M); group g multiplies by
+// B[g] ([N,K] K-major or [K,N] MN-major, `b_group_stride` elements apart).
+// `max_rows_per_group` bounds the per-group tile count (a host-known bound,
+// e.g. M); tiles beyond a group's real row count exit immediately.
+TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const int* row_start, int groups, int M,
+                                  int N, int K, long long lda, long long ldb, long long b_group_stride,
+                                  long long ldc, int b_mn, int epi, int max_rows_per_group, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  Operand oa{A, M, K, lda, false, 0, 0}, ob{B, N, K, ldb, b_mn != 0, groups, b_group_stride};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
+  p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
+  return dispatch(false, b_mn != 0, epi, ma, mb, p, tiles, stream);
+}
+
+// Grouped wgrad: C[g] ([M,N] fp32, `c_group_stride` apart) += A[rows_g, M]^T * B[rows_g, N]
+// where rows_g = [row_start[g], row_start[g+1]) is the reduction range.
+// A is stored [R, M] and B [R, N] (both MN-major with respect to the product).
+TLM_API int tlm_gemm_grouped_k(const void* A, const void* B, void* C, const int* row_start, int groups, int R,
+                               int M, int N, long long lda, long long ldb, long long ldc, long long c_group_stride,
+                               int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || R <= 0 || groups <= 0) return 0;
+  Operand oa{A, M, R, lda, true, 0, 0}, ob{B, N, R, ldb, true, 1, (long long)R * N};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = R; p.C = C; p.ldc = ldc; p.status = status_word();
+  p.groups = groups; p.row_start = row_start; p.group_mode = 2; p.c_group_stride = c_group_stride;
+  int tiles = groups * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return dispatch(true, true, epi, ma, mb, p, tiles, stream);
+}

@@ -1,0 +1,86 @@
+// Library-wide state: launch counter, device status word, tensor-map encoder.
+#include "common.cuh"
+
+#include <stdio.h>
+
+namespace tlm {
+
+unsigned long long g_launches = 0;
+
+static unsigned int* g_status_host = nullptr;
+static unsigned int* g_status_dev = nullptr;
+
+unsigned int* status_word() {
+  if (g_status_dev == nullptr) {
+    if (cudaHostAlloc((void**)&g_status_host, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return nullptr;
+    *g_status_host = 0;
+    if (cudaHostGetDevicePointer((void**)&g_status_dev, g_status_host, 0) != cudaSuccess) return nullptr;
+  }
+  return g_status_dev;
+}
+
+unsigned int read_status(bool clear) {
+  if (g_status_host == nullptr) return 0;
+  unsigned int v = *(volatile unsigned int*)g_status_host;
+  if (clear && v != 0) *(volatile unsigned int*)g_status_host = 0;
+  return v;
+}
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) return nullptr;
+    fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                   const uint32_t* box) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return -1;
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bdim[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "tlm: cuTensorMapEncodeTiled failed (%d): rank %d base %p dims", (int)r, rank, base);
+    for (int i = 0; i < rank; ++i) fprintf(stderr, " %llu", (unsigned long long)dims[i]);
+    fprintf(stderr, " box");
+    for (int i = 0; i < rank; ++i) fprintf(stderr, " %u", box[i]);
+    fprintf(stderr, "\n");
+    return (int)r;
+  }
+  return 0;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+}  // namespace tlm
+
+TLM_API unsigned long long tlm_launch_count() { return tlm::g_launches; }
+TLM_API void tlm_reset_launch_count() { tlm::g_launches = 0; }
+
+// Reads (and clears) the status word; 0 = no kernel gave up on a wait. Does not
+// synchronise: call after the work of interest has completed.
+TLM_API unsigned int tlm_take_device_status() { return tlm::read_status(true); }
+
+TLM_API int tlm_num_sms() { return tlm::num_sms(); }

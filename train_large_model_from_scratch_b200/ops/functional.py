@@ -142,6 +142,7 @@ class _RopeQK(torch.autograd.Function):
         ctx.save_for_backward(cos, sin)
         ctx.n = n_rot_heads
         if _use_native(qkv):
+            ctx.mark_dirty(qkv)
             return native.rope_qk(qkv, cos, sin, n_rot_heads, False)
         out = qkv.clone()
         out[:, :, :n_rot_heads] = oracle.rope(qkv[:, :, :n_rot_heads], cos, sin).to(qkv.dtype)
@@ -187,17 +188,20 @@ class _Attention(torch.autograd.Function):
         ctx.n_q, ctx.n_kv, ctx.causal = n_q, n_kv, causal
         if _use_native(qkv):
             o, lse = native.flash_attn_fwd(qkv, n_q, n_kv, causal)
-            ctx.save_for_backward(qkv, o, lse)
+            ctx.save_for_backward(qkv, o)
+            ctx.lse = lse
             return o
         q, k, v = qkv[:, :, :n_q], qkv[:, :, n_q:n_q + n_kv], qkv[:, :, n_q + n_kv:]
         o, lse, *_ = _attn_fwd_ref(q, k, v, causal)
         o = o.to(qkv.dtype).contiguous()
-        ctx.save_for_backward(qkv, o, lse)
+        ctx.save_for_backward(qkv, o)
+        ctx.lse = lse
         return o
 
     @staticmethod
     def backward(ctx, do):
-        qkv, o, lse = ctx.saved_tensors
+        qkv, o = ctx.saved_tensors
+        lse = ctx.lse
         n_q, n_kv = ctx.n_q, ctx.n_kv
         if _use_native(qkv):
             return native.flash_attn_bwd(do.contiguous(), qkv, o, lse, n_q, n_kv, ctx.causal), None, None, None

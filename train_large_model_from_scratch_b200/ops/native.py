@@ -38,3 +38,228 @@ def lib():
         _LIB = ctypes.CDLL(_LIB_PATH)
         _declare(_LIB)
     return _LIB
+
+
+_c = ctypes
+_P, _I, _LL, _F = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float
+
+_SIGS = {
+    "tlm_launch_count": (_c.c_ulonglong, []),
+    "tlm_reset_launch_count": (None, []),
+    "tlm_take_device_status": (_c.c_uint, []),
+    "tlm_num_sms": (_I, []),
+    "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
+    "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
+    "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
+    "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _P]),
+    "tlm_embedding_bwd": (_I, [_P, _P, _P, _I, _I, _P]),
+    "tlm_add_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
+    "tlm_add_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
+    "tlm_rope": (_I, [_P, _P, _P, _LL, _I, _I, _I, _I, _I, _P]),
+    "tlm_swiglu_fwd": (_I, [_P, _P, _LL, _I, _P]),
+    "tlm_swiglu_bwd": (_I, [_P, _P, _P, _LL, _I, _P]),
+    "tlm_ce_inplace": (_I, [_P, _P, _P, _P, _I, _I, _LL, _LL, _I, _P]),
+    "tlm_sumsq_scratch_floats": (_I, []),
+    "tlm_sumsq": (_I, [_P, _LL, _P, _P, _P]),
+    "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P]),
+}
+
+
+def _declare(l) -> None:
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(l, name, None)
+        if fn is None:
+            continue
+        fn.restype, fn.argtypes = res, args
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeError(f"{what} failed with code {code}"
+                          + (f" ({torch.cuda.get_device_name()})" if torch.cuda.is_available() else ""))
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def launch_count() -> int:
+    return int(lib().tlm_launch_count())
+
+
+def reset_launch_count() -> None:
+    lib().tlm_reset_launch_count()
+
+
+def take_device_status() -> int:
+    """Nonzero when a kernel gave up on a bounded wait since the last call
+    (`site << 8 | detail`). Call after synchronising."""
+    return int(lib().tlm_take_device_status())
+
+
+def raise_on_device_status() -> None:
+    torch.cuda.synchronize()
+    st = take_device_status()
+    if st:
+        raise NativeError(f"a kernel timed out waiting at site {st >> 8} (detail {st & 0xff})")
+
+
+# --------------------------------------------------------------------------- GEMM
+EPI_BF16, EPI_F32_ACC, EPI_F32 = 0, 1, 2
+
+
+def _rows(t: torch.Tensor) -> tuple[int, int, int]:
+    assert t.dim() == 2 and t.stride(1) == 1, "2-D tensor with contiguous rows expected"
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ w[N,K]^T (bf16)."""
+    M, K, lda = _rows(x)
+    N, K2, ldb = _rows(w)
+    assert K == K2
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    _check(lib().tlm_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, out.stride(0),
+                          0, 0, EPI_BF16, _stream()), "gemm_nt")
+    return out
+
+
+def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M,K] = dy[M,N] @ w[N,K] (bf16): the data-gradient GEMM. `w` is read in
+    place as an MN-major operand, no transpose is materialised."""
+    M, N, lda = _rows(dy)
+    N2, K, ldb = _rows(w)
+    assert N == N2
+    if out is None:
+        out = torch.empty(M, K, dtype=torch.bfloat16, device=dy.device)
+    _check(lib().tlm_gemm(dy.data_ptr(), w.data_ptr(), out.data_ptr(), M, K, N, lda, ldb, out.stride(0),
+                          0, 1, EPI_BF16, _stream()), "gemm_nn")
+    return out
+
+
+def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor) -> None:
+    """acc[N,K] (fp32) += dy[M,N]^T @ x[M,K]: the weight-gradient GEMM, both
+    operands MN-major, accumulated into the fp32 gradient buffer."""
+    M, N, lda = _rows(dy)
+    M2, K, ldb = _rows(x)
+    assert M == M2 and acc.dtype == torch.float32 and acc.shape == (N, K)
+    _check(lib().tlm_gemm(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), N, K, M, lda, ldb, acc.stride(0),
+                          1, 1, EPI_F32_ACC, _stream()), "gemm_tn_accum")
+
+
+def gemm_raw(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi) -> None:
+    _check(lib().tlm_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, lda, ldb, ldc, a_mn, b_mn, epi,
+                          _stream()), "gemm")
+
+
+# --------------------------------------------------------------------------- elementwise
+def embedding_fwd(idx: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    idx = idx.reshape(-1).contiguous()
+    rows, D = idx.numel(), weight.shape[1]
+    out = torch.empty(rows, D, dtype=torch.float32, device=weight.device)
+    _check(lib().tlm_embedding_fwd(idx.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, D, _stream()), "embedding_fwd")
+    return out
+
+
+def embedding_bwd(idx: torch.Tensor, dx: torch.Tensor, main_grad: torch.Tensor) -> None:
+    idx = idx.reshape(-1).contiguous()
+    rows, D = dx.shape
+    _check(lib().tlm_embedding_bwd(idx.data_ptr(), dx.data_ptr(), main_grad.data_ptr(), rows, D, _stream()), "embedding_bwd")
+
+
+def add_rmsnorm_fwd(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, eps: float):
+    rows, D = x.shape
+    x = x.contiguous()
+    x_new = torch.empty_like(x) if delta is not None else x
+    h = torch.empty(rows, D, dtype=torch.bfloat16, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    if delta is not None:
+        delta = delta.contiguous()
+    _check(lib().tlm_add_rmsnorm_fwd(x.data_ptr(), _ptr(delta), w.data_ptr(), x_new.data_ptr(), h.data_ptr(),
+                                     rstd.data_ptr(), rows, D, eps, _stream()), "add_rmsnorm_fwd")
+    return x_new, h, rstd
+
+
+def add_rmsnorm_bwd(g_xnew, g_h, x_new, rstd, w, main_grad, has_delta: bool):
+    rows, D = x_new.shape
+    if g_h is None:
+        g_h = torch.zeros(rows, D, dtype=torch.bfloat16, device=x_new.device)
+    g_h = g_h.contiguous()
+    if g_xnew is not None:
+        g_xnew = g_xnew.contiguous()
+    g_x = torch.empty(rows, D, dtype=torch.float32, device=x_new.device)
+    g_delta = torch.empty(rows, D, dtype=torch.bfloat16, device=x_new.device) if has_delta else None
+    _check(lib().tlm_add_rmsnorm_bwd(_ptr(g_xnew), g_h.data_ptr(), x_new.data_ptr(), rstd.data_ptr(), w.data_ptr(),
+                                     g_x.data_ptr(), _ptr(g_delta), main_grad.data_ptr(), rows, D, _stream()),
+           "add_rmsnorm_bwd")
+    return g_x, g_delta
+
+
+def rope_qk(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_rot: int, inverse: bool) -> torch.Tensor:
+    """In place on a contiguous `[B, T, H, hd]` bf16 tensor."""
+    assert qkv.is_contiguous()
+    B, T, H, hd = qkv.shape
+    _check(lib().tlm_rope(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), B * T, T, H, n_rot, hd, int(inverse),
+                          _stream()), "rope")
+    return qkv
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    gu = gu.contiguous()
+    rows, two_i = gu.shape
+    act = torch.empty(rows, two_i // 2, dtype=torch.bfloat16, device=gu.device)
+    _check(lib().tlm_swiglu_fwd(gu.data_ptr(), act.data_ptr(), rows, two_i // 2, _stream()), "swiglu_fwd")
+    return act
+
+
+def swiglu_bwd(dact: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    rows, two_i = gu.shape
+    dgu = torch.empty_like(gu)
+    _check(lib().tlm_swiglu_bwd(dact.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, two_i // 2, _stream()), "swiglu_bwd")
+    return dgu
+
+
+def ce_fwd_bwd_inplace(logits, targets, grad_scale, loss_sum, ignore_index: int, write_grad: bool) -> None:
+    rows, V = logits.shape
+    if not torch.is_tensor(grad_scale):
+        grad_scale = torch.tensor(float(grad_scale), dtype=torch.float32, device=logits.device)
+    _check(lib().tlm_ce_inplace(logits.data_ptr(), targets.data_ptr(), grad_scale.data_ptr(), loss_sum.data_ptr(),
+                                rows, V, logits.stride(0), ignore_index, int(write_grad), _stream()), "ce_inplace")
+
+
+_SUMSQ_SCRATCH: dict = {}
+
+
+def sumsq(x: torch.Tensor) -> torch.Tensor:
+    x = x.contiguous()
+    dev = x.device
+    if dev not in _SUMSQ_SCRATCH:
+        _SUMSQ_SCRATCH[dev] = torch.empty(lib().tlm_sumsq_scratch_floats(), dtype=torch.float32, device=dev)
+    out = torch.empty((), dtype=torch.float32, device=dev)
+    _check(lib().tlm_sumsq(x.data_ptr(), x.numel(), _SUMSQ_SCRATCH[dev].data_ptr(), out.data_ptr(), _stream()), "sumsq")
+    return out
+
+
+def adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, scale, step: int, lr, beta1, beta2, eps, wd) -> None:
+    import math
+    inv_bc1 = 1.0 / (1.0 - beta1 ** step)
+    inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - beta2 ** step)
+    _check(lib().tlm_adamw(master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(),
+                           param_out.data_ptr(), scale.data_ptr(), master.numel(), lr, beta1, beta2, eps, wd,
+                           inv_bc1, inv_sqrt_bc2, _stream()), "adamw")
+
+
+# --------------------------------------------------------------------------- attention
+def flash_attn_fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
+    from . import attention_cuda
+    return attention_cuda.fwd(qkv, n_q, n_kv, causal)
+
+
+def flash_attn_bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
+    from . import attention_cuda
+    return attention_cuda.bwd(do, qkv, o, lse, n_q, n_kv, causal)

@@ -245,6 +245,8 @@ class Trainer:
 
     def _to_device(self, x: torch.Tensor) -> torch.Tensor:
         x = self._sp_slice(x)
+        if x.device == self.device:
+            return x.contiguous()
         if not self.use_cuda:
             return x.contiguous()
         if x.is_pinned() and self.sp_world_size == 1:
@@ -275,12 +277,13 @@ class Trainer:
             _, batch = next(self.train_loader_iter)
         return batch
 
-    def _one_training_step(self, config: Config, step: int) -> None:
+    def _one_training_step(self, config: Config, step: int, batches: list | None = None) -> None:
         self.model.train()
         self.optimizer.zero_grad()
         loss_accum = None
         for micro_step in range(self.training_info["grad_accum_steps"]):
-            l = self._one_training_micro_step(config, micro_step, self._next_batch())
+            batch = batches[micro_step] if batches is not None else self._next_batch()
+            l = self._one_training_micro_step(config, micro_step, batch)
             loss_accum = l if loss_accum is None else loss_accum + l
         lr = self._lr_scheduler(step, self.training_info["max_steps"], config.optim.warmup_steps,
                                 config.optim.max_lr, config.optim.min_lr)
@@ -294,12 +297,14 @@ class Trainer:
         self.one_step_results["loss"] = loss_accum
         self.one_step_results["grad_norm"] = norm
 
-    def train_step(self, step: int) -> dict:
+    def train_step(self, step: int, batches: list | None = None) -> dict:
         """One optimizer step (all micro-steps). Public entry for callers that
         drive the loop themselves; returns `{lr, loss, grad_norm}` with `loss`
-        and `grad_norm` as 0-d tensors on the training device."""
+        and `grad_norm` as 0-d tensors on the training device. `batches`
+        (optional) is a list of `grad_accum_steps` dicts with full-sequence
+        `input_ids` / `labels`; by default the trainer's own loader is used."""
         self.one_step_results = {}
-        self._one_training_step(self.config, step)
+        self._one_training_step(self.config, step, batches)
         return self.one_step_results
 
     # ------------------------------------------------------------------ resume / save
