@@ -1,0 +1,392 @@
+// Causal GQA flash attention, backward, on tcgen05 / TMEM.
+//
+// Inputs: packed qkv[B,T,Hq+2Hkv,hd], o[B,T,Hq,hd], do[B,T,Hq,hd] (bf16),
+// lse[B,Hq,T] (fp32). Output: dqkv[B,T,Hq+2Hkv,hd] (bf16) in the packed layout,
+// so the QKV projection's dgrad/wgrad GEMMs consume one tensor.
+//
+// Three launches:
+//   1. delta[b,h,t] = sum_d do*o
+//   2. main kernel: one CTA per (128-row KV tile, batch, KV head). K and V stay in
+//      shared memory; the CTA walks over every query head of the group and every
+//      query tile at or below the diagonal. Per step five MMAs run on the
+//      tensor cores:   S = Q K^T,  dP = dO V^T            (TMEM, fp32)
+//                      dV += P^T dO,  dK += dS^T Q         (TMEM accumulators)
+//                      dQ  = dS K                          (TMEM, flushed per step)
+//      P and dS are written once to shared memory as [q][kv] bf16 tiles in the
+//      swizzled operand layout; read as K-major they feed dQ, read as MN-major
+//      they are P^T / dS^T, and Q / dO / K / V tiles are used as loaded (MN-major
+//      where the product needs their transpose), so nothing is transposed.
+//      Two softmax warpgroups (one thread per query row, half of the KV columns
+//      each) turn S, dP into P, dS; dQ tiles are added to an fp32 buffer with
+//      vector reductions because several KV tiles contribute to one query row.
+//      For hd = 64 the next step's S / dP MMAs are issued while the softmax
+//      warps still work on the current step.
+//   3. dq (fp32, [B,Hq,T,hd]) -> bf16 into dqkv.
+// Every wait is bounded; on a timeout the CTA records a status code, leaves its
+// loops and still releases its tensor memory.
+#include "common.cuh"
+
+namespace tlm {
+
+constexpr int AB_TILE = 128, AB_THREADS = 320;
+
+struct AttnBwdParams {
+  __nv_bfloat16* dqkv;
+  float* dq_acc;            // [B,Hq,T,hd] fp32, zeroed by the launcher
+  const float* lse;
+  const float* delta;
+  int B, T, Hq, Hkv;
+  float scale, scale_log2;
+  unsigned int* status;
+};
+
+template <int HD>
+struct AttnBwdCfg {
+  static constexpr int STAGES = HD == 64 ? 2 : 1;
+  static constexpr bool PIPELINED = HD == 64;            // dQ has its own TMEM columns
+  static constexpr int TILE_BYTES = AB_TILE * HD * 2;
+  static constexpr int PD_BYTES = AB_TILE * AB_TILE * 2;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  static constexpr int OFF_Q = OFF_V + TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + STAGES * TILE_BYTES;
+  static constexpr int OFF_P = OFF_DO + STAGES * TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + PD_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + PD_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
+  static constexpr uint32_t DQ_COL = HD == 64 ? 384 : 0;  // hd 128: dQ reuses the S columns
+};
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int B, int T, int Hq, int hd) {
+  // one warp per (b, t, h) row of hd elements
+  const long long rows = (long long)B * T * Hq;
+  const int lane = threadIdx.x & 31;
+  for (long long r = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; r < rows; r += ((long long)gridDim.x * blockDim.x) >> 5) {
+    float acc = 0.f;
+    for (int c = lane * 2; c < hd; c += 64) {
+      const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(o + r * hd + c));
+      const float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + r * hd + c));
+      acc += a.x * d.x + a.y * d.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const long long bt = r / Hq; const int h = (int)(r % Hq);
+      const long long b = bt / T; const int t = (int)(bt % T);
+      delta[(b * Hq + h) * T + t] = acc;
+    }
+  }
+}
+
+__global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int B, int T,
+                                       int Hq, int heads_total, int hd) {
+  const int vec = hd / 8;
+  const long long total = (long long)B * Hq * T * vec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec);
+    long long r = i / vec;
+    const int t = (int)(r % T); r /= T;
+    const int h = (int)(r % Hq); const long long b = r / Hq;
+    const float4 a = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8);
+    const float4 c = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8 + 4);
+    uint4 out = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(c.x, c.y), pack_bf16(c.z, c.w));
+    *reinterpret_cast<uint4*>(dqkv + ((b * T + t) * heads_total + h) * (long long)hd + v * 8) = out;
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                const AttnBwdParams p) {
+  using C = AttnBwdCfg<HD>;
+  constexpr int KB = HD / 64;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sal = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  // barriers: 0,1 qdo_full  2,3 qdo_empty  4 kv_full  5 sdp_full  6 sdp_consumed  7 pds_full  8 dq_full  9 dq_consumed
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sal + C::OFF_BAR + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (p.T + AB_TILE - 1) / AB_TILE;
+  const int j = blockIdx.x;                                   // KV tile
+  const int b = blockIdx.y / p.Hkv, kvh = blockIdx.y % p.Hkv;
+  const int rep = p.Hq / p.Hkv;
+  const int per_head = n_tiles - j;                           // query tiles j..n_tiles-1
+  const int n_it = rep * per_head;
+  const int heads_total = p.Hq + 2 * p.Hkv;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 10; ++i) mbar_init(bar(i), (i == 6 || i == 7 || i == 9) ? 8 : 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(bar(4), 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        tma_load_4d(sbase + C::OFF_K + kb * 16384, &tm_qkv, bar(4), kb * 64, p.Hq + kvh, j * AB_TILE, b);
+        tma_load_4d(sbase + C::OFF_V + kb * 16384, &tm_qkv, bar(4), kb * 64, p.Hq + p.Hkv + kvh, j * AB_TILE, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % C::STAGES;
+        const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
+        if (!mbar_wait(bar(2 + st), ph ^ 1u, 21, abort_flag, p.status)) break;
+        const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
+        mbar_expect_tx(bar(st), 2 * C::TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_4d(sbase + C::OFF_Q + st * C::TILE_BYTES + kb * 16384, &tm_qkv, bar(st), kb * 64, hq, qi * AB_TILE, b);
+          tma_load_4d(sbase + C::OFF_DO + st * C::TILE_BYTES + kb * 16384, &tm_do, bar(st), kb * 64, hq, qi * AB_TILE, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(AB_TILE, AB_TILE, 0, 0);     // S, dP : A, B K-major
+      constexpr uint32_t idesc_t = umma_idesc_bf16(AB_TILE, HD, 1, 1);          // dV, dK: A, B MN-major
+      constexpr uint32_t idesc_q = umma_idesc_bf16(AB_TILE, HD, 0, 1);          // dQ    : A K-major, B MN-major
+      const uint32_t sk = sbase + C::OFF_K, sv = sbase + C::OFF_V, sp = sbase + C::OFF_P, sds = sbase + C::OFF_DS;
+      auto issue_s_dp = [&](int it) -> bool {
+        const int st = it % C::STAGES;
+        if (!mbar_wait(bar(st), (uint32_t)(it / C::STAGES) & 1u, 22, abort_flag, p.status)) return false;
+        tc_fence_after();
+        const uint32_t sq = sbase + C::OFF_Q + st * C::TILE_BYTES, sdo = sbase + C::OFF_DO + st * C::TILE_BYTES;
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t) {
+          const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
+          umma_bf16(tmem + C::S_COL, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), idesc_s, t > 0);
+        }
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t) {
+          const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
+          umma_bf16(tmem + C::DP_COL, umma_smem_desc(sdo + off, 16, 1024), umma_smem_desc(sv + off, 16, 1024), idesc_s, t > 0);
+        }
+        umma_commit(bar(5));
+        return true;
+      };
+      bool ok = mbar_wait(bar(4), 0, 23, abort_flag, p.status);
+      if (ok && C::PIPELINED) ok = issue_s_dp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % C::STAGES;
+        const uint32_t par = (uint32_t)it & 1u;
+        if (C::PIPELINED) {
+          if (it + 1 < n_it) {
+            if (!mbar_wait(bar(6), par, 24, abort_flag, p.status)) break;          // S, dP of `it` are in registers
+            if (!issue_s_dp(it + 1)) break;
+          }
+        } else {
+          if (it > 0 && !mbar_wait(bar(9), par ^ 1u, 25, abort_flag, p.status)) break;   // dQ(it-1) read out of the S columns
+          if (!issue_s_dp(it)) break;
+        }
+        if (!mbar_wait(bar(7), par, 26, abort_flag, p.status)) break;              // P, dS published
+        if (C::PIPELINED && it > 0 && !mbar_wait(bar(9), par ^ 1u, 27, abort_flag, p.status)) break;   // dQ columns free
+        tc_fence_after();
+        const uint32_t sq = sbase + C::OFF_Q + st * C::TILE_BYTES, sdo = sbase + C::OFF_DO + st * C::TILE_BYTES;
+        const uint32_t acc = it > 0;
+#pragma unroll
+        for (int t = 0; t < AB_TILE / 16; ++t)      // dV += P^T dO : reduction over 16 query rows per step
+          umma_bf16(tmem + C::DV_COL, umma_smem_desc(sp + t * 2048, 16384, 1024), umma_smem_desc(sdo + t * 2048, 16384, 1024), idesc_t, acc | (t > 0));
+#pragma unroll
+        for (int t = 0; t < AB_TILE / 16; ++t)      // dK += dS^T Q
+          umma_bf16(tmem + C::DK_COL, umma_smem_desc(sds + t * 2048, 16384, 1024), umma_smem_desc(sq + t * 2048, 16384, 1024), idesc_t, acc | (t > 0));
+#pragma unroll
+        for (int t = 0; t < AB_TILE / 16; ++t)      // dQ = dS K : reduction over 16 kv rows per step
+          umma_bf16(tmem + C::DQ_COL, umma_smem_desc(sds + (t >> 2) * 16384 + (t & 3) * 32, 16, 1024), umma_smem_desc(sk + t * 2048, 16384, 1024), idesc_q, t > 0);
+        umma_commit(bar(8));                        // dQ ready; P / dS and this Q / dO stage are free
+        umma_commit(bar(2 + st));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax warpgroups (warps 2..9)
+    const int q4 = warp & 3, half = (warp - 2) >> 2;
+    const int row = q4 * 32 + lane;
+    const uint32_t t_lane = tmem + ((uint32_t)(q4 * 32) << 16);
+    constexpr float LOG2E = 1.4426950408889634f;
+    bool ok = true;
+
+    auto flush_dq = [&](int it) {
+      // this thread: query row `row` of step `it`, columns [half*HD/2, +HD/2)
+      const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
+      const int t_row = qi * AB_TILE + row;
+      float* dst = p.dq_acc + (((long long)b * p.Hq + hq) * p.T + t_row) * HD + half * (HD / 2);
+#pragma unroll
+      for (int c = 0; c < HD / 2; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + C::DQ_COL + half * (HD / 2) + c, r);
+        tmem_ld_wait();
+        if (t_row < p.T) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(dst + c + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(9));
+    };
+
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t par = (uint32_t)it & 1u;
+      const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
+      const int t_row = qi * AB_TILE + row;
+      const bool row_ok = t_row < p.T;
+      const float lse2 = row_ok ? p.lse[((long long)b * p.Hq + hq) * p.T + t_row] * LOG2E : INFINITY;
+      const float dlt = row_ok ? p.delta[((long long)b * p.Hq + hq) * p.T + t_row] : 0.f;
+      const bool diag = (qi == j);
+      if (!mbar_wait(bar(5), par, 28, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t pp[32], dd[32];                      // 64 columns of P and dS, packed bf16 pairs
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(t_lane + C::S_COL + half * 64 + c, s);
+        tmem_ld32(t_lane + C::DP_COL + half * 64 + c, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
+          float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            const int col = half * 64 + c + i;
+            if (col > row) p0 = 0.f;
+            if (col + 1 > row) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dp[i]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dp[i + 1]) - dlt) * p.scale;
+          pp[(c + i) >> 1] = pack_bf16(p0, p1);
+          dd[(c + i) >> 1] = pack_bf16(d0, d1);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(6));           // S / dP columns may be overwritten
+      if (it > 0) {                                 // MMAs of step it-1 done: P / dS free, dQ(it-1) ready
+        if (!mbar_wait(bar(8), par ^ 1u, 29, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+      }
+      uint8_t* prow = sal + C::OFF_P + half * 16384 + row * 128;
+      uint8_t* drow = sal + C::OFF_DS + half * 16384 + row * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const int sw = (ch ^ (row & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(7));
+      if (C::PIPELINED) {
+        if (it > 0) flush_dq(it - 1);
+      } else {
+        if (!mbar_wait(bar(8), par, 30, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        flush_dq(it);
+      }
+    }
+    if (ok && n_it > 0) {
+      if (C::PIPELINED) {
+        if (mbar_wait(bar(8), (uint32_t)(n_it - 1) & 1u, 31, abort_flag, p.status)) { tc_fence_after(); flush_dq(n_it - 1); } else ok = false;
+      }
+      if (ok) {
+        // dV, dK accumulators -> bf16 rows of the packed gradient tensor
+        tc_fence_after();
+        const int t_row = j * AB_TILE + row;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
+          const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
+          __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * HD + half * (HD / 2);
+#pragma unroll
+          for (int c = 0; c < HD / 2; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(t_lane + col0 + c, r);
+            tmem_ld_wait();
+            if (t_row < p.T) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                v.y = pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                v.z = pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                v.w = pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                *reinterpret_cast<uint4*>(dst + c + i) = v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+template <int HD>
+static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const AttnBwdParams& p, cudaStream_t st) {
+  using C = AttnBwdCfg<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.T + AB_TILE - 1) / AB_TILE, p.B * p.Hkv);
+  attn_bwd_kernel<HD><<<grid, AB_THREADS, C::TOTAL, st>>>(mq, mdo, p);
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace tlm
+
+using namespace tlm;
+
+// dq_acc: fp32 scratch [B,Hq,T,hd]; delta: fp32 scratch [B,Hq,T]. Both are owned by the caller.
+TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
+                         float* dq_acc, float* delta, int B, int T, int Hq, int Hkv, int hd, float scale,
+                         cudaStream_t st) {
+  if (hd != 64 && hd != 128) return -4;
+  if (Hq % Hkv != 0) return -5;
+  const long long rows = (long long)B * T * Hq;
+  int blocks = (int)((rows * 32 + 255) / 256);
+  if (blocks > num_sms() * 16) blocks = num_sms() * 16;
+  attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, T, Hq, hd);
+  count_launch();
+  cudaError_t ce = cudaMemsetAsync(dq_acc, 0, (size_t)rows * hd * 4, st);
+  if (ce != cudaSuccess) return (int)ce;
+  CUtensorMap mq, mdo;
+  int e = make_qkv_map(&mq, qkv, B, T, Hq + 2 * Hkv, hd, AB_TILE);
+  if (e) return e;
+  e = make_qkv_map(&mdo, dout, B, T, Hq, hd, AB_TILE);
+  if (e) return e;
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word()};
+  e = hd == 64 ? launch_bwd<64>(mq, mdo, p, st) : launch_bwd<128>(mq, mdo, p, st);
+  if (e) return e;
+  long long items = rows * (hd / 8);
+  int cb = (int)((items + 255) / 256);
+  if (cb > num_sms() * 16) cb = num_sms() * 16;
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd);
+  count_launch();
+  return launch_status();
+}

@@ -1,0 +1,263 @@
+// Causal GQA flash attention, forward, on tcgen05 / TMEM.
+//
+// Input is the packed projection output  qkv[B, T, Hq + 2*Hkv, hd]  (bf16):
+// heads [0,Hq) are queries, [Hq,Hq+Hkv) keys, [Hq+Hkv,Hq+2Hkv) values; query
+// head h reads KV head h / (Hq/Hkv) in place, nothing is expanded or transposed.
+// Output o[B, T, Hq, hd] (bf16) and lse[B, Hq, T] (fp32, natural log).
+//
+// One CTA owns 128 query rows of one (batch, head) and walks over 128-row KV
+// tiles up to the diagonal:
+//   warp 0     TMA: Q once, then K / V tiles into a 2-deep ring (128B swizzle)
+//   warp 1     one lane issues  S = Q K^T  (M128 N128) into TMEM, and after the
+//              softmax warps have published P:  O_j = P V  (M128 N=hd; V is
+//              consumed as an MN-major operand straight from its row-major tile)
+//   warps 2-5  one thread per query row: tcgen05.ld S, running max / sum with
+//              exp2, P (bf16) written to shared memory in the swizzled K-major
+//              operand layout, O accumulated in registers as o = o*alpha + O_j
+// Shared memory is 112 KB (hd 64) so two CTAs share an SM and one CTA's
+// softmax overlaps the other's MMAs. All waits are bounded.
+#include "common.cuh"
+
+namespace tlm {
+
+constexpr int AT_BQ = 128, AT_BKV = 128, AT_THREADS = 192, AT_KV_STAGES = 2;
+
+struct AttnFwdParams {
+  __nv_bfloat16* o;
+  float* lse;
+  int B, T, Hq, Hkv;
+  float scale_log2;        // softmax scale * log2(e)
+  float scale;             // softmax scale
+  unsigned int* status;
+};
+
+template <int HD>
+struct AttnFwdSmem {
+  static constexpr int KB = HD / 64;                   // 64-wide blocks along hd
+  static constexpr int Q_BYTES = AT_BQ * HD * 2;
+  static constexpr int KV_BYTES = AT_BKV * HD * 2;
+  static constexpr int P_BYTES = AT_BQ * AT_BKV * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + AT_KV_STAGES * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + AT_KV_STAGES * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;   // barriers + alignment slack
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams p) {
+  using L = AttnFwdSmem<HD>;
+  constexpr int KB = L::KB;
+  constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sal = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + L::OFF_BAR;
+  // barriers: 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 kv_empty, 7 s_full, 8 p_full, 9 o_full
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sal + L::OFF_BAR + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_q_tiles = gridDim.x;
+  const int qt = n_q_tiles - 1 - blockIdx.x;          // heavy (late) tiles first
+  const int b = blockIdx.y / p.Hq, h = blockIdx.y % p.Hq;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int q0 = qt * AT_BQ;
+  const int n_kv = qt + 1;                            // causal: KV tiles 0..qt
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 10; ++i) mbar_init(bar(i), i == 8 ? 4 : 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(0), L::Q_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) tma_load_4d(sbase + L::OFF_Q + kb * 16384, &tm_qkv, bar(0), kb * 64, h, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(bar(5 + st), ph ^ 1u, 11, abort_flag, p.status)) break;
+        mbar_expect_tx(bar(1 + st), L::KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(sbase + L::OFF_K + st * L::KV_BYTES + kb * 16384, &tm_qkv, bar(1 + st), kb * 64, p.Hq + kvh, j * AT_BKV, b);
+        mbar_expect_tx(bar(3 + st), L::KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(sbase + L::OFF_V + st * L::KV_BYTES + kb * 16384, &tm_qkv, bar(3 + st), kb * 64, p.Hq + p.Hkv + kvh, j * AT_BKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(AT_BQ, AT_BKV, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(AT_BQ, HD, 0, 1);
+      bool ok = mbar_wait(bar(0), 0, 12, abort_flag, p.status);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(bar(1 + st), ph, 13, abort_flag, p.status)) break;
+        tc_fence_after();
+        const uint32_t sq = sbase + L::OFF_Q, sk = sbase + L::OFF_K + st * L::KV_BYTES;
+#pragma unroll
+        for (int t = 0; t < HD / 16; ++t) {
+          const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
+          umma_bf16(tmem + S_COL, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), idesc_s, t > 0);
+        }
+        umma_commit(bar(7));                                    // S ready
+        if (!mbar_wait(bar(8), (uint32_t)j & 1u, 14, abort_flag, p.status)) break;   // P written
+        if (!mbar_wait(bar(3 + st), ph, 15, abort_flag, p.status)) break;            // V landed
+        tc_fence_after();
+        const uint32_t sp = sbase + L::OFF_P, sv = sbase + L::OFF_V + st * L::KV_BYTES;
+#pragma unroll
+        for (int t = 0; t < AT_BKV / 16; ++t) {
+          const uint64_t ad = umma_smem_desc(sp + (t >> 2) * 16384 + (t & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_smem_desc(sv + t * 2048, 16384, 1024);      // MN-major: 16 kv rows per step
+          umma_bf16(tmem + O_COL, ad, bd, idesc_o, t > 0);
+        }
+        umma_commit(bar(9));                                    // O_j ready, P free
+        umma_commit(bar(5 + st));                               // K/V stage free
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;                              // row inside the tile == TMEM lane
+    const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    float o_acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(bar(7), (uint32_t)j & 1u, 16, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (j == qt);
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < AT_BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + S_COL + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(r[i]);
+          if (!diag || (c + i) <= row) mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = ex2_approx((m_run - m_new) * p.scale_log2);     // 0 on the first tile (m_run = -inf)
+      const float neg_m = -m_new * p.scale_log2;
+      // pass 2: probabilities -> shared memory (swizzled K-major operand layout)
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < AT_BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + S_COL + c, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+          if (diag) { if ((c + i) > row) p0 = 0.f; if ((c + i + 1) > row) p1 = 0.f; }
+          l_tile += p0 + p1;
+          pk[i >> 1] = pack_bf16(p0, p1);
+        }
+        // 32 columns = four 16-byte chunks of this row inside 64-column block (c / 64)
+        uint8_t* prow = sal + L::OFF_P + (c >> 6) * 16384 + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = ((c & 63) >> 3) + ch;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        }
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(8));
+      // O_j
+      if (!mbar_wait(bar(9), (uint32_t)j & 1u, 17, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + O_COL + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], alpha, __uint_as_float(r[i]));
+      }
+      tc_fence_before();
+    }
+    const int t_row = q0 + row;
+    if (ok && t_row < p.T) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * HD;
+#pragma unroll
+      for (int i = 0; i < HD; i += 8) {
+        uint4 v;
+        v.x = pack_bf16(o_acc[i] * inv, o_acc[i + 1] * inv);
+        v.y = pack_bf16(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
+        v.z = pack_bf16(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
+        v.w = pack_bf16(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
+        *reinterpret_cast<uint4*>(out + i) = v;
+      }
+      p.lse[((long long)b * p.Hq + h) * p.T + t_row] = m_run * p.scale + __logf(l_run);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// 4-D map over the packed tensor: dims (hd, heads, T, B); box (64, 1, rows, 1).
+int make_qkv_map(CUtensorMap* map, const void* base, int B, int T, int heads, int hd, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)hd, (uint64_t)heads, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)heads * hd * 2, (uint64_t)T * heads * hd * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_tmap_bf16(map, base, 4, dims, strides, box);
+}
+
+template <int HD>
+static int launch_fwd(const CUtensorMap& map, const AttnFwdParams& p, cudaStream_t st) {
+  using L = AttnFwdSmem<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.T + AT_BQ - 1) / AT_BQ, p.B * p.Hq);
+  attn_fwd_kernel<HD><<<grid, AT_THREADS, L::TOTAL, st>>>(map, p);
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace tlm
+
+using namespace tlm;
+
+TLM_API int tlm_attn_fwd(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,
+                         cudaStream_t st) {
+  if (hd != 64 && hd != 128) return -4;
+  if (Hq % Hkv != 0) return -5;
+  CUtensorMap map;
+  int e = make_qkv_map(&map, qkv, B, T, Hq + 2 * Hkv, hd, AT_BQ);
+  if (e) return e;
+  AttnFwdParams p{(__nv_bfloat16*)o, lse, B, T, Hq, Hkv, scale * 1.4426950408889634f, scale, status_word()};
+  return hd == 64 ? launch_fwd<64>(map, p, st) : launch_fwd<128>(map, p, st);
+}

@@ -255,4 +255,13 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t*
 
 int num_sms();
 
+// 4-D bf16 map over a packed [B, T, heads, hd] tensor: dims (hd, heads, T, B), box (64, 1, box_rows, 1).
+int make_qkv_map(CUtensorMap* map, const void* base, int B, int T, int heads, int hd, int box_rows);
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 }  // namespace tlm

@@ -268,13 +268,13 @@ __global__ void ce_inplace_kernel(__nv_bfloat16* __restrict__ logits, const long
     m = nm;
   }
   const float wm = warp_max(m);
-  s = warp_sum(s * __expf(m - wm));
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));   // threads (or whole warps) may have seen no element
   if (lane == 0) { red_m[warp] = wm; red_s[warp] = s; }
   __syncthreads();
   if (warp == 0) {
     float mm = lane < nwarps ? red_m[lane] : -INFINITY, ss = lane < nwarps ? red_s[lane] : 0.f;
     const float gm = warp_max(mm);
-    ss = warp_sum(ss * __expf(mm - gm));
+    ss = warp_sum(mm == -INFINITY ? 0.f : ss * __expf(mm - gm));
     if (lane == 0) {
       row_m = gm; row_l = ss;
       atomicAdd(loss_sum, gm + __logf(ss) - __bfloat162float(row[tgt]));

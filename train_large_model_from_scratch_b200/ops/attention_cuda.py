@@ -1,38 +1,64 @@
-"""CUDA attention entry points used by `ops.native`.
+"""CUDA attention entry points used by `ops.native`: the tcgen05 flash-attention
+kernels for head dims 64 and 128.
 
-INTERIM: until the tcgen05 flash-attention kernels land, the forward and
-backward call the library SDPA kernels through ATen (a library call, like a
-cuBLAS GEMM). Signature and tensor layouts are those of the final kernels.
+Head dims other than 64 / 128 (and non-causal calls) go to the library SDPA
+kernels through ATen (a library call, like a cuBLAS GEMM).
 """
 from __future__ import annotations
 
+import math
+
 import torch
+
+from . import native
+
+
+def _native_ok(hd: int) -> bool:
+    return hd in (64, 128)
 
 
 def fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
-    q = qkv[:, :, :n_q].transpose(1, 2)
-    k = qkv[:, :, n_q:n_q + n_kv].transpose(1, 2)
-    v = qkv[:, :, n_q + n_kv:].transpose(1, 2)
-    rep = n_q // n_kv
-    if rep > 1:
-        k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
-    out = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, causal, False)
-    o, lse = out[0], out[1]
-    fwd._ctx = None
-    return o.transpose(1, 2).contiguous(), (lse, out[6], out[7])
-
-
-def bwd(do, qkv, o, lse_pack, n_q: int, n_kv: int, causal: bool):
-    lse, seed, offset = lse_pack
+    """qkv `[B, T, n_q + 2 n_kv, hd]` bf16 -> (o `[B, T, n_q, hd]` bf16, lse `[B, n_q, T]` fp32)."""
     B, T, _, hd = qkv.shape
-    rep = n_q // n_kv
+    if causal and _native_ok(hd):
+        assert qkv.is_contiguous()
+        o = torch.empty(B, T, n_q, hd, dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty(B, n_q, T, dtype=torch.float32, device=qkv.device)
+        native._check(native.lib().tlm_attn_fwd(qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), B, T, n_q, n_kv, hd,
+                                                1.0 / math.sqrt(hd), native._stream()), "attn_fwd")
+        return o, lse
+    q, k, v = _split(qkv, n_q, n_kv)
+    out = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, causal, False)
+    return out[0].transpose(1, 2).contiguous(), out[1]
+
+
+def _split(qkv, n_q, n_kv):
     q = qkv[:, :, :n_q].transpose(1, 2)
     k = qkv[:, :, n_q:n_q + n_kv].transpose(1, 2)
     v = qkv[:, :, n_q + n_kv:].transpose(1, 2)
+    rep = n_q // n_kv
     if rep > 1:
         k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    return q, k, v
+
+
+def bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
+    """-> dqkv `[B, T, n_q + 2 n_kv, hd]` bf16 (gradient of the packed input)."""
+    B, T, _, hd = qkv.shape
+    if causal and _native_ok(hd):
+        do, o = do.contiguous(), o.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq_acc = torch.empty(B, n_q, T, hd, dtype=torch.float32, device=qkv.device)
+        delta = torch.empty(B, n_q, T, dtype=torch.float32, device=qkv.device)
+        native._check(native.lib().tlm_attn_bwd(qkv.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                                dqkv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, T, n_q, n_kv,
+                                                hd, 1.0 / math.sqrt(hd), native._stream()), "attn_bwd")
+        return dqkv
+    rep = n_q // n_kv
+    q, k, v = _split(qkv, n_q, n_kv)
+    zero = torch.zeros((), dtype=torch.int64, device=qkv.device)
     dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-        do.transpose(1, 2), q, k, v, o.transpose(1, 2), lse, None, None, T, T, 0.0, causal, seed, offset)
+        do.transpose(1, 2), q, k, v, o.transpose(1, 2), lse, None, None, T, T, 0.0, causal, zero, zero)
     if rep > 1:
         dk = dk.reshape(B, n_kv, rep, T, hd).sum(2)
         dv = dv.reshape(B, n_kv, rep, T, hd).sum(2)

@@ -1,0 +1,139 @@
+"""Per-kernel timing against the measured roofline.
+
+    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,attn,elementwise] [--small]
+
+Times each kernel with CUDA events on the launching stream after warm-up,
+flushing L2 (a 256 MB write) between timed launches, and prints one JSON line
+per case with achieved TFLOP/s or GB/s and, when a peaks file is present
+(`MEASURED_PEAKS.json`), the fraction of the measured cuBLAS / copy peak. The
+library GEMM (`torch.matmul`, cuBLAS) is timed on the same shapes for context.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import native
+
+
+def _peaks():
+    for p in (os.environ.get("TLM_MEASURED_PEAKS"), "MEASURED_PEAKS.json"):
+        if p and os.path.exists(p):
+            with open(p) as f:
+                return json.load(f)
+    return {}
+
+
+_FLUSH = None
+
+
+def _time(fn, iters=10, warmup=3):
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _FLUSH.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(small: bool):
+    pk = _peaks().get("bf16_tflops")
+    M = 4096 if small else 32768
+    shapes = [("qkv_fwd", M, 2048, 1024), ("out_fwd", M, 1024, 1024), ("gate_up_fwd", M, 8192, 1024),
+              ("down_fwd", M, 1024, 4096), ("lm_head_chunk", 4096, 50304, 1024)]
+    for name, m, n, k in shapes:
+        x = torch.randn(m, k, device="cuda").bfloat16()
+        w = torch.randn(n, k, device="cuda").bfloat16()
+        dy = torch.randn(m, n, device="cuda").bfloat16()
+        acc = torch.zeros(n, k, device="cuda")
+        flops = 2.0 * m * n * k
+        cases = [("nt", lambda: native.gemm_nt(x, w), lambda: x @ w.t()),
+                 ("nn", lambda: native.gemm_nn(dy, w), lambda: dy @ w),
+                 ("tn_acc", lambda: native.gemm_tn_accum(dy, x, acc), lambda: acc.addmm_(dy.t().float(), x.float()) if False else dy.t() @ x)]
+        for kind, ours, lib in cases:
+            med, best = _time(ours)
+            lmed, _ = _time(lib)
+            rec = {"kernel": f"gemm_{kind}", "case": name, "M": m, "N": n, "K": k, "ms": round(med, 4),
+                   "ms_best": round(best, 4), "tflops": round(flops / med / 1e9, 1), "cublas_ms": round(lmed, 4),
+                   "cublas_tflops": round(flops / lmed / 1e9, 1)}
+            if pk:
+                rec["frac_of_measured_peak"] = round(flops / med / 1e9 / pk, 3)
+            print(json.dumps(rec), flush=True)
+
+
+def bench_elementwise(small: bool):
+    bw = _peaks().get("hbm_gbs")
+    rows, D, I = (4096 if small else 32768), 1024, 4096
+    x = torch.randn(rows, D, device="cuda")
+    delta = torch.randn(rows, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    gu = torch.randn(rows, 2 * I, device="cuda").bfloat16()
+    dact = torch.randn(rows, I, device="cuda").bfloat16()
+    mg = torch.zeros(D, device="cuda")
+    x_new, h, rstd = native.add_rmsnorm_fwd(x, delta, w, 1e-6)
+    cases = [
+        ("add_rmsnorm_fwd", lambda: native.add_rmsnorm_fwd(x, delta, w, 1e-6), rows * D * (4 + 2 + 4 + 2)),
+        ("add_rmsnorm_bwd", lambda: native.add_rmsnorm_bwd(x, delta, x_new, rstd, w, mg, True), rows * D * (4 + 2 + 4 + 4 + 2)),
+        ("swiglu_fwd", lambda: native.swiglu_fwd(gu), rows * I * 6),
+        ("swiglu_bwd", lambda: native.swiglu_bwd(dact, gu), rows * I * 10),
+    ]
+    n = 1 << 26
+    p, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v.abs_()
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    sc = torch.ones((), device="cuda")
+    cases.append(("adamw", lambda: native.adamw_step(p, m, v, g, out, sc, 3, 1e-4, 0.9, 0.95, 1e-8, 0.1), n * 30))
+    cases.append(("sumsq", lambda: native.sumsq(g), n * 4))
+    lg = torch.randn(2048 if small else 4096, 50304, device="cuda").bfloat16()
+    tg = torch.randint(0, 50304, (lg.shape[0],), device="cuda")
+    ls = torch.zeros((), device="cuda")
+    cases.append(("ce_inplace", lambda: native.ce_fwd_bwd_inplace(lg, tg, sc, ls, -100, True), lg.numel() * 4))
+    for name, fn, nbytes in cases:
+        med, best = _time(fn)
+        rec = {"kernel": name, "ms": round(med, 4), "ms_best": round(best, 4), "algorithmic_GB": round(nbytes / 1e9, 3),
+               "GBps": round(nbytes / med / 1e6, 1)}
+        if bw:
+            rec["frac_of_measured_copy_bw"] = round(nbytes / med / 1e6 / bw, 3)
+        print(json.dumps(rec), flush=True)
+
+
+def bench_attn(small: bool):
+    pk = _peaks().get("bf16_tflops")
+    B, T, Hq, Hkv, hd = (1 if small else 8), 4096, 16, 8, int(os.environ.get("TLM_BENCH_HD", "64"))
+    qkv = torch.randn(B, T, Hq + 2 * Hkv, hd, device="cuda").bfloat16()
+    o, lse = native.flash_attn_fwd(qkv, Hq, Hkv, True)
+    do = torch.randn_like(o)
+    f_fwd = 4.0 * B * Hq * T * T * hd / 2
+    for name, fn, fl in [("attn_fwd", lambda: native.flash_attn_fwd(qkv, Hq, Hkv, True), f_fwd),
+                         ("attn_bwd", lambda: native.flash_attn_bwd(do, qkv, o, lse, Hq, Hkv, True), 2.5 * f_fwd)]:
+        med, best = _time(fn)
+        rec = {"kernel": name, "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "hd": hd, "ms": round(med, 4),
+               "tflops_causal": round(fl / med / 1e9, 1)}
+        if pk:
+            rec["frac_of_measured_peak"] = round(fl / med / 1e9 / pk, 3)
+        print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,elementwise,attn")
+    ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures)")
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    for w in a.what.split(","):
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "attn": bench_attn}[w](a.small)
+    native.raise_on_device_status()

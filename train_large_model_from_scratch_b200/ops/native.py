@@ -61,6 +61,8 @@ _SIGS = {
     "tlm_ce_inplace": (_I, [_P, _P, _P, _P, _I, _I, _LL, _LL, _I, _P]),
     "tlm_sumsq_scratch_floats": (_I, []),
     "tlm_sumsq": (_I, [_P, _LL, _P, _P, _P]),
+    "tlm_attn_fwd": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
+    "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P]),
 }
 
