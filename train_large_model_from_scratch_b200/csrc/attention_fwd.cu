@@ -13,7 +13,9 @@
 //              consumed as an MN-major operand straight from its row-major tile)
 //   warps 2-5  one thread per query row: tcgen05.ld S, running max / sum with
 //              exp2, P (bf16) written to shared memory in the swizzled K-major
-//              operand layout, O accumulated in registers as o = o*alpha + O_j
+//              operand layout. O accumulates in TMEM across KV tiles; it is only
+//              rescaled (ld / multiply / st) when the row maximum grew by more
+//              than 2^8, and S of tile j+1 is issued while tile j's softmax runs
 // Shared memory is 112 KB (hd 64) so two CTAs share an SM and one CTA's
 // softmax overlaps the other's MMAs. All waits are bounded.
 #include "common.cuh"
@@ -42,8 +44,15 @@ struct AttnFwdSmem {
   static constexpr int OFF_V = OFF_K + AT_KV_STAGES * KV_BYTES;
   static constexpr int OFF_P = OFF_V + AT_KV_STAGES * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;   // barriers + alignment slack
+  static constexpr int TOTAL = OFF_BAR + 256;          // + barriers; 2 CTAs (hd 64) must fit in 228 KB
 };
+
+// Thread `row` owns one query row: running reference max `m_ref`, running sum `l_run`.
+// The exponent reference is only moved (and O rescaled in TMEM) when the tile
+// maximum exceeds it by more than RESCALE_LOG2 in the log2 domain, so most tiles
+// do no rescaling; the result is exact either way because the same reference
+// is used for P and for the final normalisation.
+constexpr float RESCALE_LOG2 = 8.0f;
 
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS)
@@ -51,11 +60,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
   using L = AttnFwdSmem<HD>;
   constexpr int KB = L::KB;
   constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sal = smem_raw + (sbase - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t sbase = smem_u32(smem_raw);
+  uint8_t* sal = smem_raw;
+  if (sbase & 1023u) {                                // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) report_status(p.status, (10u << 8) | 2u);
+    return;
+  }
   const uint32_t bar0 = sbase + L::OFF_BAR;
-  // barriers: 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 kv_empty, 7 s_full, 8 p_full, 9 o_full
+  // barriers: 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 kv_empty, 7 s_full, 8 p_full, 9 o_done, 10 s_consumed
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sal + L::OFF_BAR + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -69,7 +82,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
   const int n_kv = qt + 1;                            // causal: KV tiles 0..qt
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(bar(i), i == 8 ? 4 : 1);
+    for (int i = 0; i < 11; ++i) mbar_init(bar(i), (i == 8 || i == 10) ? 4 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -103,30 +116,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(AT_BQ, AT_BKV, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(AT_BQ, HD, 0, 1);
-      bool ok = mbar_wait(bar(0), 0, 12, abort_flag, p.status);
-      for (int j = 0; j < n_kv && ok; ++j) {
+      const uint32_t sq = sbase + L::OFF_Q, sp = sbase + L::OFF_P;
+      auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(bar(1 + st), ph, 13, abort_flag, p.status)) break;
+        if (!mbar_wait(bar(1 + st), (uint32_t)(j >> 1) & 1u, 13, abort_flag, p.status)) return false;
         tc_fence_after();
-        const uint32_t sq = sbase + L::OFF_Q, sk = sbase + L::OFF_K + st * L::KV_BYTES;
+        const uint32_t sk = sbase + L::OFF_K + st * L::KV_BYTES;
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t) {
           const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
           umma_bf16(tmem + S_COL, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), idesc_s, t > 0);
         }
-        umma_commit(bar(7));                                    // S ready
-        if (!mbar_wait(bar(8), (uint32_t)j & 1u, 14, abort_flag, p.status)) break;   // P written
-        if (!mbar_wait(bar(3 + st), ph, 15, abort_flag, p.status)) break;            // V landed
+        umma_commit(bar(7));
+        return true;
+      };
+      bool ok = mbar_wait(bar(0), 0, 12, abort_flag, p.status);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t par = (uint32_t)j & 1u;
+        if (j + 1 < n_kv) {                                     // S of the next tile overlaps this tile's softmax
+          if (!mbar_wait(bar(10), par, 18, abort_flag, p.status)) break;
+          if (!issue_s(j + 1)) break;
+        }
+        if (!mbar_wait(bar(8), par, 14, abort_flag, p.status)) break;                        // P written
+        if (!mbar_wait(bar(3 + st), (uint32_t)(j >> 1) & 1u, 15, abort_flag, p.status)) break;   // V landed
         tc_fence_after();
-        const uint32_t sp = sbase + L::OFF_P, sv = sbase + L::OFF_V + st * L::KV_BYTES;
+        const uint32_t sv = sbase + L::OFF_V + st * L::KV_BYTES;
 #pragma unroll
         for (int t = 0; t < AT_BKV / 16; ++t) {
           const uint64_t ad = umma_smem_desc(sp + (t >> 2) * 16384 + (t & 3) * 32, 16, 1024);
           const uint64_t bd = umma_smem_desc(sv + t * 2048, 16384, 1024);      // MN-major: 16 kv rows per step
-          umma_bf16(tmem + O_COL, ad, bd, idesc_o, t > 0);
+          umma_bf16(tmem + O_COL, ad, bd, idesc_o, (j > 0) | (t > 0));
         }
-        umma_commit(bar(9));                                    // O_j ready, P free
+        umma_commit(bar(9));                                    // O updated, P free
         umma_commit(bar(5 + st));                               // K/V stage free
       }
     }
@@ -134,88 +157,136 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
     const int q = warp & 3;
     const int row = q * 32 + lane;                              // row inside the tile == TMEM lane
     const uint32_t t_lane = tmem + ((uint32_t)(q * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+    const float tau = RESCALE_LOG2 / p.scale_log2;              // threshold in raw-score units
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(bar(7), (uint32_t)j & 1u, 16, abort_flag, p.status)) { ok = false; break; }
+      const uint32_t par = (uint32_t)j & 1u;
+      if (!mbar_wait(bar(7), par, 16, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (j == qt);
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < AT_BKV; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + S_COL + c, r);
-        tmem_ld_wait();
+      // ---- pass 1: row maximum; the next chunk's load is in flight while one is reduced
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      auto fold = [&](const uint32_t* r, int c) {
+        if (!diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]);
-          if (!diag || (c + i) <= row) mx = fmaxf(mx, s);
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[i]));     mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(r[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c + i <= row) mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+        }
+      };
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(t_lane + S_COL, ra);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 32, rb);
+        fold(ra, 0);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 64, ra);
+        fold(rb, 32);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 96, rb);
+        fold(ra, 64);
+        tmem_ld_wait();
+        fold(rb, 96);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // ---- move the reference (and rescale O in TMEM) only when the maximum grew a lot
+      const bool grow = mx > m_ref + tau;
+      if (j == 0) {
+        m_ref = mx;
+      } else {
+        // PV of the previous tile must be complete before P is overwritten and before O is touched
+        if (!mbar_wait(bar(9), par ^ 1u, 17, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2_approx((m_ref - mx) * p.scale_log2) : 1.f;
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(t_lane + O_COL + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_lane + O_COL + c, r);
+          }
+          tmem_st_wait();
+          l_run *= alpha;
+          if (grow) m_ref = mx;
         }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = ex2_approx((m_run - m_new) * p.scale_log2);     // 0 on the first tile (m_run = -inf)
-      const float neg_m = -m_new * p.scale_log2;
-      // pass 2: probabilities -> shared memory (swizzled K-major operand layout)
-      float l_tile = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < AT_BKV; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + S_COL + c, r);
-        tmem_ld_wait();
+      const float neg_m = -m_ref * p.scale_log2;
+      // ---- pass 2: probabilities -> shared memory (swizzled K-major operand layout)
+      float l_a = 0.f, l_b = 0.f;
+      auto emit = [&](const uint32_t* r, int c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
           float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
           if (diag) { if ((c + i) > row) p0 = 0.f; if ((c + i + 1) > row) p1 = 0.f; }
-          l_tile += p0 + p1;
+          l_a += p0; l_b += p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
-        // 32 columns = four 16-byte chunks of this row inside 64-column block (c / 64)
         uint8_t* prow = sal + L::OFF_P + (c >> 6) * 16384 + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const int chunk = ((c & 63) >> 3) + ch;
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
         }
+      };
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(t_lane + S_COL, ra);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 32, rb);
+        emit(ra, 0);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 64, ra);
+        emit(rb, 32);
+        tmem_ld_wait();
+        tmem_ld32(t_lane + S_COL + 96, rb);
+        emit(ra, 64);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(10));                    // S columns may be overwritten by the next tile
+        emit(rb, 96);
       }
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
+      l_run += l_a + l_b;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(8));
-      // O_j
-      if (!mbar_wait(bar(9), (uint32_t)j & 1u, 17, abort_flag, p.status)) { ok = false; break; }
+    }
+    if (ok) ok = mbar_wait(bar(9), (uint32_t)(n_kv - 1) & 1u, 19, abort_flag, p.status);
+    const int t_row = q0 + row;
+    if (ok) {
       tc_fence_after();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * HD;
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
         uint32_t r[32];
         tmem_ld32(t_lane + O_COL + c, r);
         tmem_ld_wait();
+        if (t_row < p.T) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], alpha, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(out + c + i) = v;
+          }
+        }
       }
-      tc_fence_before();
-    }
-    const int t_row = q0 + row;
-    if (ok && t_row < p.T) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * HD;
-#pragma unroll
-      for (int i = 0; i < HD; i += 8) {
-        uint4 v;
-        v.x = pack_bf16(o_acc[i] * inv, o_acc[i + 1] * inv);
-        v.y = pack_bf16(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-        v.z = pack_bf16(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-        v.w = pack_bf16(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-        *reinterpret_cast<uint4*>(out + i) = v;
-      }
-      p.lse[((long long)b * p.Hq + h) * p.T + t_row] = m_run * p.scale + __logf(l_run);
+      if (t_row < p.T) p.lse[((long long)b * p.Hq + h) * p.T + t_row] = m_ref * p.scale + __logf(l_run);
     }
   }
 
