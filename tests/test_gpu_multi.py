@@ -1,0 +1,61 @@
+"""Multi-GPU paths (need >= 2 GPUs): peer-memory optimizer collectives against the
+NCCL path, and layout invariance of the loss curve on real GPUs."""
+import os
+import sys
+
+import pytest
+import torch
+
+from dist_utils import ROOT, free_port
+
+pytestmark = pytest.mark.gpu
+
+FLAGS = ("--use_mock_data --mock_data_num_samples 256 --seq_len 256 --max_epochs 1 --warmup_steps 2 "
+         "--tied_lm_head --num_layer 2 --hidden_size 256 --num_attention_heads 4 --num_key_value_heads 2 "
+         "--intermediate_size 512 --vocab_size 8192 --max_lr 1e-3 --min_lr 1e-4 --total_batch_size 4096 "
+         "--batch_size 2 --debug --use_distributed_optimizer").split()
+
+
+def _run(world, env_extra, flags):
+    import json
+    import subprocess
+    import tempfile
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = tempfile.mktemp(suffix=".json")
+    log_dir = tempfile.mkdtemp(prefix="tlm_gpu_")
+    env = dict(os.environ, TLM_TEST_OUT=out, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    env.update(env_extra)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(ROOT, "tests", "_trainer_worker.py")] + flags + ["--log_dir", log_dir]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    with open(out) as f:
+        return json.load(f)
+
+
+def _close(a, b, tol):
+    for k in a:
+        assert abs(a[k] - b[k]) <= tol * max(1.0, abs(a[k])), (k, a[k], b[k])
+
+
+def test_peer_collectives_match_nccl():
+    ref = _run(2, {"TLM_COMM": "nccl"}, FLAGS + ["--sep_size", "1"])
+    p2p = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, FLAGS + ["--sep_size", "1"])
+    _close(ref["losses"], p2p["losses"], 2e-3)
+    _close(ref["norms"], p2p["norms"], 2e-2)
+    assert abs(ref["wsum"] - p2p["wsum"]) < 0.5
+
+
+def test_peer_collectives_multimem():
+    ref = _run(2, {"TLM_COMM": "nccl"}, FLAGS + ["--sep_size", "1"])
+    mc = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "1"}, FLAGS + ["--sep_size", "1"])
+    _close(ref["losses"], mc["losses"], 2e-3)
+    _close(ref["norms"], mc["norms"], 2e-2)
+
+
+def test_sequence_parallel_matches_data_parallel_on_gpu():
+    dp = _run(2, {}, FLAGS + ["--sep_size", "1"])
+    sp = _run(2, {}, [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)] + ["--sep_size", "2"])
+    _close(dp["losses"], sp["losses"], 5e-3)

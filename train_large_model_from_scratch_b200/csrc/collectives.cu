@@ -1,0 +1,225 @@
+// Gradient reduce-scatter and fused AdamW + parameter all-gather over NVLink
+// peer memory (one process per GPU, buffers in symmetric memory).
+//
+//   reduce_scatter : each rank sums ITS slice of the flat fp32 gradient buffer
+//                    over all ranks, reading the peers' buffers directly
+//                    (multimem.ld_reduce through the NVSwitch when a multicast
+//                    mapping is given, else one P2P load per peer), and emits
+//                    per-block sum-of-squares partials for the global grad norm.
+//   adamw_gather   : clipped AdamW on the rank's slice (fp32 master, exp_avg,
+//                    exp_avg_sq) whose bf16 result is stored straight into every
+//                    rank's parameter replica (multimem.st or P2P stores), i.e.
+//                    the all-gather rides on the optimizer's store.
+//   peer_barrier   : flag exchange; also fused as the prologue of reduce_scatter.
+//
+// Flags live in a symmetric int32 array: slot r of rank d is written only by
+// rank r (st.release.sys) and polled only by rank d (ld.acquire.sys). Waits are
+// bounded (2 s); on a timeout the kernel records a status code, skips its
+// remote accesses and returns.
+#include "common.cuh"
+
+namespace tlm {
+
+constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Threads 0..n-1 of the calling block: (optionally) publish `epoch` to every
+// peer, then wait until every peer has published it here. Returns false on timeout.
+__device__ __forceinline__ bool flag_exchange(const PeerPtrs& flags, int rank, int n, int epoch, bool do_signal,
+                                              unsigned int* status, unsigned int site) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    const int r = threadIdx.x;
+    if (do_signal) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<int*>(flags.p[r]) + rank, epoch);
+    }
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + r;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        report_status(status, (site << 8) | (unsigned int)r);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int n, int epoch, unsigned int* status) {
+  flag_exchange(flags, rank, n, epoch, true, status, 40);
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b32x4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// out[i] = sum_r grads[r][lo + i],  i in [0, len).  partials[blockIdx.x] = sum out[i]^2 over the block's share.
+// Prologue: every block waits until all ranks have published `epoch` (their
+// backward pass, which precedes this kernel in stream order, is complete).
+__global__ void reduce_scatter_kernel(PeerPtrs grads, const float* mc_grads, PeerPtrs flags, float* __restrict__ out,
+                                      float* __restrict__ partials, long long lo, long long len, int rank, int n,
+                                      int epoch, unsigned int* status) {
+  __shared__ float red[32];
+  const bool ok = flag_exchange(flags, rank, n, epoch, blockIdx.x == 0, status, 41);
+  float acc = 0.f;
+  if (ok) {
+    const long long nvec = len / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+      float4 s;
+      if (mc_grads != nullptr) {
+        s = multimem_ld_reduce_f32x4(mc_grads + lo + i * 4);
+      } else {
+        s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < n; ++r) {
+          const int src = (rank + r) % n;                      // start at self, spread the peers
+          const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[src]) + lo + i * 4);
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+      }
+      reinterpret_cast<float4*>(out)[i] = s;
+      acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) partials[blockIdx.x] = v;
+  }
+}
+
+__global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out) {
+  __shared__ double red[32];
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)partials[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+    out[0] = (float)t;
+  }
+}
+
+// AdamW on [0, len) of the shard; bf16 result goes to element lo + i of every rank's replica.
+__global__ void adamw_gather_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                    const float* __restrict__ g, PeerPtrs params, __nv_bfloat16* mc_params,
+                                    const float* __restrict__ scale_ptr, long long lo, long long len, int rank, int n,
+                                    float lr, float beta1, float beta2, float eps, float wd, float inv_bc1,
+                                    float inv_sqrt_bc2) {
+  const float scale = *scale_ptr;
+  const long long nvec = len / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float pa[8], ma[8], va[8], ga[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float4 a = reinterpret_cast<float4*>(p)[2 * i + h], b = reinterpret_cast<float4*>(m)[2 * i + h];
+      const float4 c = reinterpret_cast<float4*>(v)[2 * i + h], d = reinterpret_cast<const float4*>(g)[2 * i + h];
+      pa[4 * h] = a.x; pa[4 * h + 1] = a.y; pa[4 * h + 2] = a.z; pa[4 * h + 3] = a.w;
+      ma[4 * h] = b.x; ma[4 * h + 1] = b.y; ma[4 * h + 2] = b.z; ma[4 * h + 3] = b.w;
+      va[4 * h] = c.x; va[4 * h + 1] = c.y; va[4 * h + 2] = c.z; va[4 * h + 3] = c.w;
+      ga[4 * h] = d.x; ga[4 * h + 1] = d.y; ga[4 * h + 2] = d.z; ga[4 * h + 3] = d.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gr = ga[k] * scale;
+      float x = pa[k] * (1.f - lr * wd);
+      ma[k] = beta1 * ma[k] + (1.f - beta1) * gr;
+      va[k] = beta2 * va[k] + (1.f - beta2) * gr * gr;
+      x -= lr * inv_bc1 * ma[k] / (sqrtf(va[k]) * inv_sqrt_bc2 + eps);
+      pa[k] = x;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      reinterpret_cast<float4*>(p)[2 * i + h] = make_float4(pa[4 * h], pa[4 * h + 1], pa[4 * h + 2], pa[4 * h + 3]);
+      reinterpret_cast<float4*>(m)[2 * i + h] = make_float4(ma[4 * h], ma[4 * h + 1], ma[4 * h + 2], ma[4 * h + 3]);
+      reinterpret_cast<float4*>(v)[2 * i + h] = make_float4(va[4 * h], va[4 * h + 1], va[4 * h + 2], va[4 * h + 3]);
+    }
+    const uint4 packed = make_uint4(pack_bf16(pa[0], pa[1]), pack_bf16(pa[2], pa[3]), pack_bf16(pa[4], pa[5]), pack_bf16(pa[6], pa[7]));
+    if (mc_params != nullptr) {
+      multimem_st_b32x4(mc_params + lo + i * 8, packed);
+    } else {
+      for (int r = 0; r < n; ++r) {
+        const int dst = (rank + r) % n;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + lo + i * 8) = packed;
+      }
+    }
+  }
+}
+
+}  // namespace tlm
+
+using namespace tlm;
+
+static PeerPtrs to_ptrs(void* const* src, int n) {
+  PeerPtrs out{};
+  for (int i = 0; i < n && i < MAX_PEERS; ++i) out.p[i] = src[i];
+  return out;
+}
+
+TLM_API int tlm_peer_barrier(void* const* flag_ptrs, int rank, int n, int epoch, cudaStream_t st) {
+  if (n > MAX_PEERS) return -6;
+  peer_barrier_kernel<<<1, 32, 0, st>>>(to_ptrs(flag_ptrs, n), rank, n, epoch, status_word());
+  count_launch();
+  return launch_status();
+}
+
+TLM_API int tlm_reduce_scatter_blocks() { return 4 * num_sms(); }
+
+// partials: >= tlm_reduce_scatter_blocks() floats; sumsq_out: 1 float.
+TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, void* const* flag_ptrs, float* out,
+                               float* partials, float* sumsq_out, long long lo, long long len, int rank, int n,
+                               int epoch, cudaStream_t st) {
+  if (n > MAX_PEERS || len % 4 != 0 || lo % 4 != 0) return -6;
+  const int blocks = tlm_reduce_scatter_blocks();
+  reduce_scatter_kernel<<<blocks, 512, 0, st>>>(to_ptrs(grad_ptrs, n), mc_grads, to_ptrs(flag_ptrs, n), out, partials, lo,
+                                                len, rank, n, epoch, status_word());
+  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out);
+  count_launch(2);
+  return launch_status();
+}
+
+TLM_API int tlm_adamw_gather(float* p, float* m, float* v, const float* g, void* const* param_ptrs, void* mc_params,
+                             const float* scale, long long lo, long long len, int rank, int n, float lr, float beta1,
+                             float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2, cudaStream_t st) {
+  if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0) return -6;
+  long long blocks = (len / 8 + 255) / 256;
+  if (blocks > 8LL * num_sms()) blocks = 8LL * num_sms();
+  if (blocks < 1) blocks = 1;
+  adamw_gather_kernel<<<(int)blocks, 256, 0, st>>>(p, m, v, g, to_ptrs(param_ptrs, n), (__nv_bfloat16*)mc_params, scale, lo,
+                                                   len, rank, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2);
+  count_launch();
+  return launch_status();
+}

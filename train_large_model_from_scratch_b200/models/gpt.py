@@ -57,7 +57,7 @@ class Block(nn.Module):
 
 class GPT(nn.Module):
     def __init__(self, config: ModelConfig, device=None, compute_dtype: torch.dtype | None = None,
-                 flatten: bool = True, shard_world: int = 1):
+                 flatten: bool = True, shard_world: int = 1, alloc=None):
         super().__init__()
         self.config = config
         self.device = torch.device(device) if device is not None else _default_device()
@@ -83,7 +83,7 @@ class GPT(nn.Module):
         self.dense_buf = self.expert_buf = None
         if flatten:
             pad = 1024 * max(1, shard_world)
-            self.dense_buf, self.expert_buf = flatten_model(self, compute_dtype, dev, pad, pad)
+            self.dense_buf, self.expert_buf = flatten_model(self, compute_dtype, dev, pad, pad, alloc)
 
     # ------------------------------------------------------------------ forward
     def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None, loss_scale: float = 1.0,

@@ -43,7 +43,7 @@ class FlatBuffer:
     and the name -> (offset, numel, shape) table."""
 
     def __init__(self, named_params: list[tuple[str, torch.nn.Parameter]], compute_dtype: torch.dtype,
-                 device: torch.device, pad_to: int = 1):
+                 device: torch.device, pad_to: int = 1, alloc=None):
         self.layout: "OrderedDict[str, tuple[int, int, torch.Size]]" = OrderedDict()
         off = 0
         seen: dict[int, str] = {}
@@ -60,8 +60,12 @@ class FlatBuffer:
         pad_to = max(1, pad_to)
         self.padded = ((off + pad_to - 1) // pad_to) * pad_to if off else 0
         self.compute_dtype = compute_dtype
-        self.params = torch.zeros(self.padded, dtype=compute_dtype, device=device)
-        self.main_grad = torch.zeros(self.padded, dtype=torch.float32, device=device)
+        # `alloc(numel, dtype, device)` lets the caller place both buffers in symmetric
+        # (peer-addressable) memory; it must return zero-filled storage.
+        if alloc is None:
+            alloc = lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev)
+        self.params = alloc(self.padded, compute_dtype, device)
+        self.main_grad = alloc(self.padded, torch.float32, device)
         self.init_fp32: torch.Tensor | None = torch.zeros(self.padded, dtype=torch.float32, device=device)
         for name, p in named_params:
             if name not in self.layout:
@@ -111,13 +115,13 @@ def fuse_adjacent(params: list[torch.nn.Parameter]) -> torch.Tensor:
 
 
 def flatten_model(model: torch.nn.Module, compute_dtype: torch.dtype, device: torch.device,
-                  dense_pad: int = 1, expert_pad: int = 1) -> tuple[FlatBuffer, FlatBuffer | None]:
+                  dense_pad: int = 1, expert_pad: int = 1, alloc=None) -> tuple[FlatBuffer, FlatBuffer | None]:
     """Move every parameter of `model` into flat storage. Returns (dense, expert)."""
     dense, expert = [], []
     for name, p in model.named_parameters():
         (expert if is_expert_param(name) else dense).append((name, p))
-    dense_buf = FlatBuffer(dense, compute_dtype, device, dense_pad)
-    expert_buf = FlatBuffer(expert, compute_dtype, device, expert_pad) if expert else None
+    dense_buf = FlatBuffer(dense, compute_dtype, device, dense_pad, alloc)
+    expert_buf = FlatBuffer(expert, compute_dtype, device, expert_pad, alloc) if expert else None
     for m in model.modules():
         hook = getattr(m, "_post_flatten", None)
         if hook is not None:

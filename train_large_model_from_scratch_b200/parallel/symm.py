@@ -1,0 +1,123 @@
+"""Peer-memory collectives for the optimizer step (CUDA, world > 1).
+
+The flat parameter and gradient buffers are allocated in symmetric memory
+(`torch.distributed._symmetric_memory`: same size on every rank, every rank
+can address every peer's copy over NVLink, plus an NVSwitch multicast address
+when the fabric supports it). The kernels in `csrc/collectives.cu` then do the
+communication themselves:
+
+  reduce-scatter   each rank reads its 1/n slice of every peer's fp32 gradient
+                   buffer (`multimem.ld_reduce` or P2P loads) -> fp32 shard,
+                   with the sum of squares for the global norm;
+  AdamW + gather   the optimizer kernel stores the updated bf16 parameters into
+                   every rank's replica (`multimem.st` or P2P stores);
+  barriers         symmetric flag arrays with bounded waits.
+
+`torch.distributed` (NCCL) stays for the control plane: rendezvous, the scalar
+norm / loss reductions, checkpoint traffic. Set `TLM_COMM=nccl` to run the
+optimizer collectives through NCCL instead (the baseline for comparisons), and
+`TLM_NVLS=0` to keep the kernels on plain peer loads / stores.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+
+def symm_alloc(numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    import torch.distributed._symmetric_memory as symm_mem
+    t = symm_mem.empty(numel, dtype=dtype, device=device)
+    t.zero_()
+    return t
+
+
+def use_symm() -> bool:
+    return (torch.cuda.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+            and os.environ.get("TLM_COMM", "symm") == "symm")
+
+
+class _Peer:
+    """Rendezvous result for one symmetric tensor."""
+
+    def __init__(self, tensor: torch.Tensor, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.handle = symm_mem.rendezvous(tensor, group=group)
+        self.n = self.handle.world_size
+        self.rank = self.handle.rank
+        ptrs = list(self.handle.buffer_ptrs)
+        self.ptr_array = (ctypes.c_void_p * self.n)(*ptrs)
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_ptr = mc if os.environ.get("TLM_NVLS", "1") != "0" else 0
+
+
+class PeerCollectives:
+    def __init__(self):
+        self.state = {}          # id(shard) -> dict
+
+    @classmethod
+    def create(cls, fused, wire_dtype: str = "fp32") -> "PeerCollectives":
+        self = cls()
+        for s in fused.shards:
+            if s.n == 1 or not s.sharded:
+                continue
+            dev = s.buf.params.device
+            flags = symm_alloc(64, torch.int32, dev)
+            st = {
+                "grad": _Peer(s.buf.main_grad, s.group),
+                "param": _Peer(s.buf.params, s.group),
+                "flags": _Peer(flags, s.group),
+                "flags_t": flags,
+                "epoch": 0,
+                "partials": torch.zeros(native.lib().tlm_reduce_scatter_blocks(), dtype=torch.float32, device=dev),
+                "sumsq": torch.zeros((), dtype=torch.float32, device=dev),
+            }
+            self.state[id(s)] = st
+            dist.barrier(group=s.group)
+        torch.cuda.synchronize()
+        return self
+
+    def handles(self, s) -> bool:
+        return id(s) in self.state
+
+    def barrier(self, s) -> None:
+        st = self.state[id(s)]
+        st["epoch"] += 1
+        f = st["flags"]
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, st["epoch"], native._stream()),
+                      "peer_barrier")
+
+    def reduce_grads(self, s) -> torch.Tensor:
+        """Sum of every rank's gradient slice -> `s.grad_shard`; also leaves the
+        slice's sum of squares in `self.last_sumsq(s)`."""
+        st = self.state[id(s)]
+        st["epoch"] += 1
+        g, f = st["grad"], st["flags"]
+        native._check(native.lib().tlm_reduce_scatter(
+            g.ptr_array, ctypes.c_void_p(g.mc_ptr) if g.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
+            st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, st["epoch"],
+            native._stream()), "reduce_scatter")
+        return s.grad_shard
+
+    def last_sumsq(self, s) -> torch.Tensor:
+        return self.state[id(s)]["sumsq"]
+
+    def update_and_gather(self, s, grad, scale, step: int, g: dict) -> None:
+        st = self.state[id(s)]
+        b1, b2 = g["betas"]
+        pr = st["param"]
+        native._check(native.lib().tlm_adamw_gather(
+            s.master.data_ptr(), s.exp_avg.data_ptr(), s.exp_avg_sq.data_ptr(), grad.data_ptr(), pr.ptr_array,
+            ctypes.c_void_p(pr.mc_ptr) if pr.mc_ptr else None, scale.data_ptr(), s.lo, s.len, pr.rank, pr.n,
+            g["lr"], b1, b2, g["eps"], g["weight_decay"], 1.0 / (1.0 - b1 ** step),
+            1.0 / math.sqrt(1.0 - b2 ** step), native._stream()), "adamw_gather")
+        self.barrier(s)          # every replica complete before anyone's next forward reads it
+
+    def gather_params(self, s) -> None:
+        """Parameters were already distributed by `update_and_gather`."""
+        return None

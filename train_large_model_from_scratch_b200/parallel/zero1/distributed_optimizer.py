@@ -123,7 +123,10 @@ class FusedAdamW:
         norm_sq = None
         for s in self.shards:
             grad = self._reduce(s)
-            part = self._sumsq(grad if s.sharded else s.buf.main_grad[s.norm_lo:s.norm_hi])
+            if self._comm is not None and self._comm.handles(s):
+                part = self._comm.last_sumsq(s)          # produced by the reduce-scatter kernel
+            else:
+                part = self._sumsq(grad if s.sharded else s.buf.main_grad[s.norm_lo:s.norm_hi])
             norm_sq = part if norm_sq is None else norm_sq + part
         norm_sq = norm_sq * (inv * inv)
         if self.norm_group is not None and dist.get_world_size(self.norm_group) > 1:
@@ -145,7 +148,7 @@ class FusedAdamW:
         mg = s.buf.main_grad
         if s.n == 1:
             return mg
-        if self._comm is not None:
+        if self._comm is not None and self._comm.handles(s):
             return self._comm.reduce_grads(s)
         if s.sharded:
             if mg.is_cuda:
@@ -166,7 +169,9 @@ class FusedAdamW:
     def _update(self, s: _Shard, grad: torch.Tensor, scale: torch.Tensor, g: dict) -> None:
         b1, b2 = g["betas"]
         out = s.buf.params[s.lo:s.hi]
-        if grad.is_cuda:
+        if self._comm is not None and self._comm.handles(s):
+            self._comm.update_and_gather(s, grad, scale, self.step_count, g)
+        elif grad.is_cuda:
             native.adamw_step(s.master, s.exp_avg, s.exp_avg_sq, grad, out, scale, self.step_count,
                               g["lr"], b1, b2, g["eps"], g["weight_decay"])
         else:
@@ -174,10 +179,10 @@ class FusedAdamW:
                               g["eps"], g["weight_decay"], grad_scale=float(scale))
             out.copy_(s.master.to(out.dtype))
 
-    def _gather(self, s: _Shard) -> None:
+    def _gather(self, s: _Shard, via_library: bool = False) -> None:
         if not s.sharded:
             return
-        if self._comm is not None:
+        if not via_library and self._comm is not None and self._comm.handles(s):
             return self._comm.gather_params(s)
         p = s.buf.params
         if p.is_cuda:
@@ -204,7 +209,7 @@ class FusedAdamW:
         """Rewrite the compute-dtype parameters from the fp32 master shards."""
         for s in self.shards:
             s.buf.params[s.lo:s.hi].copy_(s.master.to(s.buf.params.dtype))
-            self._gather(s)
+            self._gather(s, via_library=True)
 
 
 class DistributedOptimizer:

@@ -157,9 +157,11 @@ class Trainer:
         self.model_config = config.model
         if self.master_process:
             print(f"Params config: {get_model_params(self.model_config)}")
-        self.model = GPT(self.model_config, device=self.device,
-                         compute_dtype=self._compute_dtype(config.train.precision),
-                         shard_world=self.dp_sp_world_size)
+        from ..parallel import symm
+        dtype = self._compute_dtype(config.train.precision)
+        self._symm = symm.use_symm() and dtype == torch.bfloat16 and config.parallel.use_distributed_optimizer
+        self.model = GPT(self.model_config, device=self.device, compute_dtype=dtype,
+                         shard_world=self.dp_sp_world_size, alloc=symm.symm_alloc if self._symm else None)
         self.raw_model = self.model
 
     def _init_optimizer(self, config: Config) -> None:
@@ -173,7 +175,7 @@ class Trainer:
         fused = FusedAdamW(buffers, lr=o.max_lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
                            weight_decay=o.weight_decay, groups=groups, grad_divisor=self.dp_world_size,
                            sharded=zero1, norm_group=self.dp_sp_group)
-        if self.use_cuda and self.world_size > 1 and os.environ.get("TLM_COMM", "symm") == "symm":
+        if getattr(self, "_symm", False):
             from ..parallel.symm import PeerCollectives
             fused._comm = PeerCollectives.create(fused, wire_dtype=config.parallel.grad_wire_dtype)
         if zero1:
