@@ -8,13 +8,18 @@
 namespace tlm {
 
 // ------------------------------------------------------------------ embedding
+// Token ids outside [0, V) are not dereferenced: the row is zero-filled (forward) or
+// skipped (backward) and a status code is recorded for the host.
 __global__ void embedding_fwd_kernel(const long long* __restrict__ idx, const __nv_bfloat16* __restrict__ w,
-                                     float* __restrict__ out, int rows, int D) {
+                                     float* __restrict__ out, int rows, int D, long long V, unsigned int* status) {
   const int vec_per_row = D / 8;
   const long long total = (long long)rows * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 8;
-    const uint4 v = *reinterpret_cast<const uint4*>(w + idx[r] * (long long)D + c);
+    const long long tok = idx[r];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if ((unsigned long long)tok < (unsigned long long)V) v = *reinterpret_cast<const uint4*>(w + tok * (long long)D + c);
+    else if (c == 0) report_status(status, (50u << 8) | 1u);
     const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), d = unpack_bf16(v.w);
     float4* o = reinterpret_cast<float4*>(out + (long long)r * D + c);
     o[0] = make_float4(a.x, a.y, b.x, b.y);
@@ -23,13 +28,15 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ idx, const __
 }
 
 __global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const float* __restrict__ dx,
-                                     float* __restrict__ grad, int rows, int D) {
+                                     float* __restrict__ grad, int rows, int D, long long V) {
   const int vec_per_row = D / 4;
   const long long total = (long long)rows * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 4;
+    const long long tok = idx[r];
+    if ((unsigned long long)tok >= (unsigned long long)V) continue;
     const float4 v = *reinterpret_cast<const float4*>(dx + (long long)r * D + c);
-    atomicAdd(reinterpret_cast<float4*>(grad + idx[r] * (long long)D + c), v);
+    atomicAdd(reinterpret_cast<float4*>(grad + tok * (long long)D + c), v);
   }
 }
 
@@ -246,7 +253,7 @@ __global__ void ce_inplace_kernel(__nv_bfloat16* __restrict__ logits, const long
   __nv_bfloat16* row = logits + (long long)r * ld;
   const long long tgt = targets[r];
   const int nvec = V / 8, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (tgt == ignore_index) {
+  if (tgt == ignore_index || (unsigned long long)tgt >= (unsigned long long)V) {   // never index outside the row
     if (write_grad) for (int v = threadIdx.x; v < nvec; v += blockDim.x) *reinterpret_cast<uint4*>(row + v * 8) = make_uint4(0, 0, 0, 0);
     return;
   }
@@ -376,14 +383,17 @@ static inline int grid_for(long long work_items, int threads, int max_blocks_per
 
 using namespace tlm;
 
-TLM_API int tlm_embedding_fwd(const long long* idx, const void* w, float* out, int rows, int D, cudaStream_t st) {
-  embedding_fwd_kernel<<<grid_for((long long)rows * D / 8, 256), 256, 0, st>>>(idx, (const __nv_bfloat16*)w, out, rows, D);
+TLM_API int tlm_embedding_fwd(const long long* idx, const void* w, float* out, int rows, int D, long long V,
+                              cudaStream_t st) {
+  embedding_fwd_kernel<<<grid_for((long long)rows * D / 8, 256), 256, 0, st>>>(idx, (const __nv_bfloat16*)w, out, rows, D, V,
+                                                                              status_word());
   count_launch();
   return launch_status();
 }
 
-TLM_API int tlm_embedding_bwd(const long long* idx, const float* dx, float* grad, int rows, int D, cudaStream_t st) {
-  embedding_bwd_kernel<<<grid_for((long long)rows * D / 4, 256), 256, 0, st>>>(idx, dx, grad, rows, D);
+TLM_API int tlm_embedding_bwd(const long long* idx, const float* dx, float* grad, int rows, int D, long long V,
+                              cudaStream_t st) {
+  embedding_bwd_kernel<<<grid_for((long long)rows * D / 4, 256), 256, 0, st>>>(idx, dx, grad, rows, D, V);
   count_launch();
   return launch_status();
 }

@@ -51,8 +51,8 @@ _SIGS = {
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
-    "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _P]),
-    "tlm_embedding_bwd": (_I, [_P, _P, _P, _I, _I, _P]),
+    "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
+    "tlm_embedding_bwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
     "tlm_add_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "tlm_add_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "tlm_rope": (_I, [_P, _P, _P, _LL, _I, _I, _I, _I, _I, _P]),
@@ -168,14 +168,14 @@ def embedding_fwd(idx: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     idx = idx.reshape(-1).contiguous()
     rows, D = idx.numel(), weight.shape[1]
     out = torch.empty(rows, D, dtype=torch.float32, device=weight.device)
-    _check(lib().tlm_embedding_fwd(idx.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, D, _stream()), "embedding_fwd")
+    _check(lib().tlm_embedding_fwd(idx.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, D, weight.shape[0], _stream()), "embedding_fwd")
     return out
 
 
 def embedding_bwd(idx: torch.Tensor, dx: torch.Tensor, main_grad: torch.Tensor) -> None:
     idx = idx.reshape(-1).contiguous()
     rows, D = dx.shape
-    _check(lib().tlm_embedding_bwd(idx.data_ptr(), dx.data_ptr(), main_grad.data_ptr(), rows, D, _stream()), "embedding_bwd")
+    _check(lib().tlm_embedding_bwd(idx.data_ptr(), dx.data_ptr(), main_grad.data_ptr(), rows, D, main_grad.shape[0], _stream()), "embedding_bwd")
 
 
 def add_rmsnorm_fwd(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, eps: float):

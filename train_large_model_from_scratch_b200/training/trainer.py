@@ -125,8 +125,10 @@ class Trainer:
     def _init_dataset(self, config: Config) -> None:
         d, t = config.data, config.train
         if d.use_mock_data:
-            self.train_dataset = MockDataset(d.mock_data_num_samples, t.seq_len, base_seed=config.seed.seed)
-            self.val_dataset = (MockDataset(d.mock_data_num_samples // 10, t.seq_len, base_seed=config.seed.seed,
+            self.train_dataset = MockDataset(d.mock_data_num_samples, t.seq_len, vocab_size=config.model.vocab_size,
+                                             base_seed=config.seed.seed)
+            self.val_dataset = (MockDataset(d.mock_data_num_samples // 10, t.seq_len,
+                                            vocab_size=config.model.vocab_size, base_seed=config.seed.seed,
                                             seed_offset=1_000_000_000) if t.do_val else None)
         else:
             raise NotImplementedError(
