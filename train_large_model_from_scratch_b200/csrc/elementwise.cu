@@ -486,3 +486,42 @@ TLM_API int tlm_adamw(float* p, float* m, float* v, const float* g, void* p_out,
   count_launch();
   return launch_status();
 }
+
+// ------------------------------------------------------------------ sum of squares without any allocation
+#include "tlm_noalloc.h"
+
+// Partial sums of tlm_sumsq_noalloc: one float per block, fixed size, part of the device image.
+static __device__ __align__(256) float g_sumsq_noalloc_scratch[tlm::SUMSQ_BLOCKS];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address, so the address is looked up once per device and cached here.
+static float* g_sumsq_noalloc_ptr[64] = {nullptr};
+
+TLM_API const char* tlm_noalloc_error_string(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case TLM_NOALLOC_ERR_TOO_LARGE: return "tlm_sumsq_noalloc: n is negative or exceeds TLM_SUMSQ_NOALLOC_MAX_N (2^31 elements)";
+    case TLM_NOALLOC_ERR_SYMBOL: return "tlm_sumsq_noalloc: could not resolve the device address of the built-in scratch array";
+    case TLM_NOALLOC_ERR_ARGUMENT: return "tlm_sumsq_noalloc: null pointer or x not 16-byte aligned";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "tlm_sumsq_noalloc: unknown error";
+  }
+}
+
+TLM_API int tlm_sumsq_noalloc(const float* x, long long n, float* out, cudaStream_t st) {
+  if (n < 0 || n > TLM_SUMSQ_NOALLOC_MAX_N) return TLM_NOALLOC_ERR_TOO_LARGE;
+  if (x == nullptr || out == nullptr || (reinterpret_cast<uintptr_t>(x) & 15u)) return TLM_NOALLOC_ERR_ARGUMENT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TLM_NOALLOC_ERR_SYMBOL;
+  if (g_sumsq_noalloc_ptr[dev] == nullptr) {             // set-up, once per device, with that device current
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_sumsq_noalloc_scratch) != cudaSuccess || p == nullptr) return TLM_NOALLOC_ERR_SYMBOL;
+    g_sumsq_noalloc_ptr[dev] = p;
+  }
+  float* scratch = g_sumsq_noalloc_ptr[dev];
+  int blocks = grid_for(n / 4 + 1, SUMSQ_THREADS, 4);
+  if (blocks > SUMSQ_BLOCKS) blocks = SUMSQ_BLOCKS;
+  sumsq_partial_kernel<<<blocks, SUMSQ_THREADS, 0, st>>>(x, n, scratch);
+  sumsq_final_kernel<<<1, 256, 0, st>>>(scratch, blocks, out);
+  count_launch(2);
+  return launch_status();
+}
