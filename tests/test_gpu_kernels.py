@@ -181,3 +181,22 @@ def test_adamw_matches_torch(nat):
         nat.adamw_step(p, m, v, g, out, scale, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
     torch.testing.assert_close(p, ref.detach(), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(out, p.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("counts,N,K", [([130, 0, 64, 257], 512, 256), ([5, 300, 1, 90], 264, 72), ([0, 0, 128], 256, 64)])
+def test_grouped_gemms(nat, counts, N, K):
+    R, E = sum(counts), len(counts)
+    x, w = _rand(R, K, seed=20), _rand(E, N, K, seed=21)
+    dy = _rand(R, N, seed=22)
+    y = nat.grouped_gemm_nt(x, w, counts)
+    dx = nat.grouped_gemm_nn(dy, w, counts)
+    acc = torch.ones(E, N, K, device="cuda")
+    nat.grouped_gemm_tn_accum(dy, x, acc, counts)
+    r = 0
+    for e, c in enumerate(counts):
+        if c:
+            assert _rel_err(y[r:r + c], x[r:r + c].float() @ w[e].float().t()) < 6e-3, ("nt", e)
+            assert _rel_err(dx[r:r + c], dy[r:r + c].float() @ w[e].float()) < 6e-3, ("nn", e)
+        ref = 1.0 + dy[r:r + c].float().t() @ x[r:r + c].float()
+        assert _rel_err(acc[e], ref) < 1e-4, ("tn", e)
+        r += c

@@ -57,3 +57,23 @@ def test_training_reduces_loss_on_fixed_batch():
 def test_smoke_entry():
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+def test_moe_model_matches_cpu_oracle():
+    from train_large_model_from_scratch_b200.ops import native
+    kw = dict(use_moe=True, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=256)
+    gpu = _build("cuda", torch.bfloat16, **kw)
+    cpu = _build("cpu", torch.float32, **kw)
+    cpu.dense_buf.params.copy_(gpu.dense_buf.params.float().cpu())
+    cpu.expert_buf.params.copy_(gpu.expert_buf.params.float().cpu())
+    data = torch.randint(0, 4096, (2, 257), generator=torch.Generator().manual_seed(3))
+    x, y = data[:, :-1].contiguous(), data[:, 1:].contiguous()
+    _, lg, _ = gpu(x.cuda(), y.cuda())
+    lg.backward()
+    _, lc, _ = cpu(x, y)
+    lc.backward()
+    native.raise_on_device_status()
+    assert abs(lg.item() - lc.item()) < 3e-2, (lg.item(), lc.item())
+    for a, b in ((gpu.dense_buf, cpu.dense_buf), (gpu.expert_buf, cpu.expert_buf)):
+        cos = torch.nn.functional.cosine_similarity(a.main_grad.cpu(), b.main_grad, dim=0).item()
+        assert cos > 0.98, cos

@@ -163,22 +163,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-      int stage = 0; uint32_t phase = 0;
-      int acc = 0; uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        TileCoord t = get_tile(tile);
-        if (!t.valid) continue;
-        if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, 2, abort_flag, p.status)) { ok = false; break; }
+    // The whole warp walks the loop (so it can clean a ragged reduction tail in
+    // shared memory); lane 0 alone issues the MMAs and commits.
+    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    int stage = 0; uint32_t phase = 0;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      TileCoord t = get_tile(tile);
+      if (!t.valid) continue;
+      if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, 2, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+      uint32_t accumulate = 0;
+      for (int k0 = t.k_lo; k0 < t.k_hi; k0 += BK) {
+        if (!mbar_wait(full_bar(stage), phase, 3, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        uint32_t accumulate = 0;
-        for (int k0 = t.k_lo; k0 < t.k_hi; k0 += BK) {
-          if (!mbar_wait(full_bar(stage), phase, 3, abort_flag, p.status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+        const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+        if (A_MN && p.group_mode == 2 && t.k_hi - k0 < BK) {
+          // grouped reduction: rows past this group's end belong to the next group.
+          // Zero them in the A tile (each k index is one 128-byte row per 64-wide box,
+          // so whole-row zeroing is independent of the swizzle).
+          const int valid = t.k_hi - k0;
+          uint8_t* a_ptr = smem_al + stage * STAGE_BYTES;
+          const int n16 = (BK - valid) * 8;                      // 16-byte pieces per box
+          for (int box = 0; box < BM / 64; ++box)
+            for (int i = lane; i < n16; i += 32)
+              *reinterpret_cast<uint4*>(a_ptr + box * BOX_MN_BYTES + valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) {
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // K-major: 16 bf16 = 32 B further along the 128 B row;
@@ -191,12 +206,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             accumulate = 1;
           }
           umma_commit(empty_bar(stage));          // stage reusable once these MMAs retire
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit(accf_bar(acc));               // accumulator complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      if (!ok) break;
+      if (lane == 0) umma_commit(accf_bar(acc));  // accumulator complete
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)

@@ -123,8 +123,22 @@ def _rows(t: torch.Tensor) -> tuple[int, int, int]:
     return t.shape[0], t.shape[1], t.stride(0)
 
 
+def _pad8(t: torch.Tensor, dim: int) -> torch.Tensor:
+    """Zero-pad `dim` to a multiple of 8 elements (TMA needs 16-byte row pitches).
+    Only tiny operands ever need it (e.g. a router with a number of experts that
+    is not a multiple of 8)."""
+    n = t.shape[dim]
+    if n % 8 == 0:
+        return t
+    pad = list(t.shape)
+    pad[dim] = 8 - n % 8
+    return torch.cat([t, t.new_zeros(pad)], dim=dim)
+
+
 def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T (bf16)."""
+    if w.shape[0] % 8 and out is None:
+        return gemm_nt(x, _pad8(w, 0))[:, :w.shape[0]].contiguous()
     M, K, lda = _rows(x)
     N, K2, ldb = _rows(w)
     assert K == K2
@@ -138,6 +152,8 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -
 def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """out[M,K] = dy[M,N] @ w[N,K] (bf16): the data-gradient GEMM. `w` is read in
     place as an MN-major operand, no transpose is materialised."""
+    if dy.shape[1] % 8:
+        dy, w = _pad8(dy, 1), _pad8(w, 0)
     M, N, lda = _rows(dy)
     N2, K, ldb = _rows(w)
     assert N == N2
@@ -151,9 +167,12 @@ def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor) -> None:
     """acc[N,K] (fp32) += dy[M,N]^T @ x[M,K]: the weight-gradient GEMM, both
     operands MN-major, accumulated into the fp32 gradient buffer."""
+    if dy.shape[1] % 8:                      # output rows beyond acc.shape[0] are masked by the kernel (M = N rows)
+        dy = _pad8(dy, 1)
     M, N, lda = _rows(dy)
     M2, K, ldb = _rows(x)
-    assert M == M2 and acc.dtype == torch.float32 and acc.shape == (N, K)
+    N = acc.shape[0]
+    assert M == M2 and acc.dtype == torch.float32 and acc.shape[1] == K
     _check(lib().tlm_gemm(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), N, K, M, lda, ldb, acc.stride(0),
                           1, 1, EPI_F32_ACC, _stream()), "gemm_tn_accum")
 
@@ -269,3 +288,55 @@ def flash_attn_fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
 def flash_attn_bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
     from . import attention_cuda
     return attention_cuda.bwd(do, qkv, o, lse, n_q, n_kv, causal)
+
+
+# --------------------------------------------------------------------------- grouped GEMMs (MoE experts)
+def _row_start(counts, device) -> torch.Tensor:
+    acc, out = 0, [0]
+    for c in counts:
+        acc += int(c)
+        out.append(acc)
+    return torch.tensor(out, dtype=torch.int32, device=device)
+
+
+def grouped_gemm_nt(x: torch.Tensor, weight: torch.Tensor, counts) -> torch.Tensor:
+    """rows of `x [R,K]` grouped by expert (`counts`); out[rows_e] = x[rows_e] @ weight[e]^T, weight `[E,N,K]`."""
+    R, K, lda = _rows(x)
+    E, N, K2 = weight.shape
+    assert K == K2 and weight.is_contiguous()
+    out = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
+    if R == 0:
+        return out
+    rs = _row_start(counts, x.device)
+    _check(lib().tlm_gemm_grouped_rows(x.data_ptr(), weight.data_ptr(), out.data_ptr(), rs.data_ptr(), E, R, N, K,
+                                       lda, K, N * K, N, 0, EPI_BF16, max(int(c) for c in counts), _stream()),
+           "grouped_gemm_nt")
+    return out
+
+
+def grouped_gemm_nn(dy: torch.Tensor, weight: torch.Tensor, counts) -> torch.Tensor:
+    """dx[rows_e] = dy[rows_e] @ weight[e]  (dy `[R,N]`, weight `[E,N,K]` -> `[R,K]`)."""
+    R, N, lda = _rows(dy)
+    E, N2, K = weight.shape
+    assert N == N2 and weight.is_contiguous()
+    out = torch.empty(R, K, dtype=torch.bfloat16, device=dy.device)
+    if R == 0:
+        return out
+    rs = _row_start(counts, dy.device)
+    _check(lib().tlm_gemm_grouped_rows(dy.data_ptr(), weight.data_ptr(), out.data_ptr(), rs.data_ptr(), E, R, K, N,
+                                       lda, K, N * K, K, 1, EPI_BF16, max(int(c) for c in counts), _stream()),
+           "grouped_gemm_nn")
+    return out
+
+
+def grouped_gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor, counts) -> None:
+    """acc[e] (`[E,N,K]` fp32) += dy[rows_e]^T @ x[rows_e]."""
+    R, N, lda = _rows(dy)
+    R2, K, ldb = _rows(x)
+    E = acc.shape[0]
+    assert R == R2 and acc.shape == (E, N, K) and acc.dtype == torch.float32 and acc.is_contiguous()
+    if R == 0:
+        return
+    rs = _row_start(counts, dy.device)
+    _check(lib().tlm_gemm_grouped_k(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), rs.data_ptr(), E, R, N, K, lda, ldb,
+                                    K, N * K, EPI_F32_ACC, _stream()), "grouped_gemm_tn_accum")
