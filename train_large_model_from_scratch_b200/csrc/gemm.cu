@@ -32,7 +32,9 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int BOX_MN_BYTES = 64 * BK * 2;            // one 64(mn) x 64(k) MN-major box = 8 KB
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 bf16 staging tile
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
 
@@ -48,6 +50,10 @@ struct GemmParams {
   int group_mode;           // 1: rows of A/C grouped, B per group (3-D map); 2: K grouped (wgrad), C per group
   long long c_group_stride; // elements between per-group C matrices (mode 2)
   int max_tiles_m;          // upper bound of m-tiles per group (mode 1)
+  int split_k;              // plain GEMM with fp32 accumulate: reduction split into this many tiles (>= 1);
+                            // with split_k > 1 the epilogue adds with red.global (order not deterministic)
+  int k_chunk;              // reduction length per split (multiple of BK)
+  int tma_store;            // bf16 epilogue through shared memory + TMA store (plain GEMM only)
 };
 
 struct TileCoord {
@@ -60,7 +66,8 @@ struct TileCoord {
   bool valid;
 };
 
-__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile, int tiles_m, int tiles_n) {
+__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n) {
+  const int ks = tile_in % p.split_k, tile = tile_in / p.split_k;
   // bands of 16 row-tiles, column-tiles fastest inside a band -> the CTAs that
   // run together share a handful of A and B tiles in L2
   constexpr int GROUP_M = 16;
@@ -71,19 +78,20 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile, i
   int tm = first_m + r % gm, tn = r / gm;
   TileCoord t;
   t.m0 = tm * BM; t.n0 = tn * BN; t.a_row0 = t.m0; t.b_grp = 0;
-  t.k_lo = 0; t.k_hi = p.K; t.m_end = p.M; t.c_off = 0; t.valid = true;
+  t.k_lo = ks * p.k_chunk; t.k_hi = min(p.K, t.k_lo + p.k_chunk); t.m_end = p.M; t.c_off = 0; t.valid = t.k_hi > t.k_lo;
   return t;
 }
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES + EPI_BYTES);
   // barrier slots: full[0..S), empty[S..2S), acc_full[2S..2S+2), acc_empty[2S+2..2S+4)
-  const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES + EPI_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto accf_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
@@ -112,7 +120,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int tiles_n = (p.N + BN - 1) / BN;
   int tiles_m, total_tiles;
-  if (p.groups == 0) { tiles_m = (p.M + BM - 1) / BM; total_tiles = tiles_m * tiles_n; }
+  if (p.groups == 0) { tiles_m = (p.M + BM - 1) / BM; total_tiles = tiles_m * tiles_n * p.split_k; }
   else if (p.group_mode == 1) { tiles_m = p.max_tiles_m; total_tiles = p.groups * tiles_m * tiles_n; }
   else { tiles_m = (p.M + BM - 1) / BM; total_tiles = p.groups * tiles_m * tiles_n; }
 
@@ -228,6 +236,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = t.m0 + q * 32 + lane;
       const bool row_ok = row < t.m_end;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      if (EPI == EPI_BF16 && p.tma_store) {
+        // 64-column slabs: TMEM -> bf16 -> swizzled staging tile -> TMA store (clips at the matrix edge).
+        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+#pragma unroll 1
+        for (int slab = 0; slab < BN / 64; ++slab) {
+          const int bsel = slab & 1;
+          uint32_t r0[32], r1[32];
+          tmem_ld32(taddr + slab * 64, r0);
+          tmem_ld32(taddr + slab * 64 + 32, r1);
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // this buffer's previous store has read it
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = ebuf + bsel * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t* r = ch < 4 ? r0 : r1;
+            const int j = (ch & 3) * 8;
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            v.y = pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            v.z = pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            v.w = pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int c0 = t.n0 + slab * 64, c1 = t.m0 + q * 32;
+            if (c0 < p.N && c1 < p.M)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"((uint64_t)&tmC), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(c0), "r"(c1) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -255,21 +299,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               if (col + j < p.N) {
                 float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
                                        __uint_as_float(r[j + 3]));
-                if (EPI == EPI_F32_ACC) {
-                  const float4 o = *reinterpret_cast<const float4*>(out + j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                if (EPI == EPI_F32_ACC && p.split_k > 1) {
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + j), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                } else {
+                  if (EPI == EPI_F32_ACC) {
+                    const float4 o = *reinterpret_cast<const float4*>(out + j);
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                  }
+                  *reinterpret_cast<float4*>(out + j) = v;
                 }
-                *reinterpret_cast<float4*>(out + j) = v;
               }
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acce_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (EPI == EPI_BF16 && p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------------------------------------------ teardown
@@ -311,7 +361,8 @@ static int build_map(CUtensorMap* map, const Operand& o, int box_rows) {
 }
 
 template <bool A_MN, bool B_MN, int EPI>
-static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles, cudaStream_t st) {
+static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p, int tiles,
+                    cudaStream_t st) {
   static bool configured = false;
   auto kern = gemm_kernel<A_MN, B_MN, EPI>;
   if (!configured) {
@@ -321,14 +372,21 @@ static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPara
   }
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (grid <= 0) return 0;
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, p);
   count_launch();
   return launch_status();
 }
 
-static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p,
                     int tiles, cudaStream_t st) {
-#define TLM_CASE(A, B, E) if (a_mn == A && b_mn == B && epi == E) return launch_t<A, B, E>(ma, mb, p, tiles, st);
+  CUtensorMap mc = ma;                      // placeholder when the TMA-store epilogue is off
+  if (p.split_k < 1) { p.split_k = 1; p.k_chunk = p.K; }
+  if (epi == EPI_BF16 && p.groups == 0 && p.ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+    uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.M}, strides[1] = {(uint64_t)p.ldc * 2};
+    uint32_t box[2] = {64, 32};
+    if (make_tmap_bf16(&mc, p.C, 2, dims, strides, box) == 0) p.tma_store = 1;
+  }
+#define TLM_CASE(A, B, E) if (a_mn == A && b_mn == B && epi == E) return launch_t<A, B, E>(ma, mb, mc, p, tiles, st);
   TLM_CASE(false, false, EPI_BF16) TLM_CASE(false, true, EPI_BF16) TLM_CASE(true, true, EPI_F32_ACC)
   TLM_CASE(false, false, EPI_F32) TLM_CASE(true, true, EPI_F32) TLM_CASE(false, false, EPI_F32_ACC)
   TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32)
@@ -356,7 +414,19 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return dispatch(a_mn != 0, b_mn != 0, epi, ma, mb, p, tiles, stream);
+  p.split_k = 1; p.k_chunk = K;
+  if (epi == EPI_F32_ACC && tiles * 2 <= num_sms()) {      // few output tiles, long reduction (weight gradients)
+    int want = num_sms() / tiles;
+    int kblocks = (K + BK - 1) / BK;
+    int max_split = kblocks / 8 > 0 ? kblocks / 8 : 1;      // keep at least 8 k-blocks per split
+    int split = want < max_split ? want : max_split;
+    if (split > 1) {
+      int per = (kblocks + split - 1) / split;
+      p.k_chunk = per * BK;
+      p.split_k = (kblocks + per - 1) / per;
+    }
+  }
+  return dispatch(a_mn != 0, b_mn != 0, epi, ma, mb, p, tiles * p.split_k, stream);
 }
 
 // Grouped forward / dgrad: rows of A and C are grouped (`row_start`, device,
