@@ -59,3 +59,24 @@ def test_sequence_parallel_matches_data_parallel_on_gpu():
     dp = _run(2, {}, FLAGS + ["--sep_size", "1"])
     sp = _run(2, {}, [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)] + ["--sep_size", "2"])
     _close(dp["losses"], sp["losses"], 5e-3)
+
+
+MOE = ["--use_moe", "--num_experts", "8", "--num_experts_per_tok", "2", "--moe_intermediate_size", "256"]
+
+
+def test_ulysses_peer_path_matches_nccl_path():
+    flags = [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)] + ["--sep_size", "2"]
+    ref = _run(2, {"TLM_COMM": "nccl"}, flags)
+    peer = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags)
+    _close(ref["losses"], peer["losses"], 2e-3)
+    _close(ref["norms"], peer["norms"], 2e-2)
+
+
+def test_expert_parallel_peer_path_matches_nccl_path_and_single_group():
+    flags4 = [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)]
+    ref = _run(2, {"TLM_COMM": "nccl"}, flags4 + MOE + ["--sep_size", "2"])
+    peer = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags4 + MOE + ["--sep_size", "2"])
+    dp = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, FLAGS + MOE + ["--sep_size", "1"])
+    _close(ref["losses"], peer["losses"], 3e-3)
+    _close(ref["losses"], dp["losses"], 5e-3)
+    _close(ref["norms"], peer["norms"], 3e-2)

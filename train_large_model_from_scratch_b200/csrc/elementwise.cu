@@ -156,6 +156,86 @@ __global__ void add_rmsnorm_bwd_kernel(const float* __restrict__ g_xnew, const _
   }
 }
 
+// Register-resident variant for D = NV * 256 (NV <= 6): each lane owns NV groups of 8
+// columns, keeps x_hat, g*w and its dweight partial sums in registers; one pass over
+// global memory, no shared-memory traffic in the row loop.
+template <int NV>
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
+add_rmsnorm_bwd_reg_kernel(const float* __restrict__ g_xnew, const __nv_bfloat16* __restrict__ g_h,
+                           const float* __restrict__ x_new, const float* __restrict__ rstd_in,
+                           const __nv_bfloat16* __restrict__ w, float* __restrict__ g_x,
+                           __nv_bfloat16* __restrict__ g_delta, float* __restrict__ dw_out, int rows) {
+  constexpr int D = NV * 256;
+  __shared__ float dw_s[8][D > 1024 ? 1 : D];       // block fold (only used when it fits; else atomics per warp)
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float dw[NV * 8];
+#pragma unroll
+  for (int i = 0; i < NV * 8; ++i) dw[i] = 0.f;
+  for (int r = blockIdx.x * warps + warp; r < rows; r += gridDim.x * warps) {
+    const float rstd = rstd_in[r];
+    float xh[NV * 8], gw[NV * 8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      const float4 a = *reinterpret_cast<const float4*>(x_new + (long long)r * D + c);
+      const float4 b = *reinterpret_cast<const float4*>(x_new + (long long)r * D + c + 4);
+      const uint4 gv = *reinterpret_cast<const uint4*>(g_h + (long long)r * D + c);
+      const float2 g0 = unpack_bf16(gv.x), g1 = unpack_bf16(gv.y), g2 = unpack_bf16(gv.z), g3 = unpack_bf16(gv.w);
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + c);          // 2 KB table, stays in L1
+      const float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+      const float xs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      const float gs[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+      const float ws[8] = {w0.x, w0.y, w1.x, w1.y, w2.x, w2.y, w3.x, w3.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = xs[j] * rstd;
+        xh[k * 8 + j] = xhat;
+        dw[k * 8 + j] = fmaf(gs[j], xhat, dw[k * 8 + j]);
+        const float t = gs[j] * ws[j];
+        gw[k * 8 + j] = t;
+        dot = fmaf(t, xhat, dot);
+      }
+    }
+    dot = warp_sum(dot) * (1.f / (float)D);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (gw[k * 8 + j] - xh[k * 8 + j] * dot);
+      if (g_xnew != nullptr) {
+        const float4 ga = *reinterpret_cast<const float4*>(g_xnew + (long long)r * D + c);
+        const float4 gb = *reinterpret_cast<const float4*>(g_xnew + (long long)r * D + c + 4);
+        o[0] += ga.x; o[1] += ga.y; o[2] += ga.z; o[3] += ga.w; o[4] += gb.x; o[5] += gb.y; o[6] += gb.z; o[7] += gb.w;
+      }
+      float4* out = reinterpret_cast<float4*>(g_x + (long long)r * D + c);
+      out[0] = make_float4(o[0], o[1], o[2], o[3]);
+      out[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (g_delta != nullptr)
+        *reinterpret_cast<uint4*>(g_delta + (long long)r * D + c) =
+            make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+    }
+  }
+  if (D <= 1024) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dw_s[warp][(D > 1024 ? 0 : (lane + 32 * k) * 8 + j)] = dw[k * 8 + j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      float t = 0.f;
+      for (int wi = 0; wi < warps; ++wi) t += dw_s[wi][D > 1024 ? 0 : c];
+      atomicAdd(dw_out + c, t);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(dw_out + (lane + 32 * k) * 8 + j, dw[k * 8 + j]);
+  }
+}
+
 // ------------------------------------------------------------------ RoPE (in place)
 // qkv: [rows = B*T, heads_total, hd]; the first n_rot heads are rotated with
 // tables cos/sin [T, hd] (row t = r % T). Pairing is (j, j + hd/2) with an
@@ -419,6 +499,15 @@ TLM_API int tlm_add_rmsnorm_fwd(const float* x, const void* delta, const void* w
 TLM_API int tlm_add_rmsnorm_bwd(const float* g_xnew, const void* g_h, const float* x_new, const float* rstd,
                                 const void* w, float* g_x, void* g_delta, float* dw, int rows, int D,
                                 cudaStream_t st) {
+  if (D % 256 == 0 && D / 256 <= 6 && D / 256 != 5) {
+    const int grid = grid_for((rows + 7) / 8, 1, 4);
+#define TLM_RMS_CASE(NV) case NV: add_rmsnorm_bwd_reg_kernel<NV><<<grid, 256, 0, st>>>(g_xnew, (const __nv_bfloat16*)g_h, x_new, rstd, \
+      (const __nv_bfloat16*)w, g_x, (__nv_bfloat16*)g_delta, dw, rows); break;
+    switch (D / 256) { TLM_RMS_CASE(1) TLM_RMS_CASE(2) TLM_RMS_CASE(3) TLM_RMS_CASE(4) TLM_RMS_CASE(6) }
+#undef TLM_RMS_CASE
+    count_launch();
+    return launch_status();
+  }
   int warps = 8;
   while (warps > 1 && (size_t)warps * 2 * D * 4 > 200 * 1024) warps >>= 1;
   size_t smem = (size_t)warps * 2 * D * 4;

@@ -188,14 +188,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!mbar_wait(full_bar(stage), phase, 3, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
-        if (A_MN && p.group_mode == 2 && t.k_hi - k0 < BK) {
+        if (A_MN && B_MN && p.group_mode == 2 && t.k_hi - k0 < BK) {
           // grouped reduction: rows past this group's end belong to the next group.
           // Zero them in the A tile (each k index is one 128-byte row per 64-wide box,
           // so whole-row zeroing is independent of the swizzle).
           const int valid = t.k_hi - k0;
           uint8_t* a_ptr = smem_al + stage * STAGE_BYTES;
           const int n16 = (BK - valid) * 8;                      // 16-byte pieces per box
-          for (int box = 0; box < BM / 64; ++box)
+          // A and B boxes are contiguous in the stage (2 + 4 boxes of 8 KB); B is cleared as well so that
+          // a non-finite value in a foreign row cannot meet a zero
+          for (int box = 0; box < (BM + BN) / 64; ++box)
             for (int i = lane; i < n16; i += 32)
               *reinterpret_cast<uint4*>(a_ptr + box * BOX_MN_BYTES + valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
           fence_proxy_async_smem();

@@ -81,6 +81,7 @@ class Attention(nn.Module):
         self.c_proj = _Proj(D, D, config.init_std, config.seed, device)
         self._qkv_weight = None
         self._rope_cache: dict = {}
+        self._rope_cache_full: dict = {}
 
     def _post_flatten(self) -> None:
         self._qkv_weight = fuse_adjacent([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
@@ -93,6 +94,22 @@ class Attention(nn.Module):
             self._rope_cache = {key: oracle.rope_tables(pos, self.head_dim, self.config.rope_theta,
                                                         self.config.rope_variant)}
         return self._rope_cache[key]
+
+    def _rope_full(self, T_full: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+        key = ("full", T_full, str(device))
+        if key not in self._rope_cache_full:
+            pos = torch.arange(0, T_full, device=device)
+            self._rope_cache_full = {key: oracle.rope_tables(pos, self.head_dim, self.config.rope_theta,
+                                                             self.config.rope_variant)}
+        return self._rope_cache_full[key]
+
+    def _peer_path(self, qkv: torch.Tensor, sp: int) -> bool:
+        if not (qkv.is_cuda and qkv.dtype == torch.bfloat16):
+            return False
+        from ...parallel import symm
+        from ...parallel.sequence_parallel import ulysses_peer
+        return symm.use_symm() and ulysses_peer.supported(self.num_attention_heads, self.num_key_value_heads, sp,
+                                                          self.head_dim)
 
     def forward(self, h: torch.Tensor, B: int | None = None, T_local: int | None = None) -> torch.Tensor:
         """h: `[B*T_local, D]` (or `[B, T_local, D]`) in the compute dtype -> same shape."""
@@ -109,10 +126,20 @@ class Attention(nn.Module):
                              F_ops.linear(h, self.v_proj.weight)], dim=-1)
         qkv = qkv.view(B, T_local, Hq + 2 * Hkv, hd)
         cos, sin = self._rope(T_local, h.device)
-        qkv = F_ops.rope_qk(qkv, cos, sin, Hq + Hkv)
         sp = parallel_state.get_sep_world_size()
+        group = parallel_state.get_sep_group()
+        if sp > 1 and self._peer_path(qkv, sp):
+            # RoPE + seq->head exchange in one kernel writing into the head owners' memory,
+            # attention, then the head->seq exchange; see parallel/sequence_parallel/ulysses_peer.py
+            from ...parallel.sequence_parallel import ulysses_peer
+            cos_f, sin_f = self._rope_full(T_local * sp, h.device)
+            qkv_l = ulysses_peer.seq_to_head(qkv, Hq, Hkv, cos, sin, cos_f, sin_f, id(self), group)
+            o = F_ops.attention_packed(qkv_l, Hq // sp, Hkv // sp, True)
+            o = ulysses_peer.head_to_seq(o, Hq, id(self), group)
+            y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
+            return y.view(shape)
+        qkv = F_ops.rope_qk(qkv, cos, sin, Hq + Hkv)
         if sp > 1:
-            group = parallel_state.get_sep_group()
             qkv_l, q_l, kv_l = ulysses.seq_to_head(qkv, Hq, Hkv, group)
             o = F_ops.attention_packed(qkv_l.contiguous(), q_l, kv_l, True)
             o = ulysses.head_to_seq(o, group)

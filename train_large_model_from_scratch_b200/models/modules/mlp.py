@@ -96,6 +96,7 @@ class MoE(nn.Module):
         out, aux = moe_ops.moe_forward(
             x2, logits, self.experts_gate_weights, self.experts_up_weights, self.experts_down_weights,
             self.top_k, self.num_experts, parallel_state.get_ep_group(), self.ep_size,
-            aux_coef=self.config.moe_aux_loss_coef, capacity_factor=self.config.moe_capacity_factor)
+            aux_coef=self.config.moe_aux_loss_coef, capacity_factor=self.config.moe_capacity_factor,
+            layer_key=id(self))
         self.aux_loss = aux
         return out.view(shape), logits

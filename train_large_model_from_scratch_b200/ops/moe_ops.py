@@ -82,8 +82,12 @@ def aux_loss(logits: torch.Tensor, experts: torch.Tensor, num_experts: int) -> t
 
 
 def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_group, ep_size: int,
-                aux_coef: float = 0.0, capacity_factor: float = 0.0):
-    """x `[M, D]`, logits `[M, E]` -> (out `[M, D]`, aux loss or None)."""
+                aux_coef: float = 0.0, capacity_factor: float = 0.0, layer_key=None):
+    """x `[M, D]`, logits `[M, E]` -> (out `[M, D]`, aux loss or None).
+
+    On CUDA (bf16) the routing never touches the host: expert row ranges stay in
+    a device `row_start` array read by the grouped GEMM's tile scheduler, and with
+    expert parallelism the rows travel through `parallel.expert_parallel.peer`."""
     M, D = x.shape
     E_local = num_experts // ep_size
     weights, experts = route(logits, k)                                    # [M,k]
@@ -102,9 +106,22 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
         order = order[keep]
     token_of = torch.div(order, k, rounding_mode="floor")
     sorted_x = x.index_select(0, token_of)                                 # gather (bwd: index_add)
-    counts = torch.bincount(flat_e[order], minlength=num_experts).view(ep_size, E_local)
+    counts = _count(flat_e[order], num_experts).view(ep_size, E_local)
 
-    if ep_size > 1:
+    on_device = x.is_cuda and x.dtype == torch.bfloat16 and capacity_factor <= 0.0
+    peer_plan = None
+    if ep_size > 1 and on_device and _peer_enabled():
+        from ..parallel.expert_parallel import peer as ep_peer
+        pm = ep_peer.PeerMoE.get(ep_group, num_experts)
+        peer_plan = pm.plan(counts.view(-1), flat_e[order])
+        local_x = ep_peer.dispatch(sorted_x, pm, peer_plan, layer_key)
+        per_expert = native.DeviceCounts(peer_plan["row_start"], peer_plan["R"])
+    elif ep_size == 1 and on_device:
+        c = counts.view(-1)
+        row_start = torch.cat([c.new_zeros(1), torch.cumsum(c, 0)]).to(torch.int32)
+        local_x = sorted_x
+        per_expert = native.DeviceCounts(row_start, sorted_x.shape[0])
+    elif ep_size > 1:
         recv_counts = exchange_counts(counts, ep_group)                    # [src, E_local]
         both = torch.stack([counts, recv_counts]).tolist()                 # one host sync for both
         send_c, recv_c = both
@@ -124,7 +141,9 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     act = F_ops.swiglu(torch.cat([gate, up], dim=-1))
     y = grouped_linear(act, w_down, per_expert)
 
-    if ep_size > 1:
+    if peer_plan is not None:
+        y = ep_peer.combine(y, pm, peer_plan, layer_key)
+    elif ep_size > 1:
         inv = torch.empty_like(regroup)
         inv[regroup] = torch.arange(regroup.numel(), device=x.device)
         y = ep_all_to_all(y.index_select(0, inv), recv_splits, send_splits, ep_group)
@@ -133,6 +152,16 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     contrib = y.float() * w_sorted[:, None]
     out = torch.zeros(M, D, dtype=torch.float32, device=x.device).index_add(0, token_of, contrib)
     return out.to(x.dtype), aux
+
+
+def _count(idx: torch.Tensor, n: int) -> torch.Tensor:
+    """Histogram without the host sync that `torch.bincount` does on CUDA."""
+    return torch.zeros(n, dtype=torch.int64, device=idx.device).scatter_add_(0, idx, torch.ones_like(idx))
+
+
+def _peer_enabled() -> bool:
+    from ..parallel import symm
+    return symm.use_symm()
 
 
 def _regroup_index(recv_counts: list[list[int]], device) -> torch.Tensor:

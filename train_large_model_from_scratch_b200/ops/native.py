@@ -67,6 +67,9 @@ _SIGS = {
     "tlm_reduce_scatter_blocks": (_I, []),
     "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
     "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P]),
+    "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),
+    "tlm_peer_scatter_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _LL, _LL, _P]),
     "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P]),
 }
 
@@ -291,6 +294,20 @@ def flash_attn_bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
 
 
 # --------------------------------------------------------------------------- grouped GEMMs (MoE experts)
+class DeviceCounts:
+    """Row grouping known only on the device: `row_start` int32 `[groups + 1]`
+    plus a host-side upper bound of the rows of any one group."""
+
+    def __init__(self, row_start: torch.Tensor, max_rows: int):
+        self.row_start, self.max_rows = row_start, int(max_rows)
+
+
+def _grouping(counts, device):
+    if isinstance(counts, DeviceCounts):
+        return counts.row_start, counts.max_rows
+    return _row_start(counts, device), max(int(c) for c in counts)
+
+
 def _row_start(counts, device) -> torch.Tensor:
     acc, out = 0, [0]
     for c in counts:
@@ -307,9 +324,9 @@ def grouped_gemm_nt(x: torch.Tensor, weight: torch.Tensor, counts) -> torch.Tens
     out = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
     if R == 0:
         return out
-    rs = _row_start(counts, x.device)
+    rs, bound = _grouping(counts, x.device)
     _check(lib().tlm_gemm_grouped_rows(x.data_ptr(), weight.data_ptr(), out.data_ptr(), rs.data_ptr(), E, R, N, K,
-                                       lda, K, N * K, N, 0, EPI_BF16, max(int(c) for c in counts), _stream()),
+                                       lda, K, N * K, N, 0, EPI_BF16, bound, _stream()),
            "grouped_gemm_nt")
     return out
 
@@ -322,9 +339,9 @@ def grouped_gemm_nn(dy: torch.Tensor, weight: torch.Tensor, counts) -> torch.Ten
     out = torch.empty(R, K, dtype=torch.bfloat16, device=dy.device)
     if R == 0:
         return out
-    rs = _row_start(counts, dy.device)
+    rs, bound = _grouping(counts, dy.device)
     _check(lib().tlm_gemm_grouped_rows(dy.data_ptr(), weight.data_ptr(), out.data_ptr(), rs.data_ptr(), E, R, K, N,
-                                       lda, K, N * K, K, 1, EPI_BF16, max(int(c) for c in counts), _stream()),
+                                       lda, K, N * K, K, 1, EPI_BF16, bound, _stream()),
            "grouped_gemm_nn")
     return out
 
@@ -337,6 +354,6 @@ def grouped_gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor, 
     assert R == R2 and acc.shape == (E, N, K) and acc.dtype == torch.float32 and acc.is_contiguous()
     if R == 0:
         return
-    rs = _row_start(counts, dy.device)
+    rs, _ = _grouping(counts, dy.device)
     _check(lib().tlm_gemm_grouped_k(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), rs.data_ptr(), E, R, N, K, lda, ldb,
                                     K, N * K, EPI_F32_ACC, _stream()), "grouped_gemm_tn_accum")

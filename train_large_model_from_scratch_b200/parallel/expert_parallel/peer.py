@@ -1,0 +1,160 @@
+"""Expert-parallel dispatch / combine as direct row stores into peer memory (CUDA).
+
+The NCCL path (`comm.py`, and the reference's `model/modules/mlp.py:104-127,
+160-167`) needs the per-rank split sizes on the HOST before it can call
+`all_to_all_single`: two device->host syncs per MoE layer. Here nothing leaves
+the device:
+
+  1. every rank publishes its per-expert pair counts into all peers' count
+     table (`[ep, E]`, symmetric memory) and a flag barrier follows;
+  2. from that table each rank derives, with a few tiny device ops,
+       - where each of ITS sorted (token, slot) pairs lands in the destination
+         rank's receive buffer, which is laid out expert-major / source-minor,
+         i.e. already grouped for the expert GEMMs,
+       - the row ranges of its own experts (`row_start`, consumed by the grouped
+         GEMM's device-side tile scheduler),
+       - for every received row, which rank and which sorted-pair slot it came
+         from (for the way back);
+  3. one kernel stores the rows into the peers' buffers (dispatch); after the
+     expert MLP the same kernel returns them (combine). Backward uses the same
+     two routes in the opposite roles.
+
+Receive buffers have the worst-case size (`ep * M * k` rows: dropless routing can
+send every pair to one rank); rows past the real count are never read.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ...ops import native
+
+
+class PeerMoE:
+    _instance = None
+
+    def __init__(self, group, num_experts: int):
+        from ..symm import symm_alloc, _Peer
+        self.group, self.ep, self.me = group, dist.get_world_size(group), dist.get_rank(group)
+        self.E = num_experts
+        self.E_l = num_experts // self.ep
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        self.flags = _Peer(symm_alloc(64, torch.int32, dev), group)
+        self.counts_t = symm_alloc(self.ep * num_experts, torch.int32, dev)
+        self.counts = _Peer(self.counts_t, group)
+        self.epoch = 0
+        self.buffers: dict = {}
+        dist.barrier(group=group)
+
+    @classmethod
+    def get(cls, group, num_experts: int) -> "PeerMoE":
+        if cls._instance is None or cls._instance.group is not group or cls._instance.E != num_experts:
+            cls._instance = cls(group, num_experts)
+        return cls._instance
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        f = self.flags
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, self.epoch, native._stream()), "peer_barrier")
+
+    def buffer(self, key, rows: int, D: int):
+        from ..symm import symm_alloc, _Peer
+        b = self.buffers.get(key)
+        if b is None or b[0].shape != (rows, D):
+            t = symm_alloc(rows * D, torch.bfloat16, self.dev).view(rows, D)
+            b = (t, _Peer(t, self.group))
+            self.buffers[key] = b
+        return b
+
+    # ------------------------------------------------------------------ routing
+    def plan(self, my_counts: torch.Tensor, sorted_e: torch.Tensor):
+        """my_counts `[E]` (pairs per expert on this rank), sorted_e `[P]` (expert of each sorted pair).
+        Returns a dict of device tensors describing both routes."""
+        ep, E, E_l, me = self.ep, self.E, self.E_l, self.me
+        c32 = my_counts.to(torch.int32).contiguous()
+        native._check(native.lib().tlm_peer_put_i32(c32.data_ptr(), E, self.counts.ptr_array, ep, me * E,
+                                                    native._stream()), "peer_put_i32")
+        self.barrier()
+        C = self.counts_t.view(ep, E).to(torch.int64).clone()              # [src, expert]; clone: the table is reused
+        self.barrier()                                                      # nobody overwrites the table before all have read it
+        tot = C.sum(0)                                                      # [E]
+        base = (torch.cumsum(tot.view(ep, E_l), 1) - tot.view(ep, E_l)).view(E)     # expert's first row on its owner
+        src_prefix = torch.cumsum(C, 0) - C                                 # [src, E] rows of earlier sources
+        my_start = torch.cumsum(C[me], 0) - C[me]                           # first sorted-pair index of each expert here
+        P = sorted_e.numel()
+        pos = torch.arange(P, device=self.dev)
+        send_rank = torch.div(sorted_e, E_l, rounding_mode="floor").to(torch.int32)
+        send_row = base[sorted_e] + src_prefix[me][sorted_e] + (pos - my_start[sorted_e])
+        # my experts
+        mine = slice(me * E_l, (me + 1) * E_l)
+        row_start = torch.cat([base[mine], (base[mine][-1:] + tot[mine][-1:])]).to(torch.int32)
+        n_recv = tot[mine].sum().reshape(1)                                 # rows really received (device scalar)
+        # received row -> (source rank, slot in the source's sorted order)
+        R = ep * P
+        blk_start = (base[mine].view(E_l, 1) + src_prefix[:, mine].t()).reshape(-1)            # (e_l, s) blocks, ascending
+        blk_cnt = C[:, mine].t().reshape(-1)
+        r = torch.arange(R, device=self.dev)
+        # last block whose start <= r among NON-EMPTY blocks: search over block ends instead
+        blk_end = blk_start + blk_cnt
+        blk = torch.searchsorted(blk_end, r, right=True).clamp(max=ep * E_l - 1)
+        src = (blk % ep)
+        e_glob = me * E_l + torch.div(blk, ep, rounding_mode="floor")
+        start_on_src = (torch.cumsum(C, 1) - C)                             # [src, E]
+        back_row = start_on_src[src, e_glob] + (r - blk_start[blk])
+        valid = r < n_recv
+        back_rank = torch.where(valid, src, torch.full_like(src, -1)).to(torch.int32)
+        return {"send_rank": send_rank, "send_row": send_row.contiguous(), "row_start": row_start,
+                "n_recv": n_recv.contiguous(), "back_rank": back_rank, "back_row": back_row.contiguous(),
+                "P": P, "R": R}
+
+    def scatter(self, src: torch.Tensor, dest_rank, dest_row, dst, n_ptr, n_max: int) -> None:
+        t, peer = dst
+        native._check(native.lib().tlm_peer_scatter_rows(
+            src.data_ptr(), None, dest_rank.data_ptr(), dest_row.data_ptr(), peer.ptr_array, self.ep, src.shape[1],
+            native._ptr(n_ptr), n_max, t.shape[0], native._stream()), "peer_scatter_rows")
+        self.barrier()
+
+
+class _Dispatch(torch.autograd.Function):
+    """sorted pairs `[P, D]` -> expert-grouped rows on their owners `[R, D]`."""
+
+    @staticmethod
+    def forward(ctx, x_sorted, pm: PeerMoE, plan: dict, key):
+        dst = pm.buffer((key, "disp"), plan["R"], x_sorted.shape[1])
+        pm.scatter(x_sorted.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"])
+        ctx.pm, ctx.plan, ctx.key = pm, plan, key
+        return dst[0]
+
+    @staticmethod
+    def backward(ctx, d_local):
+        pm, plan = ctx.pm, ctx.plan
+        dst = pm.buffer((ctx.key, "disp_bwd"), plan["P"], d_local.shape[1])
+        pm.scatter(d_local.contiguous(), plan["back_rank"], plan["back_row"], dst, plan["n_recv"], plan["R"])
+        return dst[0], None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    """expert outputs `[R, D]` -> back to the pairs' owners in sorted order `[P, D]`."""
+
+    @staticmethod
+    def forward(ctx, y_local, pm: PeerMoE, plan: dict, key):
+        dst = pm.buffer((key, "comb"), plan["P"], y_local.shape[1])
+        pm.scatter(y_local.contiguous(), plan["back_rank"], plan["back_row"], dst, plan["n_recv"], plan["R"])
+        ctx.pm, ctx.plan, ctx.key = pm, plan, key
+        return dst[0]
+
+    @staticmethod
+    def backward(ctx, d_comb):
+        pm, plan = ctx.pm, ctx.plan
+        dst = pm.buffer((ctx.key, "comb_bwd"), plan["R"], d_comb.shape[1])
+        pm.scatter(d_comb.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"])
+        return dst[0], None, None, None
+
+
+def dispatch(x_sorted, pm, plan, key):
+    return _Dispatch.apply(x_sorted, pm, plan, key)
+
+
+def combine(y_local, pm, plan, key):
+    return _Combine.apply(y_local, pm, plan, key)

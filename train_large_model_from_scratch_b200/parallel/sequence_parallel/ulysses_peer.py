@@ -1,0 +1,181 @@
+"""Ulysses seq<->head exchanges as direct stores into peer memory (CUDA).
+
+Replaces, on the GPU, the pack -> `all_to_all_single` -> unpack sequence of
+`ulysses.py` (and the reference's `model/modules/attn.py:143-171`) by one
+scatter kernel per exchange (`csrc/ulysses.cu`) followed by a flag barrier:
+
+  forward   qkv  [B, T_l, Hq+2Hkv, hd] --RoPE + scatter--> every head owner's
+            [B, T_full, q_l+2kv_l, hd]; attention; o [B, T_full, q_l, hd]
+            --scatter--> every sequence owner's [B, T_l, Hq, hd]
+  backward  the transposed routes; the transposed RoPE rides on the way back.
+
+RoPE is applied inside the first scatter, so the separate RoPE pass and its
+read + write of the qkv tensor disappear as well.
+
+Receive buffers live in symmetric memory, one set per attention layer, created
+at the layer's first call (a collective rendezvous, same order on every rank)
+and reused by later steps. They double as the tensors saved for backward. Reuse
+is safe without extra handshakes: a peer can only reach the next write into a
+buffer after an exchange that this rank completes after its last read of it.
+
+Only head plans without KV replication (`Hkv % sp == 0`) take this path; the
+others use the NCCL path, where replicated KV gradients are summed by autograd.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ...ops import native
+from . import ulysses
+
+
+class _Exchange:
+    """One symmetric receive buffer + its peers' addresses."""
+
+    def __init__(self, shape, group, device):
+        from ..symm import symm_alloc, _Peer
+        n = 1
+        for s in shape:
+            n *= s
+        self.tensor = symm_alloc(n, torch.bfloat16, device).view(shape)
+        self.peer = _Peer(self.tensor, group)
+
+
+class PeerState:
+    """Per-process state of the peer path for one SEP group."""
+
+    _instance = None
+
+    def __init__(self, group):
+        from ..symm import symm_alloc, _Peer
+        self.group = group
+        self.sp = dist.get_world_size(group)
+        self.me = dist.get_rank(group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.flags_t = symm_alloc(64, torch.int32, dev)
+        self.flags = _Peer(self.flags_t, group)
+        self.epoch = 0
+        self.buffers: dict = {}
+        self.tables: dict = {}
+        dist.barrier(group=group)
+
+    @classmethod
+    def get(cls, group) -> "PeerState":
+        if cls._instance is None or cls._instance.group is not group:
+            cls._instance = cls(group)
+        return cls._instance
+
+    def buffer(self, key, shape, device) -> _Exchange:
+        ex = self.buffers.get(key)
+        if ex is None or tuple(ex.tensor.shape) != tuple(shape):
+            ex = _Exchange(shape, self.group, device)
+            self.buffers[key] = ex
+        return ex
+
+    def table(self, key, rows, device) -> torch.Tensor:
+        t = self.tables.get(key)
+        if t is None:
+            t = torch.tensor(rows, dtype=torch.int32, device=device).contiguous()
+            self.tables[key] = t
+        return t
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        f = self.flags
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, self.epoch, native._stream()),
+                      "peer_barrier")
+
+
+def supported(n_q: int, n_kv: int, sp: int, hd: int) -> bool:
+    return n_q % sp == 0 and n_kv % sp == 0 and hd % 16 == 0
+
+
+def _scatter(st: PeerState, src: torch.Tensor, ex: _Exchange, table: torch.Tensor, mode: int, cos, sin, pos0: int):
+    B, Ts, Hs, hd = src.shape
+    Hd = ex.tensor.shape[2]
+    native._check(native.lib().tlm_peer_scatter_heads(
+        src.data_ptr(), ex.peer.ptr_array, table.data_ptr(), native._ptr(cos), native._ptr(sin), mode, B, Ts, Hs, Hd, hd,
+        st.sp, st.me, table.shape[0], pos0, native._stream()), "peer_scatter_heads")
+    st.barrier()
+
+
+class _SeqToHead(torch.autograd.Function):
+    """qkv (un-rotated) `[B, T_l, Hq+2Hkv, hd]` -> rotated `[B, T_full, q_l+2kv_l, hd]` of my heads."""
+
+    @staticmethod
+    def forward(ctx, qkv, n_q, n_kv, cos_l, sin_l, cos_f, sin_f, layer_key, group):
+        st = PeerState.get(group)
+        sp, me = st.sp, st.me
+        B, T_l, Ht, hd = qkv.shape
+        plans, q_l, kv_l = ulysses.head_plan(n_q, n_kv, sp)
+        hpr = q_l + 2 * kv_l
+        rows = []
+        for dest, plan in enumerate(plans):
+            for slot, h in enumerate(plan):
+                rows.append([h, dest, slot, 1 if h < n_q + n_kv else 0])
+        table = st.table(("s2h", n_q, n_kv), rows, qkv.device)
+        ex = st.buffer((layer_key, "qkv"), (B, sp * T_l, hpr, hd), qkv.device)
+        _scatter(st, qkv.contiguous(), ex, table, 0, cos_l, sin_l, 0)
+        ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
+        ctx.save_for_backward(cos_f, sin_f)
+        return ex.tensor
+
+    @staticmethod
+    def backward(ctx, d_full):
+        n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd = ctx.meta
+        cos_f, sin_f = ctx.saved_tensors
+        st = PeerState.get(group)
+        me = st.me
+        # my local slot -> packed head index on the sequence owner; q and k slots get the transposed rotation
+        rows = []
+        for i in range(q_l):
+            rows.append([i, 0, me * q_l + i, 2])
+        for i in range(kv_l):
+            rows.append([q_l + i, 0, n_q + me * kv_l + i, 2])
+        for i in range(kv_l):
+            rows.append([q_l + kv_l + i, 0, n_q + n_kv + me * kv_l + i, 0])
+        table = st.table(("h2s_dqkv", n_q, n_kv), rows, d_full.device)
+        ex = st.buffer((layer_key, "dqkv"), (B, T_l, n_q + 2 * n_kv, hd), d_full.device)
+        _scatter(st, d_full.contiguous(), ex, table, 1, cos_f, sin_f, 0)
+        return ex.tensor, None, None, None, None, None, None, None, None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    """attention output `[B, T_full, q_l, hd]` (my heads) -> `[B, T_l, Hq, hd]` (my rows)."""
+
+    @staticmethod
+    def forward(ctx, o, n_q, layer_key, group):
+        st = PeerState.get(group)
+        sp, me = st.sp, st.me
+        B, T_full, q_l, hd = o.shape
+        rows = [[i, 0, me * q_l + i, 0] for i in range(q_l)]
+        table = st.table(("h2s_o", n_q), rows, o.device)
+        ex = st.buffer((layer_key, "o"), (B, T_full // sp, n_q, hd), o.device)
+        _scatter(st, o.contiguous(), ex, table, 1, None, None, 0)
+        ctx.meta = (n_q, q_l, layer_key, group, B, T_full, hd)
+        return ex.tensor
+
+    @staticmethod
+    def backward(ctx, d_seq):
+        n_q, q_l, layer_key, group, B, T_full, hd = ctx.meta
+        st = PeerState.get(group)
+        sp = st.sp
+        rows = []
+        for dest in range(sp):
+            for i in range(q_l):
+                rows.append([dest * q_l + i, dest, i, 0])
+        table = st.table(("s2h_do", n_q), rows, d_seq.device)
+        ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), d_seq.device)
+        _scatter(st, d_seq.contiguous(), ex, table, 0, None, None, 0)
+        return ex.tensor, None, None, None
+
+
+def seq_to_head(qkv, n_q, n_kv, cos_l, sin_l, cos_f, sin_f, layer_key, group):
+    return _SeqToHead.apply(qkv, n_q, n_kv, cos_l, sin_l, cos_f, sin_f, layer_key, group)
+
+
+def head_to_seq(o, n_q, layer_key, group):
+    return _HeadToSeq.apply(o, n_q, layer_key, group)
