@@ -125,6 +125,42 @@ def test_rope(nat, hd, variant):
     assert _rel_err(gotb, refb) < 4e-3
 
 
+@pytest.mark.parametrize("hd,Hq,Hkv,B,T,K", [(64, 4, 2, 2, 96, 192), (128, 2, 1, 1, 160, 256), (64, 16, 8, 1, 256, 1024),
+                                              (64, 3, 1, 2, 32, 64)])
+def test_gemm_heads_rope_epilogue(nat, hd, Hq, Hkv, B, T, K):
+    """QKV projection whose epilogue rotates q/k heads and writes the packed tensor, against GEMM -> RoPE in fp32."""
+    import ctypes
+    from train_large_model_from_scratch_b200.ops import oracle
+    Ht = Hq + 2 * Hkv
+    x, w = _rand(B * T, K, seed=30), _rand(Ht * hd, K, scale=0.05, seed=31)
+    cos, sin = oracle.rope_tables(torch.arange(7, 7 + T, device="cuda"), hd, 10000.0, "reference")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    out = torch.full((B, T, Ht, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dst = (ctypes.c_void_p * 1)(out.data_ptr())
+    nat.gemm_heads(x, w, False, dst, 1, B, T, T, Ht, 0, Hq, Hkv, Hq, Hkv, hd, Hq + Hkv, cos, sin)
+    ref = (x.float() @ w.float().t()).view(B, T, Ht, hd)
+    ref[:, :, :Hq + Hkv] = oracle.rope(ref[:, :, :Hq + Hkv], cos, sin)
+    assert torch.isfinite(out.float()).all()
+    assert _rel_err(out, ref) < 6e-3
+    assert _rel_err(out[:, :, Hq + Hkv:], ref[:, :, Hq + Hkv:]) < 6e-3
+
+
+def test_gemm_heads_scatter_plan(nat):
+    """Two destinations (both local buffers here) with the Ulysses head plan and a row offset; MN-major weight."""
+    import ctypes
+    hd, Hq, B, T_l, sp, me = 64, 4, 2, 64, 2, 1
+    q_l = Hq // sp
+    dy, w = _rand(B * T_l, 192, seed=32), _rand(192, Hq * hd, scale=0.05, seed=33)     # dy @ w, w is [K, N]
+    bufs = [torch.zeros(B, sp * T_l, q_l, hd, dtype=torch.bfloat16, device="cuda") for _ in range(sp)]
+    dst = (ctypes.c_void_p * sp)(*[b.data_ptr() for b in bufs])
+    nat.gemm_heads(dy, w, True, dst, sp, B, T_l, sp * T_l, q_l, me * T_l, Hq, 0, q_l, 1, hd, 0, None, None)
+    ref = (dy.float() @ w.float()).view(B, T_l, Hq, hd)
+    for r in range(sp):
+        got = bufs[r][:, me * T_l:(me + 1) * T_l]
+        assert _rel_err(got, ref[:, :, r * q_l:(r + 1) * q_l]) < 6e-3
+        assert float(bufs[r][:, :me * T_l].abs().max()) == 0.0            # rows of the other source stay untouched
+
+
 def test_swiglu(nat):
     gu = _rand(77, 2 * 384, seed=13)
     act = nat.swiglu_fwd(gu)

@@ -67,9 +67,12 @@ MOE = ["--use_moe", "--num_experts", "8", "--num_experts_per_tok", "2", "--moe_i
 def test_ulysses_peer_path_matches_nccl_path():
     flags = [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)] + ["--sep_size", "2"]
     ref = _run(2, {"TLM_COMM": "nccl"}, flags)
-    peer = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags)
+    peer = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags)                       # exchanges inside GEMM / attention epilogues
     _close(ref["losses"], peer["losses"], 2e-3)
     _close(ref["norms"], peer["norms"], 2e-2)
+    plain = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0", "TLM_SP_FUSED": "0"}, flags)   # stand-alone scatter kernels
+    _close(ref["losses"], plain["losses"], 2e-3)
+    _close(ref["norms"], plain["norms"], 2e-2)
 
 
 def test_expert_parallel_peer_path_matches_nccl_path_and_single_group():

@@ -24,6 +24,8 @@ namespace tlm {
 
 constexpr int AT_BQ = 128, AT_BKV = 128, AT_THREADS = 192, AT_KV_STAGES = 2;
 
+constexpr int AT_MAX_DST = 8;
+
 struct AttnFwdParams {
   __nv_bfloat16* o;
   float* lse;
@@ -31,6 +33,12 @@ struct AttnFwdParams {
   float scale_log2;        // softmax scale * log2(e)
   float scale;             // softmax scale
   unsigned int* status;
+  // Optional second copy of the output for sequence parallelism (head -> sequence exchange done by
+  // this kernel's epilogue): row t of head h also goes to
+  //   o_dst[t / dst_rows][b, t % dst_rows, dst_head0 + h, :]   (bf16 [B, dst_rows, dst_heads, hd] per rank;
+  // peer-mapped addresses, plain 16-byte stores). n_dst == 0 disables it.
+  __nv_bfloat16* o_dst[AT_MAX_DST];
+  int n_dst, dst_rows, dst_heads, dst_head0;
 };
 
 template <int HD>
@@ -269,6 +277,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
       tc_fence_after();
       const float inv = 1.f / l_run;
       __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * HD;
+      __nv_bfloat16* out2 = nullptr;
+      if (p.n_dst > 0 && t_row < p.T) {
+        const int dest = t_row / p.dst_rows, tl = t_row - dest * p.dst_rows;
+        if (dest < p.n_dst) out2 = p.o_dst[dest] + (((long long)b * p.dst_rows + tl) * p.dst_heads + p.dst_head0 + h) * HD;
+      }
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
         uint32_t r[32];
@@ -283,6 +296,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
             v.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
             v.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
             *reinterpret_cast<uint4*>(out + c + i) = v;
+            if (out2 != nullptr) *reinterpret_cast<uint4*>(out2 + c + i) = v;
           }
         }
       }
@@ -322,13 +336,31 @@ static int launch_fwd(const CUtensorMap& map, const AttnFwdParams& p, cudaStream
 
 using namespace tlm;
 
-TLM_API int tlm_attn_fwd(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,
-                         cudaStream_t st) {
+static int attn_fwd_impl(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,
+                         void* const* o_dst, int n_dst, int dst_rows, int dst_heads, int dst_head0, cudaStream_t st) {
   if (hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
+  if (n_dst < 0 || n_dst > AT_MAX_DST || (n_dst > 0 && (dst_rows <= 0 || (long long)dst_rows * n_dst < T))) return -6;
   CUtensorMap map;
   int e = make_qkv_map(&map, qkv, B, T, Hq + 2 * Hkv, hd, AT_BQ);
   if (e) return e;
-  AttnFwdParams p{(__nv_bfloat16*)o, lse, B, T, Hq, Hkv, scale * 1.4426950408889634f, scale, status_word()};
+  AttnFwdParams p{};
+  p.o = (__nv_bfloat16*)o; p.lse = lse; p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale_log2 = scale * 1.4426950408889634f; p.scale = scale; p.status = status_word();
+  p.n_dst = n_dst; p.dst_rows = dst_rows; p.dst_heads = dst_heads; p.dst_head0 = dst_head0;
+  for (int i = 0; i < n_dst; ++i) p.o_dst[i] = (__nv_bfloat16*)o_dst[i];
   return hd == 64 ? launch_fwd<64>(map, p, st) : launch_fwd<128>(map, p, st);
+}
+
+TLM_API int tlm_attn_fwd(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,
+                         cudaStream_t st) {
+  return attn_fwd_impl(qkv, o, lse, B, T, Hq, Hkv, hd, scale, nullptr, 0, 0, 0, 0, st);
+}
+
+// Same, and the epilogue also stores every output row into the memory of the rank that owns the
+// row's sequence chunk (see AttnFwdParams): the head -> sequence exchange of Ulysses sequence parallelism.
+TLM_API int tlm_attn_fwd_scatter(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd,
+                                 float scale, void* const* o_dst, int n_dst, int dst_rows, int dst_heads,
+                                 int dst_head0, cudaStream_t st) {
+  return attn_fwd_impl(qkv, o, lse, B, T, Hq, Hkv, hd, scale, o_dst, n_dst, dst_rows, dst_heads, dst_head0, st);
 }

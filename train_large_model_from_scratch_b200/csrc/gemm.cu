@@ -36,7 +36,12 @@ constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3 };
+
+// Destinations of the head-scatter epilogue: one 4-D map (hd, heads, T, B; box 64 x 1 x 32 x 1)
+// per rank of the sequence-parallel group; entry 0 alone when the output stays local.
+constexpr int MAX_HEAD_DST = 8;
+struct HeadDstMaps { CUtensorMap m[MAX_HEAD_DST]; };
 
 struct GemmParams {
   int M, N, K;
@@ -54,6 +59,15 @@ struct GemmParams {
                             // with split_k > 1 the epilogue adds with red.global (order not deterministic)
   int k_chunk;              // reduction length per split (multiple of BK)
   int tma_store;            // bf16 epilogue through shared memory + TMA store (plain GEMM only)
+  // EPI_HEADS: the N axis is a run of heads of `hd` columns (q heads, then k, then v) and the M axis is
+  // [batch][rows_per_batch]. Head h of row (b, t) is rotated (RoPE, heads < n_rot) and stored as bf16 into
+  //   dst[owner(h)][b, row_off + t, slot(h), :]
+  // where owner / slot follow the Ulysses head plan: q head h -> (h / q_l, h % q_l), k head j ->
+  // (j / kv_l, q_l + j % kv_l), v head j -> (j / kv_l, q_l + kv_l + j % kv_l). With one destination and
+  // q_l = Hq, kv_l = Hkv this is the identity layout [B, T, Hq + 2 Hkv, hd].
+  int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot;
+  const float* cosT;        // [rows_per_batch, hd]
+  const float* sinT;
 };
 
 struct TileCoord {
@@ -83,9 +97,8 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in
 }
 
 template <bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                                          const GemmParams& p, const CUtensorMap* dst_maps) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -238,7 +251,110 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = t.m0 + q * 32 + lane;
       const bool row_ok = row < t.m_end;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      if (EPI == EPI_BF16 && p.tma_store) {
+      if (EPI == EPI_HEADS) {
+        // One head (hd columns) at a time: TMEM -> RoPE -> bf16 -> swizzled staging tile(s) -> TMA store into
+        // the head owner's packed tensor. The warp's 32 rows belong to one batch entry (rows_per_batch % 32 == 0).
+        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const int grow = t.m0 + q * 32;
+        const bool rows_ok = grow < p.M;                       // warp-uniform (M % 32 == 0)
+        const int bi = grow / p.rows_per_batch, t0 = grow - bi * p.rows_per_batch;
+        const int hd = p.hd, half = hd >> 1;
+        const int n_heads = p.Hq + 2 * p.Hkv;
+        const float* crow = p.cosT + (long long)(t0 + lane) * hd;
+        const float* srow = p.sinT + (long long)(t0 + lane) * hd;
+        // rotate 32 (lo, hi) column pairs: lo = columns [c, c+32), hi = [c+half, c+half+32) of the head
+        auto rotate = [&](uint32_t* lo, uint32_t* hi, int c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 cl = *reinterpret_cast<const float4*>(crow + c + i), sl = *reinterpret_cast<const float4*>(srow + c + i);
+            const float4 ch = *reinterpret_cast<const float4*>(crow + c + half + i), sh = *reinterpret_cast<const float4*>(srow + c + half + i);
+            const float clv[4] = {cl.x, cl.y, cl.z, cl.w}, slv[4] = {sl.x, sl.y, sl.z, sl.w};
+            const float chv[4] = {ch.x, ch.y, ch.z, ch.w}, shv[4] = {sh.x, sh.y, sh.z, sh.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float a = __uint_as_float(lo[i + k]), b = __uint_as_float(hi[i + k]);
+              lo[i + k] = __float_as_uint(a * clv[k] - b * slv[k]);
+              hi[i + k] = __float_as_uint(b * chv[k] + a * shv[k]);
+            }
+          }
+        };
+        // 32 fp32 columns -> bf16 -> 16-byte chunks [chunk0, chunk0 + 4) of this lane's 128-byte staging row
+        auto stage32 = [&](const uint32_t* r, uint8_t* buf, int chunk0) {
+          uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const int j = ch * 8;
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            v.y = pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            v.z = pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            v.w = pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            *reinterpret_cast<uint4*>(rowp + (((chunk0 + ch) ^ (lane & 7)) << 4)) = v;
+          }
+        };
+        const int heads_per_tile = BN / hd;
+#pragma unroll 1
+        for (int hh = 0; hh < heads_per_tile; ++hh) {
+          const int head = t.n0 / hd + hh;
+          const bool live = rows_ok && head < n_heads;          // warp-uniform
+          int dest, slot;
+          if (head < p.Hq) { dest = head / p.q_l; slot = head - dest * p.q_l; }
+          else if (head < p.Hq + p.Hkv) { const int k = head - p.Hq; dest = k / p.kv_l; slot = p.q_l + (k - dest * p.kv_l); }
+          else { const int v = head - p.Hq - p.Hkv; dest = v / p.kv_l; slot = p.q_l + p.kv_l + (v - dest * p.kv_l); }
+          const bool rot = head < p.n_rot;
+          if (hd == 64) {
+            const int bsel = hh & 1;
+            uint32_t r0[32], r1[32];
+            tmem_ld32(taddr + hh * 64, r0);
+            tmem_ld32(taddr + hh * 64 + 32, r1);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            tmem_ld_wait();
+            if (live) {
+              if (rot) rotate(r0, r1, 0);
+              stage32(r0, ebuf + bsel * EPI_BUF_BYTES, 0);
+              stage32(r1, ebuf + bsel * EPI_BUF_BYTES, 4);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (live)
+                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                             ::"l"((uint64_t)(dst_maps + dest)), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(0), "r"(slot),
+                               "r"(p.row_off + t0), "r"(bi) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          } else {                                              // hd == 128: both staging tiles hold one head
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+#pragma unroll 1
+            for (int part = 0; part < 2; ++part) {              // columns [32 part, +32) pair with [64 + 32 part, +32)
+              uint32_t r0[32], r1[32];
+              tmem_ld32(taddr + hh * 128 + part * 32, r0);
+              tmem_ld32(taddr + hh * 128 + 64 + part * 32, r1);
+              tmem_ld_wait();
+              if (live) {
+                if (rot) rotate(r0, r1, part * 32);
+                stage32(r0, ebuf, part * 4);
+                stage32(r1, ebuf + EPI_BUF_BYTES, part * 4);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (live) {
+#pragma unroll
+                for (int s2 = 0; s2 < 2; ++s2)
+                  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                               ::"l"((uint64_t)(dst_maps + dest)), "r"(ebuf_s + s2 * EPI_BUF_BYTES), "r"(s2 * 64), "r"(slot),
+                                 "r"(p.row_off + t0), "r"(bi) : "memory");
+              }
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+      } else if (EPI == EPI_BF16 && p.tma_store) {
         // 64-column slabs: TMEM -> bf16 -> swizzled staging tile -> TMA store (clips at the matrix edge).
         uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
         const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
@@ -321,7 +437,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(acce_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (EPI == EPI_BF16 && p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (((EPI == EPI_BF16 && p.tma_store) || EPI == EPI_HEADS) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------------------------------------------ teardown
@@ -331,6 +447,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  gemm_body<A_MN, B_MN, EPI>(tmA, tmB, tmC, p, nullptr);
+}
+
+// Same main loop, head-scatter epilogue: the output maps (one per destination rank) replace the C map.
+template <bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_heads_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ HeadDstMaps dst, const GemmParams p) {
+  gemm_body<false, B_MN, EPI_HEADS>(tmA, tmB, tmA, p, dst.m);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -396,9 +527,62 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
   return -2;
 }
 
+template <bool B_MN>
+static int launch_heads(const CUtensorMap& ma, const CUtensorMap& mb, const HeadDstMaps& dst, const GemmParams& p,
+                        int tiles, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_heads_kernel<B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, dst, p);
+  count_launch();
+  return launch_status();
+}
+
 }  // namespace tlm
 
 using namespace tlm;
+
+// Projection GEMM whose epilogue applies RoPE and scatters heads (see GemmParams):
+//   A [M = batch * rows_per_batch, K] (lda);  B [N, K] K-major (b_mn = 0) or [K, N] MN-major (b_mn = 1),
+//   N = (Hq + 2 Hkv) * hd;  dst_ptrs[r]: bf16 [batch, dst_rows, dst_heads, hd] on rank r (peer-mapped
+//   addresses are fine: the stores are TMA tile stores without multicast).
+// Requirements: hd in {64, 128}, rows_per_batch % 32 == 0, n_dst <= 8, Hq % q_l == 0, Hkv % kv_l == 0.
+TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
+                           void* const* dst_ptrs, int n_dst, int batch, int rows_per_batch, int dst_rows, int dst_heads,
+                           int row_off, int Hq, int Hkv, int q_l, int kv_l, int hd, int n_rot, const float* cosT,
+                           const float* sinT, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((hd != 64 && hd != 128) || rows_per_batch % 32 != 0 || n_dst < 1 || n_dst > MAX_HEAD_DST) return -4;
+  if (M != batch * rows_per_batch || N != (Hq + 2 * Hkv) * hd || q_l <= 0 || Hq % q_l != 0) return -5;
+  if (Hkv > 0 && (kv_l <= 0 || Hkv % kv_l != 0)) return -5;
+  if (Hq / q_l > n_dst || (Hkv > 0 && Hkv / kv_l > n_dst)) return -5;
+  if (n_rot > 0 && (cosT == nullptr || sinT == nullptr)) return -5;
+  Operand oa{A, M, K, lda, false, 0, 0}, ob{B, N, K, ldb, b_mn != 0, 1, (long long)N * K};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  HeadDstMaps dst;
+  for (int r = 0; r < n_dst; ++r) {
+    e = make_qkv_map(&dst.m[r], dst_ptrs[r], batch, dst_rows, dst_heads, hd, 32);
+    if (e) return e;
+  }
+  for (int r = n_dst; r < MAX_HEAD_DST; ++r) dst.m[r] = dst.m[0];
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
+  p.split_k = 1; p.k_chunk = K;
+  p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
+  p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cosT = cosT; p.sinT = sinT;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return b_mn ? launch_heads<true>(ma, mb, dst, p, tiles, stream) : launch_heads<false>(ma, mb, dst, p, tiles, stream);
+}
 
 // C[M,N] = A * B^T with arbitrary operand majors.
 //   a_mn = 0: A is [M,K] (lda); a_mn = 1: A is [K,M] (lda)

@@ -2,6 +2,10 @@
 #include "common.cuh"
 
 #include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
 
 namespace tlm {
 
@@ -38,10 +42,39 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// Encoded maps are pure functions of (base, dims, strides, box); training re-launches the same
+// few hundred operand shapes on the same addresses every step, so they are memoised.
+struct TmapKey {
+  uint64_t v[16];
+  bool operator==(const TmapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 16; ++i) { h ^= k.v[i]; h *= 1099511628211ull; }
+    return (size_t)h;
+  }
+};
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+static std::mutex g_tmap_mutex;
+
 int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                    const uint32_t* box) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return -1;
+  TmapKey key{};
+  key.v[0] = (uint64_t)(uintptr_t)base;
+  key.v[1] = (uint64_t)rank;
+  for (int i = 0; i < rank; ++i) {
+    key.v[2 + i] = dims[i];
+    key.v[7 + i] = (uint64_t)box[i];
+    if (i + 1 < rank) key.v[12 + i] = strides_bytes[i];
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) { *map = it->second; return 0; }
+  }
   cuuint64_t gdim[5], gstr[4];
   cuuint32_t bdim[5], estr[5];
   for (int i = 0; i < rank; ++i) {
@@ -60,6 +93,11 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t*
     for (int i = 0; i < rank; ++i) fprintf(stderr, " %u", box[i]);
     fprintf(stderr, "\n");
     return (int)r;
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
+    g_tmap_cache.emplace(key, *map);
   }
   return 0;
 }

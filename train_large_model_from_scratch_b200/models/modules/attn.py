@@ -119,15 +119,29 @@ class Attention(nn.Module):
             h = h.reshape(-1, shape[-1])
         Hq, Hkv, hd = self.num_attention_heads, self.num_key_value_heads, self.head_dim
         h = h.to(self.q_proj.weight.dtype)
+        sp = parallel_state.get_sep_world_size()
+        group = parallel_state.get_sep_group()
+        cos, sin = self._rope(T_local, h.device)
+        if F_ops.qkv_project_fused_ok(h, self._qkv_weight, hd, T_local):
+            # CUDA: projection + RoPE (+ the seq->head exchange) are one GEMM with a head-scatter epilogue
+            if sp == 1:
+                qkv = F_ops.qkv_project(h, self._qkv_weight, cos, sin, B, T_local, Hq, Hkv, hd)
+                o = F_ops.attention_packed(qkv, Hq, Hkv, True)
+                y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
+                return y.view(shape)
+            from ...parallel.sequence_parallel import ulysses_peer
+            if self._peer_path(h, sp) and ulysses_peer.fused_ok(Hq, Hkv, sp, hd, T_local):
+                cos_f, sin_f = self._rope_full(T_local * sp, h.device)
+                qkv_l = ulysses_peer.qkv_project_scatter(h, self._qkv_weight, Hq, Hkv, hd, B, T_local, cos, sin,
+                                                         cos_f, sin_f, id(self), group)
+                y = ulysses_peer.attention_out_project(qkv_l, self.c_proj.weight, Hq, Hkv, id(self), group)
+                return y.view(shape)
         if self._qkv_weight is not None:
             qkv = F_ops.linear(h, self._qkv_weight)
         else:
             qkv = torch.cat([F_ops.linear(h, self.q_proj.weight), F_ops.linear(h, self.k_proj.weight),
                              F_ops.linear(h, self.v_proj.weight)], dim=-1)
         qkv = qkv.view(B, T_local, Hq + 2 * Hkv, hd)
-        cos, sin = self._rope(T_local, h.device)
-        sp = parallel_state.get_sep_world_size()
-        group = parallel_state.get_sep_group()
         if sp > 1 and self._peer_path(qkv, sp):
             # RoPE + seq->head exchange in one kernel writing into the head owners' memory,
             # attention, then the head->seq exchange; see parallel/sequence_parallel/ulysses_peer.py

@@ -32,6 +32,21 @@ def fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
     return out[0].transpose(1, 2).contiguous(), out[1]
 
 
+def fwd_scatter(qkv: torch.Tensor, n_q: int, n_kv: int, dst_ptrs, n_dst: int, dst_rows: int, dst_heads: int,
+                dst_head0: int):
+    """Causal attention (head dims 64 / 128) whose epilogue also stores each output row into
+    `dst[t // dst_rows][b, t % dst_rows, dst_head0 + h, :]` (`dst_ptrs`: ctypes array of device addresses of
+    bf16 `[B, dst_rows, dst_heads, hd]` tensors, typically peers' symmetric buffers)."""
+    B, T, _, hd = qkv.shape
+    assert _native_ok(hd) and qkv.is_contiguous()
+    o = torch.empty(B, T, n_q, hd, dtype=torch.bfloat16, device=qkv.device)
+    lse = torch.empty(B, n_q, T, dtype=torch.float32, device=qkv.device)
+    native._check(native.lib().tlm_attn_fwd_scatter(qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), B, T, n_q, n_kv, hd,
+                                                    1.0 / math.sqrt(hd), dst_ptrs, n_dst, dst_rows, dst_heads,
+                                                    dst_head0, native._stream()), "attn_fwd_scatter")
+    return o, lse
+
+
 def _split(qkv, n_q, n_kv):
     q = qkv[:, :, :n_q].transpose(1, 2)
     k = qkv[:, :, n_q:n_q + n_kv].transpose(1, 2)

@@ -162,6 +162,46 @@ def rope_qk(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_rot_heads
     return _RopeQK.apply(qkv, cos, sin, n_rot_heads)
 
 
+# --------------------------------------------------------------------------- fused QKV projection + RoPE
+class _QKVProject(torch.autograd.Function):
+    """`h [B*T, D]` -> packed, rotated `[B, T, n_q + 2 n_kv, hd]` in one GEMM:
+    the epilogue applies RoPE to the q and k heads while the accumulator is
+    still in registers and writes the packed layout that attention reads. The
+    backward applies the transposed rotation in place to the incoming gradient
+    and runs the weight- and data-gradient GEMMs on it."""
+
+    @staticmethod
+    def forward(ctx, h, weight, cos, sin, B, T, n_q, n_kv, hd):
+        ctx.save_for_backward(h, cos, sin)
+        ctx.weight, ctx.n_rot = weight, n_q + n_kv
+        Ht = n_q + 2 * n_kv
+        out = torch.empty(B, T, Ht, hd, dtype=torch.bfloat16, device=h.device)
+        import ctypes
+        dst = (ctypes.c_void_p * 1)(out.data_ptr())
+        native.gemm_heads(h, weight, False, dst, 1, B, T, T, Ht, 0, n_q, n_kv, n_q, max(n_kv, 1), hd,
+                          n_q + n_kv, cos, sin)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_rot):
+        h, cos, sin = ctx.saved_tensors
+        w = ctx.weight
+        d = native.rope_qk(d_rot.contiguous(), cos, sin, ctx.n_rot, True)      # in place: the gradient is ours
+        d2 = d.view(h.shape[0], -1)
+        native.gemm_tn_accum(d2, h, _main_grad(w))
+        dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
+        return dh, None, None, None, None, None, None, None, None
+
+
+def qkv_project_fused_ok(h: torch.Tensor, weight: torch.Tensor | None, hd: int, T: int) -> bool:
+    return weight is not None and _use_native(h, weight) and native.heads_epilogue_ok(hd, T)
+
+
+def qkv_project(h, weight, cos, sin, B: int, T: int, n_q: int, n_kv: int, hd: int) -> torch.Tensor:
+    """CUDA only (check `qkv_project_fused_ok` first)."""
+    return _QKVProject.apply(h, weight, cos, sin, B, T, n_q, n_kv, hd)
+
+
 # --------------------------------------------------------------------------- attention
 def _attn_fwd_ref(q, k, v, causal):
     """Returns (out, lse) with fp32 math. q [B,T,Hq,hd], k/v [B,T,Hkv,hd]."""

@@ -49,6 +49,7 @@ _SIGS = {
     "tlm_take_device_status": (_c.c_uint, []),
     "tlm_num_sms": (_I, []),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
+    "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
     "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
@@ -62,6 +63,7 @@ _SIGS = {
     "tlm_sumsq_scratch_floats": (_I, []),
     "tlm_sumsq": (_I, [_P, _LL, _P, _P, _P]),
     "tlm_attn_fwd": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
+    "tlm_attn_fwd_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P]),
     "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "tlm_peer_barrier": (_I, [_P, _I, _I, _I, _P]),
     "tlm_reduce_scatter_blocks": (_I, []),
@@ -178,6 +180,29 @@ def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor) -> None:
     assert M == M2 and acc.dtype == torch.float32 and acc.shape[1] == K
     _check(lib().tlm_gemm(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), N, K, M, lda, ldb, acc.stride(0),
                           1, 1, EPI_F32_ACC, _stream()), "gemm_tn_accum")
+
+
+def heads_epilogue_ok(hd: int, rows_per_batch: int, n_dst: int = 1) -> bool:
+    """Shapes the head-scatter GEMM epilogue supports."""
+    return hd in (64, 128) and rows_per_batch % 32 == 0 and 1 <= n_dst <= 8
+
+
+def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: int, batch: int, rows_per_batch: int,
+               dst_rows: int, dst_heads: int, row_off: int, n_q: int, n_kv: int, q_l: int, kv_l: int, hd: int,
+               n_rot: int, cos: torch.Tensor | None, sin: torch.Tensor | None) -> None:
+    """Projection GEMM with the head-scatter epilogue (`csrc/gemm.cu`, `tlm_gemm_heads`):
+    `x [batch*rows_per_batch, K]` times `w` (`[N, K]`, or `[K, N]` when `b_mn`), N = (n_q + 2 n_kv) * hd;
+    head h of row (b, t) -> RoPE (heads < n_rot) -> `dst[owner(h)][b, row_off + t, slot(h), :]`.
+    `dst_ptrs` is a ctypes array of `n_dst` device addresses (this rank's own tensor or peers' buffers)."""
+    M, K, lda = _rows(x)
+    if b_mn:
+        K2, N, ldb = _rows(w)
+    else:
+        N, K2, ldb = _rows(w)
+    assert K == K2 and M == batch * rows_per_batch
+    _check(lib().tlm_gemm_heads(x.data_ptr(), w.data_ptr(), M, N, K, lda, ldb, int(b_mn), dst_ptrs, n_dst, batch,
+                                rows_per_batch, dst_rows, dst_heads, row_off, n_q, n_kv, q_l, kv_l, hd, n_rot,
+                                _ptr(cos), _ptr(sin), _stream()), "gemm_heads")
 
 
 def gemm_raw(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi) -> None:

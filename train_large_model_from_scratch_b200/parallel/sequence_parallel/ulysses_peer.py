@@ -1,8 +1,13 @@
 """Ulysses seq<->head exchanges as direct stores into peer memory (CUDA).
 
 Replaces, on the GPU, the pack -> `all_to_all_single` -> unpack sequence of
-`ulysses.py` (and the reference's `model/modules/attn.py:143-171`) by one
-scatter kernel per exchange (`csrc/ulysses.cu`) followed by a flag barrier:
+`ulysses.py` (and the reference's `model/modules/attn.py:143-171`). Three of the
+four exchanges per layer happen inside compute kernels (`_QKVProjectScatter`:
+QKV projection + RoPE + seq->head in the GEMM epilogue; `_AttnOutProject`:
+head->seq in the attention epilogue, and in backward seq->head in the epilogue
+of the output projection's data-gradient GEMM); the packed gradient's way back
+is one scatter kernel (`csrc/ulysses.cu`) that also applies the transposed
+rotation. Every exchange ends with a flag barrier:
 
   forward   qkv  [B, T_l, Hq+2Hkv, hd] --RoPE + scatter--> every head owner's
             [B, T_full, q_l+2kv_l, hd]; attention; o [B, T_full, q_l, hd]
@@ -128,16 +133,7 @@ class _SeqToHead(torch.autograd.Function):
         n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd = ctx.meta
         cos_f, sin_f = ctx.saved_tensors
         st = PeerState.get(group)
-        me = st.me
-        # my local slot -> packed head index on the sequence owner; q and k slots get the transposed rotation
-        rows = []
-        for i in range(q_l):
-            rows.append([i, 0, me * q_l + i, 2])
-        for i in range(kv_l):
-            rows.append([q_l + i, 0, n_q + me * kv_l + i, 2])
-        for i in range(kv_l):
-            rows.append([q_l + kv_l + i, 0, n_q + n_kv + me * kv_l + i, 0])
-        table = st.table(("h2s_dqkv", n_q, n_kv), rows, d_full.device)
+        table = _dqkv_table(st, n_q, n_kv, q_l, kv_l, d_full.device)
         ex = st.buffer((layer_key, "dqkv"), (B, T_l, n_q + 2 * n_kv, hd), d_full.device)
         _scatter(st, d_full.contiguous(), ex, table, 1, cos_f, sin_f, 0)
         return ex.tensor, None, None, None, None, None, None, None, None
@@ -171,6 +167,113 @@ class _HeadToSeq(torch.autograd.Function):
         ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), d_seq.device)
         _scatter(st, d_seq.contiguous(), ex, table, 0, None, None, 0)
         return ex.tensor, None, None, None
+
+
+def _dqkv_table(st: PeerState, n_q, n_kv, q_l, kv_l, device) -> torch.Tensor:
+    """head->seq route of the packed gradient: my local slot -> packed head index on the
+    sequence owner; q and k slots get the transposed rotation."""
+    me = st.me
+    rows = [[i, 0, me * q_l + i, 2] for i in range(q_l)]
+    rows += [[q_l + i, 0, n_q + me * kv_l + i, 2] for i in range(kv_l)]
+    rows += [[q_l + kv_l + i, 0, n_q + n_kv + me * kv_l + i, 0] for i in range(kv_l)]
+    return st.table(("h2s_dqkv", n_q, n_kv), rows, device)
+
+
+class _QKVProjectScatter(torch.autograd.Function):
+    """`h [B*T_l, D]` -> rotated `[B, T_full, q_l + 2 kv_l, hd]` of my heads, with ONE kernel doing the
+    projection GEMM, RoPE and the seq->head exchange: the GEMM epilogue stores every (32-row, head) tile with
+    a TMA tile store into the memory of the rank that owns the head (`csrc/gemm.cu`, head-scatter epilogue).
+    Backward: the packed gradient returns head->seq with the transposed rotation (one scatter kernel) and
+    feeds the weight- and data-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group):
+        st = PeerState.get(group)
+        sp, me = st.sp, st.me
+        _, q_l, kv_l = ulysses.head_plan(n_q, n_kv, sp)
+        hpr = q_l + 2 * kv_l
+        ex = st.buffer((layer_key, "qkv"), (B, sp * T_l, hpr, hd), h.device)
+        native.gemm_heads(h, weight, False, ex.peer.ptr_array, sp, B, T_l, sp * T_l, hpr, me * T_l, n_q, n_kv,
+                          q_l, kv_l, hd, n_q + n_kv, cos_l, sin_l)
+        st.barrier()
+        ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
+        ctx.weight = weight
+        ctx.save_for_backward(h, cos_f, sin_f)
+        return ex.tensor
+
+    @staticmethod
+    def backward(ctx, d_full):
+        from ...ops.functional import _main_grad
+        n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd = ctx.meta
+        h, cos_f, sin_f = ctx.saved_tensors
+        w = ctx.weight
+        st = PeerState.get(group)
+        table = _dqkv_table(st, n_q, n_kv, q_l, kv_l, d_full.device)
+        ex = st.buffer((layer_key, "dqkv"), (B, T_l, n_q + 2 * n_kv, hd), d_full.device)
+        _scatter(st, d_full.contiguous(), ex, table, 1, cos_f, sin_f, 0)
+        d2 = ex.tensor.view(B * T_l, -1)
+        native.gemm_tn_accum(d2, h, _main_grad(w))
+        dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
+        return (dh,) + (None,) * 12
+
+
+class _AttnOutProject(torch.autograd.Function):
+    """Causal attention over my heads `[B, T_full, q_l + 2 kv_l, hd]` followed by the output projection
+    on my sequence chunk -> `[B*T_l, D]`, with both exchanges inside compute kernels:
+
+      forward   the attention epilogue stores each output row into the memory of the rank that owns the
+                row's sequence chunk (head->seq), then the output GEMM runs on the assembled rows;
+      backward  the data-gradient GEMM `dy @ W` has the head-scatter epilogue, so d(o) goes straight from
+                the accumulator to the head owners (seq->head), where the attention backward consumes it.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv_l, weight, n_q, n_kv, layer_key, group):
+        from ...ops import attention_cuda
+        st = PeerState.get(group)
+        sp, me = st.sp, st.me
+        B, T_full, _, hd = qkv_l.shape
+        q_l, kv_l, T_l = n_q // sp, n_kv // sp, T_full // sp
+        ex = st.buffer((layer_key, "o"), (B, T_l, n_q, hd), qkv_l.device)
+        o, lse = attention_cuda.fwd_scatter(qkv_l, q_l, kv_l, ex.peer.ptr_array, sp, T_l, n_q, me * q_l)
+        st.barrier()
+        o_seq = ex.tensor.view(B * T_l, n_q * hd)
+        ctx.meta = (n_q, q_l, kv_l, layer_key, group, B, T_full, T_l, hd)
+        ctx.weight = weight
+        ctx.save_for_backward(qkv_l, o, lse, o_seq)
+        return native.gemm_nt(o_seq, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ...ops import attention_cuda
+        from ...ops.functional import _main_grad
+        n_q, q_l, kv_l, layer_key, group, B, T_full, T_l, hd = ctx.meta
+        qkv_l, o, lse, o_seq = ctx.saved_tensors
+        w = ctx.weight
+        st = PeerState.get(group)
+        dy = dy.contiguous()
+        native.gemm_tn_accum(dy, o_seq, _main_grad(w))
+        ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), dy.device)
+        native.gemm_heads(dy, w, True, ex.peer.ptr_array, st.sp, B, T_l, T_full, q_l, st.me * T_l, n_q, 0, q_l, 1,
+                          hd, 0, None, None)
+        st.barrier()
+        dqkv = attention_cuda.bwd(ex.tensor, qkv_l, o, lse, q_l, kv_l, True)
+        return dqkv, None, None, None, None, None
+
+
+def fused_ok(n_q: int, n_kv: int, sp: int, hd: int, T_l: int) -> bool:
+    """Shapes for which the exchanges ride on the GEMM epilogues."""
+    import os
+    return (supported(n_q, n_kv, sp, hd) and native.heads_epilogue_ok(hd, T_l, sp)
+            and os.environ.get("TLM_SP_FUSED", "1") != "0")       # 0: keep the stand-alone scatter kernels
+
+
+def qkv_project_scatter(h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group):
+    return _QKVProjectScatter.apply(h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group)
+
+
+def attention_out_project(qkv_l, weight, n_q, n_kv, layer_key, group):
+    return _AttnOutProject.apply(qkv_l, weight, n_q, n_kv, layer_key, group)
 
 
 def seq_to_head(qkv, n_q, n_kv, cos_l, sin_l, cos_f, sin_f, layer_key, group):
