@@ -21,7 +21,14 @@ def main():
     t._resume_from_checkpoint()
     losses, norms = {}, {}
     last = t.training_info["max_steps"] if stop_after < 0 else stop_after
+    exit_rank, exit_step = int(os.environ.get("TLM_EXIT_RANK", "-1")), int(os.environ.get("TLM_EXIT_BEFORE_STEP", "-1"))
+    marker = os.environ.get("TLM_EXIT_ONCE_MARKER")
     for step in range(t.start_step, last):
+        if rank == exit_rank and step == exit_step and not (marker and os.path.exists(marker)):
+            # a host-made failure: this rank leaves between steps, with nothing in flight
+            if marker:
+                open(marker, "w").close()
+            os._exit(17)
         r = t.train_step(step)
         losses[step] = float(r["loss"])
         norms[step] = float(r["grad_norm"])

@@ -236,3 +236,74 @@ def test_grouped_gemms(nat, counts, N, K):
         ref = 1.0 + dy[r:r + c].float().t() @ x[r:r + c].float()
         assert _rel_err(acc[e], ref) < 1e-4, ("tn", e)
         r += c
+
+
+@pytest.mark.parametrize("M,E,k", [(300, 8, 2), (129, 128, 8), (64, 4, 1), (1000, 40, 3)])
+def test_moe_route_and_row_movement(nat, M, E, k):
+    """Device routing (top-k, softmax of the winners, stable expert-major order) and the gather / combine /
+    pair-dot kernels against torch."""
+    D = 64
+    g = torch.Generator(device="cuda").manual_seed(40)
+    # distinct logits per row so that the top-k set is unambiguous
+    logits = (torch.rand(M, E, device="cuda", generator=g).argsort(dim=1).float() * 0.125 - 2.0).to(torch.bfloat16)
+    w, ex, counts, base, pos, order = nat.moe_route(logits, k)
+    vals, ref_e = torch.topk(logits.float(), k, dim=-1)
+    assert torch.equal(ex.long(), ref_e)
+    torch.testing.assert_close(w, torch.softmax(vals, -1), rtol=1e-5, atol=1e-6)
+    flat = ref_e.reshape(-1)
+    ref_order = torch.sort(flat, stable=True).indices
+    assert torch.equal(order.long(), ref_order)
+    assert torch.equal(pos.long()[ref_order], torch.arange(M * k, device="cuda"))
+    ref_counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(counts.long(), ref_counts)
+    assert torch.equal(base.long(), torch.cat([ref_counts.new_zeros(1), ref_counts.cumsum(0)]))
+    x = _rand(M, D, seed=41)
+    rows = nat.moe_gather(x, order, k)
+    assert torch.equal(rows, x[ref_order // k])
+    y = _rand(M * k, D, seed=42)
+    out = nat.moe_combine(y, pos, w, M, k)
+    ref = (y.float()[pos.long()].view(M, k, D) * w[:, :, None]).sum(1)
+    assert _rel_err(out, ref) < 4e-3
+    d_out = _rand(M, D, seed=43)
+    dw = nat.moe_pair_dot(d_out, y, pos, k)
+    ref_dw = (d_out.float()[:, None, :] * y.float()[pos.long()].view(M, k, D)).sum(-1).reshape(-1)
+    torch.testing.assert_close(dw, ref_dw, rtol=1e-4, atol=1e-3)
+    scaled = nat.moe_gather(d_out, order, k, scale=w)
+    assert _rel_err(scaled, d_out.float()[ref_order // k] * w.reshape(-1)[ref_order][:, None]) < 4e-3
+    # gradient of softmax-over-top-k
+    dwt = torch.randn(M, k, device="cuda", generator=g)
+    dl = nat.moe_route_bwd(dwt, w, ex, M, E)
+    lf = logits.float().requires_grad_()
+    v2, e2 = torch.topk(lf, k, dim=-1)
+    (torch.softmax(v2, -1) * dwt).sum().backward()
+    assert _rel_err(dl, lf.grad) < 1e-2
+
+
+def test_grouped_gemm_row_scatter_epilogue(nat):
+    """Grouped GEMM whose epilogue stores each output row at a looked-up (buffer, row): two local buffers
+    stand in for two ranks; rows flagged -1 are dropped."""
+    import ctypes
+    E, N, K = 3, 256, 128
+    counts = [70, 0, 130]
+    R = sum(counts)
+    x, w = _rand(R + 16, K, seed=44), _rand(E, N, K, scale=0.1, seed=45)      # 16 trailing rows belong to no expert
+    rs = torch.tensor([0, 70, 70, 200], dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(46)
+    perm = torch.randperm(R, device="cuda", generator=g)
+    dest_rank = (perm % 2).to(torch.int32)
+    dest_row = (perm // 2).to(torch.int64)
+    dest_rank[5] = -1
+    dest_rank = torch.cat([dest_rank, dest_rank.new_full((16,), -1)])
+    dest_row = torch.cat([dest_row, dest_row.new_zeros(16)])
+    bufs = [torch.zeros(R // 2, N, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    ptrs = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+    nat.grouped_gemm_nt_scatter(x, w, nat.DeviceCounts(rs, R), dest_rank, dest_row, ptrs, 2, R // 2)
+    ref = torch.zeros(2, R // 2, N, device="cuda")
+    r = 0
+    for e, c in enumerate(counts):
+        for i in range(r, r + c):
+            if int(dest_rank[i]) >= 0:
+                ref[int(dest_rank[i]), int(dest_row[i])] = x[i].float() @ w[e].float().t()
+        r += c
+    for b in range(2):
+        assert _rel_err(bufs[b], ref[b]) < 6e-3

@@ -18,7 +18,7 @@
 //      where the product needs their transpose), so nothing is transposed.
 //      Two softmax warpgroups (one thread per query row, half of the KV columns
 //      each) turn S, dP into P, dS; dQ tiles are added to an fp32 buffer with
-//      vector reductions because several KV tiles contribute to one query row.
+//      TMA reduce-add tile stores because several KV tiles contribute to one query row.
 //      For hd = 64 the next step's S / dP MMAs are issued while the softmax
 //      warps still work on the current step.
 //   3. dq (fp32, [B,Hq,T,hd]) -> bf16 into dqkv.
@@ -52,7 +52,9 @@ struct AttnBwdCfg {
   static constexpr int OFF_DO = OFF_Q + STAGES * TILE_BYTES;
   static constexpr int OFF_P = OFF_DO + STAGES * TILE_BYTES;
   static constexpr int OFF_DS = OFF_P + PD_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + PD_BYTES;
+  static constexpr int OFF_DQS = OFF_DS + PD_BYTES;      // dQ staging: one [32 rows][32 fp32] swizzled box per softmax warp
+  static constexpr int DQS_BYTES = 8 * 4096;
+  static constexpr int OFF_BAR = OFF_DQS + DQS_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
   static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
   static constexpr uint32_t DQ_COL = HD == 64 ? 384 : 0;  // hd 128: dQ reuses the S columns
@@ -80,7 +82,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 }
 
 __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int B, int T,
-                                       int Hq, int heads_total, int hd) {
+                                       int Hq, int heads_total, int hd, float scale) {
   const int vec = hd / 8;
   const long long total = (long long)B * Hq * T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -90,19 +92,16 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bf
     const int h = (int)(r % Hq); const long long b = r / Hq;
     const float4 a = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8);
     const float4 c = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8 + 4);
-    uint4 out = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(c.x, c.y), pack_bf16(c.z, c.w));
+    uint4 out = make_uint4(pack_bf16(a.x * scale, a.y * scale), pack_bf16(a.z * scale, a.w * scale),
+                           pack_bf16(c.x * scale, c.y * scale), pack_bf16(c.z * scale, c.w * scale));
     *reinterpret_cast<uint4*>(dqkv + ((b * T + t) * heads_total + h) * (long long)hd + v * 8) = out;
   }
-}
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 template <int HD>
 __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams p) {
   using C = AttnBwdCfg<HD>;
   constexpr int KB = HD / 64;
   constexpr uint32_t TMEM_COLS = 512;
@@ -130,6 +129,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
     tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_dq);
   }
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -224,20 +224,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     constexpr float LOG2E = 1.4426950408889634f;
     bool ok = true;
 
+    // dQ tile of step `it` -> fp32 accumulator in global memory. Each warp turns its [32 rows][HD/2 columns]
+    // part into swizzled [32][32 fp32] boxes in shared memory and one lane hands them to the TMA unit as
+    // reduce-add tile stores (several KV tiles add into the same query rows), so the SM issues one bulk
+    // operation per 4 KB instead of 256 vector atomics.
+    uint8_t* stg = sal + C::OFF_DQS + (warp - 2) * 4096;
+    const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 2) * 4096;
     auto flush_dq = [&](int it) {
-      // this thread: query row `row` of step `it`, columns [half*HD/2, +HD/2)
       const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
-      const int t_row = qi * AB_TILE + row;
-      float* dst = p.dq_acc + (((long long)b * p.Hq + hq) * p.T + t_row) * HD + half * (HD / 2);
+      const int y0 = qi * AB_TILE + q4 * 32;                 // first of this warp's 32 query rows
 #pragma unroll
       for (int c = 0; c < HD / 2; c += 32) {
         uint32_t r[32];
         tmem_ld32(t_lane + C::DQ_COL + half * (HD / 2) + c, r);
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging box free again
+        __syncwarp();
         tmem_ld_wait();
-        if (t_row < p.T) {
+        uint8_t* rowp = stg + lane * 128;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(dst + c + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (y0 < p.T)
+            asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                         ::"l"((uint64_t)&tm_dq), "r"(stg_s), "r"(half * (HD / 2) + c), "r"(y0), "r"(b * p.Hq + hq) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
       tc_fence_before();
@@ -271,8 +284,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             if (col > row) p0 = 0.f;
             if (col + 1 > row) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(dp[i]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dp[i + 1]) - dlt) * p.scale;
+          const float d0 = p0 * (__uint_as_float(dp[i]) - dlt);        // the softmax scale is applied once, when
+          const float d1 = p1 * (__uint_as_float(dp[i + 1]) - dlt);    // dQ and dK leave their accumulators
           pp[(c + i) >> 1] = pack_bf16(p0, p1);
           dd[(c + i) >> 1] = pack_bf16(d0, d1);
         }
@@ -314,6 +327,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
+          const float osc = which == 0 ? 1.f : p.scale;
           const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
           __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * HD + half * (HD / 2);
 #pragma unroll
@@ -325,10 +339,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                v.y = pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-                v.z = pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-                v.w = pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                v.x = pack_bf16(__uint_as_float(r[i]) * osc, __uint_as_float(r[i + 1]) * osc);
+                v.y = pack_bf16(__uint_as_float(r[i + 2]) * osc, __uint_as_float(r[i + 3]) * osc);
+                v.z = pack_bf16(__uint_as_float(r[i + 4]) * osc, __uint_as_float(r[i + 5]) * osc);
+                v.w = pack_bf16(__uint_as_float(r[i + 6]) * osc, __uint_as_float(r[i + 7]) * osc);
                 *reinterpret_cast<uint4*>(dst + c + i) = v;
               }
             }
@@ -336,6 +350,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         }
       }
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // dQ reductions have left shared memory and landed
   }
 
   tc_fence_before();
@@ -344,7 +359,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 }
 
 template <int HD>
-static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const AttnBwdParams& p, cudaStream_t st) {
+static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mdq, const AttnBwdParams& p,
+                      cudaStream_t st) {
   using C = AttnBwdCfg<HD>;
   static bool configured = false;
   if (!configured) {
@@ -353,7 +369,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const AttnB
     configured = true;
   }
   dim3 grid((p.T + AB_TILE - 1) / AB_TILE, p.B * p.Hkv);
-  attn_bwd_kernel<HD><<<grid, AB_THREADS, C::TOTAL, st>>>(mq, mdo, p);
+  attn_bwd_kernel<HD><<<grid, AB_THREADS, C::TOTAL, st>>>(mq, mdo, mdq, p);
   count_launch();
   return launch_status();
 }
@@ -381,12 +397,20 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   e = make_qkv_map(&mdo, dout, B, T, Hq, hd, AB_TILE);
   if (e) return e;
   AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word()};
-  e = hd == 64 ? launch_bwd<64>(mq, mdo, p, st) : launch_bwd<128>(mq, mdo, p, st);
+  CUtensorMap mdq;                                     // fp32 [B*Hq, T, hd] accumulator, box 32 x 32 x 1
+  {
+    uint64_t dims[3] = {(uint64_t)hd, (uint64_t)T, (uint64_t)B * Hq};
+    uint64_t strides[2] = {(uint64_t)hd * 4, (uint64_t)T * hd * 4};
+    uint32_t box[3] = {32, 32, 1};
+    e = make_tmap_f32(&mdq, dq_acc, 3, dims, strides, box);
+    if (e) return e;
+  }
+  e = hd == 64 ? launch_bwd<64>(mq, mdo, mdq, p, st) : launch_bwd<128>(mq, mdo, mdq, p, st);
   if (e) return e;
   long long items = rows * (hd / 8);
   int cb = (int)((items + 255) / 256);
   if (cb > num_sms() * 16) cb = num_sms() * 16;
-  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd);
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale);
   count_launch();
   return launch_status();
 }

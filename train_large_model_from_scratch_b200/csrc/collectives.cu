@@ -67,6 +67,19 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int n, int epoch, 
   flag_exchange(flags, rank, n, epoch, true, status, 40);
 }
 
+// Waits until *flag >= expect or `limit_ns` elapse; a timeout is reported through the status word
+// (site 42) and the kernel returns normally, so the context and the stream stay usable.
+__global__ void wait_flag_kernel(const int* flag, int expect, unsigned long long limit_ns, unsigned int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while ((int)(ld_acquire_sys(flag) - expect) < 0) {
+    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) {
+      report_status(status, (42u << 8) | 1u);
+      break;
+    }
+  }
+}
+
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
   float4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -192,6 +205,15 @@ static PeerPtrs to_ptrs(void* const* src, int n) {
 TLM_API int tlm_peer_barrier(void* const* flag_ptrs, int rank, int n, int epoch, cudaStream_t st) {
   if (n > MAX_PEERS) return -6;
   peer_barrier_kernel<<<1, 32, 0, st>>>(to_ptrs(flag_ptrs, n), rank, n, epoch, status_word());
+  count_launch();
+  return launch_status();
+}
+
+// Stream-ordered bounded wait on a device-visible int32 flag (one thread). Work queued behind it starts when
+// the flag reaches `expect`, or after `limit_ns` with the timeout recorded in the device status word.
+TLM_API int tlm_wait_flag(const int* flag, int expect, unsigned long long limit_ns, cudaStream_t st) {
+  if (flag == nullptr || limit_ns == 0 || limit_ns > 10000000000ull) return -6;
+  wait_flag_kernel<<<1, 1, 0, st>>>(flag, expect, limit_ns, status_word());
   count_launch();
   return launch_status();
 }

@@ -253,6 +253,10 @@ EncodeTiledFn get_encode_tiled();
 int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                    const uint32_t* box);
 
+// same for fp32 elements (inner box extent <= 32 elements with the 128-byte swizzle)
+int make_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                  const uint32_t* box);
+
 int num_sms();
 
 // 4-D bf16 map over a packed [B, T, heads, hd] tensor: dims (hd, heads, T, B), box (64, 1, box_rows, 1).

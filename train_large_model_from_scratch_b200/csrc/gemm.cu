@@ -68,6 +68,14 @@ struct GemmParams {
   int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot;
   const float* cosT;        // [rows_per_batch, hd]
   const float* sinT;
+  // Row-scatter epilogue (bf16 store, grouped rows): output row r is not written to C but to
+  //   rs_dst[rs_rank[r]] + rs_row[r] * ldc   (rows with rs_rank[r] < 0 are dropped).
+  // This is the expert-parallel combine: the down-projection's accumulator goes straight to the
+  // token owner's buffer (peer-mapped addresses, plain 16-byte stores). rs_rank == nullptr: off.
+  const int* rs_rank;
+  const long long* rs_row;
+  void* rs_dst[MAX_HEAD_DST];
+  long long rs_rows;        // rows of a destination buffer (stores outside are refused)
 };
 
 struct TileCoord {
@@ -390,15 +398,27 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           }
         }
       } else {
+      __nv_bfloat16* scat = nullptr;                 // row-scatter destination of this thread's row
+      bool row_live = row_ok;
+      if (EPI == EPI_BF16 && p.rs_rank != nullptr) {
+        const int dr = row_ok ? p.rs_rank[row] : -1;
+        const long long drow = dr >= 0 ? p.rs_row[row] : -1;
+        if (dr >= 0 && dr < MAX_HEAD_DST && drow >= 0 && drow < p.rs_rows)
+          scat = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[dr]) + drow * p.ldc;
+        else if (dr >= 0)
+          report_status(p.status, (61u << 8) | 1u);
+        row_live = scat != nullptr;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c, r);
         tmem_ld_wait();
         const int col = t.n0 + c;
-        if (row_ok && col < p.N) {
+        if (row_live && col < p.N) {
           if (EPI == EPI_BF16) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
+            __nv_bfloat16* out = scat != nullptr ? scat + col
+                                                 : reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col + j < p.N) {
@@ -636,6 +656,31 @@ TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const i
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
   return dispatch(false, b_mn != 0, epi, ma, mb, p, tiles, stream);
+}
+
+// Same as tlm_gemm_grouped_rows with a bf16 store, but output row r goes to dst_ptrs[dest_rank[r]] row dest_row[r]
+// (row pitch ldc; rows with dest_rank < 0 are dropped): the expert-parallel combine done by the GEMM epilogue.
+TLM_API int tlm_gemm_grouped_rows_scatter(const void* A, const void* B, const int* row_start, int groups, int M, int N,
+                                          int K, long long lda, long long ldb, long long b_group_stride, long long ldc,
+                                          int b_mn, int max_rows_per_group, const int* dest_rank,
+                                          const long long* dest_row, void* const* dst_ptrs, int n_dst,
+                                          long long dst_rows, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (n_dst < 1 || n_dst > MAX_HEAD_DST || dest_rank == nullptr || dest_row == nullptr || ldc % 8 != 0) return -6;
+  Operand oa{A, M, K, lda, false, 0, 0}, ob{B, N, K, ldb, b_mn != 0, groups, b_group_stride};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.status = status_word();
+  p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  p.rs_rank = dest_rank; p.rs_row = dest_row; p.rs_rows = dst_rows;
+  for (int i = 0; i < n_dst; ++i) p.rs_dst[i] = dst_ptrs[i];
+  int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
+  return dispatch(false, b_mn != 0, EPI_BF16, ma, mb, p, tiles, stream);
 }
 
 // Grouped wgrad: C[g] ([M,N] fp32, `c_group_stride` apart) += A[rows_g, M]^T * B[rows_g, N]

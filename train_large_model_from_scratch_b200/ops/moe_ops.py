@@ -77,8 +77,87 @@ def route(logits: torch.Tensor, k: int):
 
 def aux_loss(logits: torch.Tensor, experts: torch.Tensor, num_experts: int) -> torch.Tensor:
     probs = torch.softmax(logits.float(), dim=-1).mean(0)
-    frac = torch.bincount(experts.reshape(-1), minlength=num_experts).float() / experts.numel()
+    frac = _count(experts.reshape(-1), num_experts).float() / experts.numel()
     return num_experts * (frac.detach() * probs).sum()
+
+
+# --------------------------------------------------------------------------- CUDA path: routing and row movement as kernels
+class _RouteDevice(torch.autograd.Function):
+    """Top-k routing on the device (`csrc/moe.cu`): no sort, no host sync."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        weights, experts, counts, base, pos, order = native.moe_route(logits, k)
+        ctx.save_for_backward(weights, experts)
+        ctx.shape = logits.shape
+        for t in (experts, counts, base, pos, order):
+            ctx.mark_non_differentiable(t)
+        return weights, experts, counts, base, pos, order
+
+    @staticmethod
+    def backward(ctx, dw, *unused):
+        weights, experts = ctx.saved_tensors
+        return native.moe_route_bwd(dw, weights, experts, ctx.shape[0], ctx.shape[1]), None
+
+
+class _GatherDevice(torch.autograd.Function):
+    """tokens `[M, D]` -> expert-major pair rows `[M*k, D]`; backward sums each token's k rows."""
+
+    @staticmethod
+    def forward(ctx, x, order, pos, k):
+        ctx.save_for_backward(pos)
+        ctx.k, ctx.M = k, x.shape[0]
+        return native.moe_gather(x.contiguous(), order, k)
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        (pos,) = ctx.saved_tensors
+        return native.moe_combine(d_rows.contiguous(), pos, None, ctx.M, ctx.k), None, None, None
+
+
+class _CombineDevice(torch.autograd.Function):
+    """`out[t] = sum_s w[t,s] * y[pos[t,s]]`; backward gives `d_y` (expert-major rows) and `d_w`."""
+
+    @staticmethod
+    def forward(ctx, y, weights, order, pos, k):
+        ctx.save_for_backward(y, weights, order, pos)
+        ctx.k = k
+        return native.moe_combine(y.contiguous(), pos, weights, weights.shape[0], k)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        y, weights, order, pos = ctx.saved_tensors
+        d_out = d_out.contiguous()
+        d_y = native.moe_gather(d_out, order, ctx.k, scale=weights)
+        dw = native.moe_pair_dot(d_out, y.contiguous(), pos, ctx.k).view_as(weights)
+        return d_y, dw, None, None, None
+
+
+def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_group, ep_size, aux_coef, layer_key):
+    """bf16 CUDA path without token dropping. Nothing here reads a device value on the host: the expert
+    row ranges go to the grouped GEMMs as a device array, and with expert parallelism the rows travel
+    through peer memory (`parallel.expert_parallel.peer`)."""
+    weights, experts, counts, base, pos, order = _RouteDevice.apply(logits.contiguous(), k)
+    aux = aux_loss(logits, experts.long(), num_experts) * aux_coef if aux_coef > 0.0 else None
+    P = order.numel()
+    if ep_size == 1:
+        per_expert = native.DeviceCounts(base, P)
+        local_x = _GatherDevice.apply(x, order, pos, k)
+    else:
+        from ..parallel.expert_parallel import peer as ep_peer
+        pm = ep_peer.PeerMoE.get(ep_group, num_experts)
+        plan = pm.plan(counts, experts.view(-1)[order.long()].long())
+        per_expert = native.DeviceCounts(plan["row_start"], plan["R"])
+        local_x = ep_peer.dispatch_tokens(x, pm, plan, order, pos, k, layer_key)
+    gate = grouped_linear(local_x, w_gate, per_expert)
+    up = grouped_linear(local_x, w_up, per_expert)
+    act = F_ops.swiglu(torch.cat([gate, up], dim=-1))
+    if ep_size == 1:
+        y = grouped_linear(act, w_down, per_expert)
+        out = _CombineDevice.apply(y, weights, order, pos, k)
+    else:
+        out = ep_peer.down_combine(act, w_down, weights, pm, plan, per_expert, order, pos, k, layer_key)
+    return out, aux
 
 
 def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_group, ep_size: int,
@@ -90,6 +169,10 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     expert parallelism the rows travel through `parallel.expert_parallel.peer`."""
     M, D = x.shape
     E_local = num_experts // ep_size
+    if (x.is_cuda and x.dtype == torch.bfloat16 and capacity_factor <= 0.0 and num_experts <= 256 and k <= 8
+            and D % 8 == 0 and (ep_size == 1 or (_peer_enabled() and ep_size <= 8))):
+        return _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_group, ep_size, aux_coef,
+                                   layer_key)
     weights, experts = route(logits, k)                                    # [M,k]
     aux = aux_loss(logits, experts, num_experts) * aux_coef if aux_coef > 0.0 else None
 
@@ -108,20 +191,7 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     sorted_x = x.index_select(0, token_of)                                 # gather (bwd: index_add)
     counts = _count(flat_e[order], num_experts).view(ep_size, E_local)
 
-    on_device = x.is_cuda and x.dtype == torch.bfloat16 and capacity_factor <= 0.0
-    peer_plan = None
-    if ep_size > 1 and on_device and _peer_enabled():
-        from ..parallel.expert_parallel import peer as ep_peer
-        pm = ep_peer.PeerMoE.get(ep_group, num_experts)
-        peer_plan = pm.plan(counts.view(-1), flat_e[order])
-        local_x = ep_peer.dispatch(sorted_x, pm, peer_plan, layer_key)
-        per_expert = native.DeviceCounts(peer_plan["row_start"], peer_plan["R"])
-    elif ep_size == 1 and on_device:
-        c = counts.view(-1)
-        row_start = torch.cat([c.new_zeros(1), torch.cumsum(c, 0)]).to(torch.int32)
-        local_x = sorted_x
-        per_expert = native.DeviceCounts(row_start, sorted_x.shape[0])
-    elif ep_size > 1:
+    if ep_size > 1:
         recv_counts = exchange_counts(counts, ep_group)                    # [src, E_local]
         both = torch.stack([counts, recv_counts]).tolist()                 # one host sync for both
         send_c, recv_c = both
@@ -141,9 +211,7 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     act = F_ops.swiglu(torch.cat([gate, up], dim=-1))
     y = grouped_linear(act, w_down, per_expert)
 
-    if peer_plan is not None:
-        y = ep_peer.combine(y, pm, peer_plan, layer_key)
-    elif ep_size > 1:
+    if ep_size > 1:
         inv = torch.empty_like(regroup)
         inv[regroup] = torch.arange(regroup.numel(), device=x.device)
         y = ep_all_to_all(y.index_select(0, inv), recv_splits, send_splits, ep_group)

@@ -66,12 +66,20 @@ _SIGS = {
     "tlm_attn_fwd_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P]),
     "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "tlm_peer_barrier": (_I, [_P, _I, _I, _I, _P]),
+    "tlm_wait_flag": (_I, [_P, _I, _c.c_ulonglong, _P]),
     "tlm_reduce_scatter_blocks": (_I, []),
     "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
     "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P]),
     "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),
-    "tlm_peer_scatter_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _LL, _LL, _P]),
+    "tlm_peer_scatter_rows": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _P, _LL, _LL, _P]),
+    "tlm_moe_route_blocks": (_I, [_I]),
+    "tlm_moe_route": (_I, [_P, _LL, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "tlm_moe_route_bwd": (_I, [_P, _P, _P, _P, _LL, _I, _I, _P]),
+    "tlm_moe_gather": (_I, [_P, _P, _I, _P, _P, _LL, _I, _P]),
+    "tlm_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "tlm_moe_pair_dot": (_I, [_P, _P, _P, _P, _LL, _I, _I, _P]),
+    "tlm_gemm_grouped_rows_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _P, _P, _P, _I, _LL, _P]),
     "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P]),
 }
 
@@ -117,6 +125,13 @@ def raise_on_device_status() -> None:
     st = take_device_status()
     if st:
         raise NativeError(f"a kernel timed out waiting at site {st >> 8} (detail {st & 0xff})")
+
+
+def wait_flag(flag: torch.Tensor, expect: int, limit_s: float) -> None:
+    """Queue a bounded device-side wait for `flag[0] >= expect` (int32 tensor) on the current stream.
+    If the limit passes first the kernel returns anyway and `take_device_status()` reports site 42."""
+    assert flag.dtype == torch.int32 and flag.is_cuda
+    _check(lib().tlm_wait_flag(flag.data_ptr(), expect, int(limit_s * 1e9), _stream()), "wait_flag")
 
 
 # --------------------------------------------------------------------------- GEMM
@@ -382,3 +397,71 @@ def grouped_gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor, 
     rs, _ = _grouping(counts, dy.device)
     _check(lib().tlm_gemm_grouped_k(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), rs.data_ptr(), E, R, N, K, lda, ldb,
                                     K, N * K, EPI_F32_ACC, _stream()), "grouped_gemm_tn_accum")
+
+
+def grouped_gemm_nt_scatter(x: torch.Tensor, weight: torch.Tensor, counts, dest_rank: torch.Tensor,
+                            dest_row: torch.Tensor, dst_ptrs, n_dst: int, dst_rows: int) -> None:
+    """Like `grouped_gemm_nt`, but output row r is stored into `dst[dest_rank[r]][dest_row[r], :]`
+    (bf16 `[dst_rows, N]` buffers given by device address; rows with `dest_rank < 0` are dropped)."""
+    R, K, lda = _rows(x)
+    E, N, K2 = weight.shape
+    assert K == K2 and weight.is_contiguous() and dest_rank.dtype == torch.int32 and dest_row.dtype == torch.int64
+    if R == 0:
+        return
+    rs, bound = _grouping(counts, x.device)
+    _check(lib().tlm_gemm_grouped_rows_scatter(x.data_ptr(), weight.data_ptr(), rs.data_ptr(), E, R, N, K, lda, K, N * K,
+                                               N, 0, bound, dest_rank.data_ptr(), dest_row.data_ptr(), dst_ptrs, n_dst,
+                                               dst_rows, _stream()), "grouped_gemm_nt_scatter")
+
+
+# --------------------------------------------------------------------------- MoE routing and row movement
+def moe_route(logits: torch.Tensor, k: int):
+    """Top-k routing of `[M, E]` bf16 logits on the device. Returns
+    `(weights [M,k] fp32, experts [M,k] int32, counts [E] int32, base [E+1] int32, pos [M*k] int32,
+    order [M*k] int32)`: `pos[p]` is the place of pair p = token*k + slot in expert-major / token-minor
+    order, `order` its inverse, `base[e]` the first place of expert e."""
+    M, E = logits.shape
+    assert logits.dtype == torch.bfloat16 and logits.stride(1) == 1
+    dev = logits.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    weights = torch.empty(M, k, dtype=torch.float32, device=dev)
+    experts = torch.empty(M, k, **i32)
+    hist = torch.empty(max(1, lib().tlm_moe_route_blocks(M)) * E, **i32)
+    counts, base = torch.empty(E, **i32), torch.empty(E + 1, **i32)
+    pos, order = torch.empty(M * k, **i32), torch.empty(M * k, **i32)
+    _check(lib().tlm_moe_route(logits.data_ptr(), logits.stride(0), M, E, k, weights.data_ptr(), experts.data_ptr(),
+                               hist.data_ptr(), counts.data_ptr(), base.data_ptr(), pos.data_ptr(), order.data_ptr(),
+                               _stream()), "moe_route")
+    return weights, experts, counts, base, pos, order
+
+
+def moe_route_bwd(dw: torch.Tensor, w: torch.Tensor, experts: torch.Tensor, M: int, E: int) -> torch.Tensor:
+    d_logits = torch.zeros(M, E, dtype=torch.bfloat16, device=w.device)
+    _check(lib().tlm_moe_route_bwd(dw.contiguous().data_ptr(), w.data_ptr(), experts.data_ptr(), d_logits.data_ptr(), E, M,
+                                   w.shape[1], _stream()), "moe_route_bwd")
+    return d_logits
+
+
+def moe_gather(x: torch.Tensor, order: torch.Tensor, k: int, scale: torch.Tensor | None = None) -> torch.Tensor:
+    """`out[i] = scale[order[i]] * x[order[i] // k]` (bf16 rows)."""
+    P, D = order.numel(), x.shape[1]
+    out = torch.empty(P, D, dtype=torch.bfloat16, device=x.device)
+    _check(lib().tlm_moe_gather(x.data_ptr(), order.data_ptr(), k, _ptr(scale), out.data_ptr(), P, D, _stream()), "moe_gather")
+    return out
+
+
+def moe_combine(y: torch.Tensor, pos: torch.Tensor, w: torch.Tensor | None, M: int, k: int) -> torch.Tensor:
+    """`out[t] = sum_s w[t,s] * y[pos[t*k+s]]` (`w=None`: plain sum)."""
+    D = y.shape[1]
+    out = torch.empty(M, D, dtype=torch.bfloat16, device=y.device)
+    _check(lib().tlm_moe_combine(y.data_ptr(), pos.data_ptr(), _ptr(w), out.data_ptr(), M, D, k, _stream()), "moe_combine")
+    return out
+
+
+def moe_pair_dot(d_out: torch.Tensor, y: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
+    """`dw[p] = <d_out[p // k], y[pos[p]]>` -> `[P]` fp32."""
+    P, D = pos.numel(), y.shape[1]
+    dw = torch.empty(P, dtype=torch.float32, device=y.device)
+    _check(lib().tlm_moe_pair_dot(d_out.data_ptr(), y.data_ptr(), pos.data_ptr(), dw.data_ptr(), P, D, k, _stream()),
+           "moe_pair_dot")
+    return dw

@@ -108,11 +108,15 @@ class PeerMoE:
                 "n_recv": n_recv.contiguous(), "back_rank": back_rank, "back_row": back_row.contiguous(),
                 "P": P, "R": R}
 
-    def scatter(self, src: torch.Tensor, dest_rank, dest_row, dst, n_ptr, n_max: int) -> None:
+    def scatter(self, src: torch.Tensor, dest_rank, dest_row, dst, n_ptr, n_max: int, src_idx=None, src_div: int = 1,
+                row_scale=None) -> None:
+        """Row i (< *n_ptr) of the route: `dst[dest_rank[i]][dest_row[i]] = scale * src[j // src_div]`,
+        `j = src_idx[i]` (or i), `scale = row_scale[j]` (or 1); then the flag barrier."""
         t, peer = dst
         native._check(native.lib().tlm_peer_scatter_rows(
-            src.data_ptr(), None, dest_rank.data_ptr(), dest_row.data_ptr(), peer.ptr_array, self.ep, src.shape[1],
-            native._ptr(n_ptr), n_max, t.shape[0], native._stream()), "peer_scatter_rows")
+            src.data_ptr(), native._ptr(src_idx), src_div, native._ptr(row_scale), dest_rank.data_ptr(),
+            dest_row.data_ptr(), peer.ptr_array, self.ep, src.shape[1], native._ptr(n_ptr), n_max, t.shape[0],
+            native._stream()), "peer_scatter_rows")
         self.barrier()
 
 
@@ -158,3 +162,69 @@ def dispatch(x_sorted, pm, plan, key):
 
 def combine(y_local, pm, plan, key):
     return _Combine.apply(y_local, pm, plan, key)
+
+
+class _DispatchTokens(torch.autograd.Function):
+    """tokens `[M, D]` -> expert-grouped rows on the experts' owners `[R, D]` in one kernel: row
+    `order[i] // k` of `x` is read and stored straight into the destination rank's buffer (no
+    sorted copy of the tokens is made). Backward: the rows' gradients return to the token owner in
+    sorted-pair order and are summed over each token's k slots."""
+
+    @staticmethod
+    def forward(ctx, x, pm: PeerMoE, plan: dict, order, pos, k: int, key):
+        dst = pm.buffer((key, "disp"), plan["R"], x.shape[1])
+        pm.scatter(x.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"], src_idx=order, src_div=k)
+        ctx.pm, ctx.plan, ctx.key, ctx.k, ctx.M = pm, plan, key, k, x.shape[0]
+        ctx.save_for_backward(pos)
+        return dst[0]
+
+    @staticmethod
+    def backward(ctx, d_local):
+        pm, plan = ctx.pm, ctx.plan
+        (pos,) = ctx.saved_tensors
+        dst = pm.buffer((ctx.key, "disp_bwd"), plan["P"], d_local.shape[1])
+        pm.scatter(d_local.contiguous(), plan["back_rank"], plan["back_row"], dst, plan["n_recv"], plan["R"])
+        return native.moe_combine(dst[0], pos, None, ctx.M, ctx.k), None, None, None, None, None, None
+
+
+class _DownCombine(torch.autograd.Function):
+    """Expert down-projection + combine: the grouped GEMM's epilogue stores every output row into the
+    token owner's buffer (`csrc/gemm.cu`, row-scatter epilogue), then the owner forms
+    `out[t] = sum_s w[t,s] * row(t,s)`. Backward: weight gradients from the received rows, and
+    `w * d_out[token]` is pushed to the experts' owners, where the down-projection's own backward runs."""
+
+    @staticmethod
+    def forward(ctx, act, w_down, weights, pm: PeerMoE, plan: dict, per_expert, order, pos, k: int, key):
+        D = w_down.shape[1]
+        comb = pm.buffer((key, "comb"), plan["P"], D)
+        native.grouped_gemm_nt_scatter(act, w_down, per_expert, plan["back_rank"], plan["back_row"],
+                                       comb[1].ptr_array, pm.ep, plan["P"])
+        pm.barrier()
+        M = weights.shape[0]
+        out = native.moe_combine(comb[0], pos, weights, M, k)
+        ctx.pm, ctx.plan, ctx.key, ctx.k, ctx.per_expert, ctx.w_down = pm, plan, key, k, per_expert, w_down
+        ctx.save_for_backward(act, weights, order, pos, comb[0])
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from ...ops.functional import _main_grad
+        pm, plan, k = ctx.pm, ctx.plan, ctx.k
+        act, weights, order, pos, comb = ctx.saved_tensors
+        d_out = d_out.contiguous()
+        dw = native.moe_pair_dot(d_out, comb, pos, k).view_as(weights)
+        dst = pm.buffer((ctx.key, "comb_bwd"), plan["R"], d_out.shape[1])
+        pm.scatter(d_out, plan["send_rank"], plan["send_row"], dst, None, plan["P"], src_idx=order, src_div=k,
+                   row_scale=weights)
+        d_y = dst[0]
+        native.grouped_gemm_tn_accum(d_y, act, _main_grad(ctx.w_down), ctx.per_expert)
+        d_act = native.grouped_gemm_nn(d_y, ctx.w_down, ctx.per_expert)
+        return d_act, None, dw, None, None, None, None, None, None, None
+
+
+def dispatch_tokens(x, pm, plan, order, pos, k, key):
+    return _DispatchTokens.apply(x, pm, plan, order, pos, k, key)
+
+
+def down_combine(act, w_down, weights, pm, plan, per_expert, order, pos, k, key):
+    return _DownCombine.apply(act, w_down, weights, pm, plan, per_expert, order, pos, k, key)

@@ -67,6 +67,8 @@ _FLAG_TABLE: list[tuple[str, list[tuple[str, dict]]]] = [
         ("--ddp_gradient_as_bucket_view", dict(action=_S)),
         ("--use_distributed_optimizer", dict(action=_S, help="ZeRO-1 optimizer-state sharding")),
         ("--grad_wire_dtype", dict(type=str, default="fp32", choices=["bf16", "fp32"], help="(added) dtype of gradients on the wire")),
+        ("--heartbeat_timeout_s", dict(type=float, default=0.0, help="(added) > 0: ranks exchange heartbeats between steps; a rank silent for this long fails the job")),
+        ("--dist_timeout_s", dict(type=float, default=1800.0, help="(added) process-group timeout for collectives")),
     ]),
     ("model", [
         ("--block_size", dict(type=int, default=4096)),

@@ -12,7 +12,8 @@ Differences, all deliberate:
     crashes because it is missing, `training/trainer.py:398`).
   * Extra optional knobs with reference-parity defaults: `moe_aux_loss_coef`
     (0.0 = no auxiliary loss, as in the reference), `moe_capacity_factor`
-    (0.0 = dropless), `rope_variant` ("reference"), `grad_wire_dtype`.
+    (0.0 = dropless), `rope_variant` ("reference"), `grad_wire_dtype`,
+    `heartbeat_timeout_s` (0 = off), `dist_timeout_s`.
 """
 from __future__ import annotations
 
@@ -99,6 +100,9 @@ class ParallelConfig:
     # "bf16": gradients cross NVLink as bf16 and are summed in fp32;
     # "fp32": full-precision wire, used for parity runs.
     grad_wire_dtype: str = "fp32"
+    # > 0: host-side heartbeats between steps (`utils.health`); a peer silent for this long fails the job
+    heartbeat_timeout_s: float = 0.0
+    dist_timeout_s: float = 1800.0
 
 
 @dataclass(frozen=True)

@@ -105,6 +105,8 @@ class Trainer:
             kwargs = {}
             if self.use_cuda and backend == "nccl":
                 kwargs["device_id"] = torch.device("cuda", self.local_rank)
+            import datetime
+            kwargs["timeout"] = datetime.timedelta(seconds=float(config.parallel.dist_timeout_s))
             dist.init_process_group(backend=backend, init_method=config.parallel.init_method, **kwargs)
             self._owns_pg = True
         if self.use_cuda:
@@ -121,6 +123,10 @@ class Trainer:
         self.sp_group, self.sp_rank, self.sp_world_size = ps.get_sp_group(), ps.get_sp_rank(), ps.get_sp_world_size()
         self.dp_sp_group, self.dp_sp_rank, self.dp_sp_world_size = (
             ps.get_dp_sp_group(), ps.get_dp_sp_rank(), ps.get_dp_sp_world_size())
+        self.heartbeat = None
+        if self.world_size > 1 and config.parallel.heartbeat_timeout_s > 0:
+            from ..utils.health import Heartbeat
+            self.heartbeat = Heartbeat(self.rank, self.world_size, config.parallel.heartbeat_timeout_s)
 
     def _init_dataset(self, config: Config) -> None:
         d, t = config.data, config.train
@@ -308,7 +314,20 @@ class Trainer:
         (optional) is a list of `grad_accum_steps` dicts with full-sequence
         `input_ids` / `labels`; by default the trainer's own loader is used."""
         self.one_step_results = {}
-        self._one_training_step(self.config, step, batches)
+        hb = self.heartbeat
+        if hb is not None:
+            # learn about a dead or stalled peer on the host, before any kernel or collective of this step
+            hb.enter_step(step)
+        try:
+            self._one_training_step(self.config, step, batches)
+        except BaseException as e:
+            if hb is not None:
+                hb.announce_failure(f"{type(e).__name__}: {e}")
+            raise
+        if hb is not None:
+            if self.use_cuda:
+                torch.cuda.synchronize()
+            hb.beat(step)
         return self.one_step_results
 
     # ------------------------------------------------------------------ resume / save
@@ -398,14 +417,13 @@ class Trainer:
         write = tqdm.write if tqdm is not None else print
         measured_peak = get_measured_peak_flops()
         for step in bar:
-            self.one_step_results = {}
             t0 = time.time()
             last_step = step == max_steps - 1
             if self.use_cuda:
                 ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 ev0.record()
             with self.profiler_record_fn("training_step"):
-                self._one_training_step(cfg, step)
+                self.train_step(step)
             if self.use_cuda:
                 ev1.record()
                 torch.cuda.synchronize()
