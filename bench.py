@@ -35,7 +35,40 @@ REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 MODEL = dict(num_layer=16, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
              intermediate_size=4096, vocab_size=50304, block_size=4096)
 SEQ_LEN, MICRO_BATCH, GRAD_ACCUM = 4096, 8, 2
+SEP_SIZE, EXTRA_FLAGS = 1, []
+MODEL_NAME = "dense GPT 16L/1024/16q-8kv/SwiGLU-4096/vocab 50304 tied (0.30B params)"
 BASELINE_TOKENS_PER_S = None          # the reference publishes no number
+
+# Other configurations of the same benchmark (`--config`); "B" above is the headline one.
+#   C: the same model under Ulysses sequence parallelism over all GPUs, 4096 tokens per rank, micro-batch 1
+#   D: 0.3B-class MoE, 8 experts top-2, expert hidden 2048, SEP = number of GPUs (SP and EP share the group)
+#   E: 3B-class dense, head dim 128, DP x SEP = (N/2) x 2
+#   S: the reference's shipped debug_gpt_0.25b shape (12 layers, 32 query / 4 KV heads of dim 32)
+CONFIGS = {
+    "C": dict(model=MODEL, name="dense 0.30B, Ulysses sep=N, seq 4096 x N", seq_per_rank=4096, micro=1, ga=2,
+              sep="all"),
+    "D": dict(model=dict(num_layer=12, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                         intermediate_size=4096, vocab_size=50304, block_size=4096),
+              name="MoE 12L/1024/16q-8kv/8 experts top-2/expert hidden 2048", seq=4096, micro=4, ga=2, sep="all",
+              extra=["--use_moe", "--num_experts", "8", "--num_experts_per_tok", "2", "--moe_intermediate_size", "2048"]),
+    "E": dict(model=dict(num_layer=36, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8,
+                         intermediate_size=8192, vocab_size=50304, block_size=4096),
+              name="dense 36L/3072/24q-8kv hd128/SwiGLU-8192 (3.78B params)", seq=4096, micro=2, ga=2, sep=2),
+    "S": dict(model=dict(num_layer=12, hidden_size=1024, num_attention_heads=32, num_key_value_heads=4,
+                         intermediate_size=4096, vocab_size=50304, block_size=4096),
+              name="dense 12L/1024/32q-4kv hd32/SwiGLU-4096 (shipped debug_gpt_0.25b)", seq=4096, micro=8, ga=2, sep=1),
+}
+
+
+def _select_config(name: str, n_gpus: int) -> None:
+    global MODEL, SEQ_LEN, MICRO_BATCH, GRAD_ACCUM, SEP_SIZE, EXTRA_FLAGS, MODEL_NAME
+    if name == "B":
+        return
+    c = CONFIGS[name]
+    SEP_SIZE = n_gpus if c["sep"] == "all" else min(int(c["sep"]), n_gpus)
+    SEQ_LEN = c["seq_per_rank"] * SEP_SIZE if "seq_per_rank" in c else c["seq"]
+    MODEL = dict(c["model"], block_size=max(4096, SEQ_LEN))
+    MICRO_BATCH, GRAD_ACCUM, EXTRA_FLAGS, MODEL_NAME = c["micro"], c["ga"], list(c.get("extra", [])), c["name"]
 
 
 # --------------------------------------------------------------------------- clocks
@@ -127,16 +160,17 @@ def _timed(torch, dist, world, fn, steps):
 
 
 def _flags(n_gpus: int, steps_total: int, log_dir: str) -> list[str]:
-    tokens = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n_gpus
-    samples = MICRO_BATCH * GRAD_ACCUM * n_gpus * (steps_total + 4)
+    dp = n_gpus // SEP_SIZE
+    tokens = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * dp
+    samples = MICRO_BATCH * GRAD_ACCUM * dp * (steps_total + 4)
     f = ["--use_mock_data", "--mock_data_num_samples", str(samples), "--total_batch_size", str(tokens),
          "--batch_size", str(MICRO_BATCH), "--seq_len", str(SEQ_LEN), "--max_steps", str(steps_total + 4),
          "--warmup_steps", "2", "--max_lr", "6e-4", "--min_lr", "6e-5", "--weight_decay", "0.1",
-         "--grad_clip_value", "1.0", "--debug", "--sep_size", "1", "--use_distributed_optimizer", "--tied_lm_head",
+         "--grad_clip_value", "1.0", "--debug", "--sep_size", str(SEP_SIZE), "--use_distributed_optimizer", "--tied_lm_head",
          "--pin_memory", "--precision", "bf16", "--log_dir", log_dir, "--exp_name", "bench"]
     for k, v in MODEL.items():
         f += [f"--{k}", str(v)]
-    return f
+    return f + EXTRA_FLAGS
 
 
 def _result(impl, n, steps, warmup, ms_total, tokens_per_step, clocks, extra):
@@ -148,9 +182,10 @@ def _result(impl, n, steps, warmup, ms_total, tokens_per_step, clocks, extra):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
         "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": impl,
-        "config": {"model": "dense GPT 16L/1024/16q-8kv/SwiGLU-4096/vocab 50304 tied (0.30B params)",
+        "config": {"model": MODEL_NAME,
                    "global_batch": tokens_per_step, "seq_len": SEQ_LEN, "micro_batch": MICRO_BATCH,
-                   "grad_accum": GRAD_ACCUM, "parallelism": f"dp{n} zero1",
+                   "grad_accum": GRAD_ACCUM,
+                   "parallelism": f"dp{n // SEP_SIZE} zero1" + (f" x sep{SEP_SIZE}" if SEP_SIZE > 1 else ""),
                    "l2": "per-step working set (~20 GB of activations) far exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks,
     }
@@ -173,10 +208,10 @@ def run_ours(args) -> dict:
     cfg = build_config(parse_args(_flags(n, 2 * (K + W), log_dir)))
     trainer = Trainer(cfg)
     dev = trainer.device
-    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n
+    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * (n // SEP_SIZE)
 
     # ---- device-resident batches (kernel-side number) ----
-    gen = torch.Generator().manual_seed(1234 + rank)
+    gen = torch.Generator().manual_seed(1234 + rank // SEP_SIZE)      # ranks of one SEP group share their sequences
     pool = []
     for _ in range(4):
         step_batches = []
@@ -212,7 +247,7 @@ def run_ours(args) -> dict:
     for i in range(max(1, W // 2)):
         step_e2e(i)
     ms_e2e, _ = _timed(torch, dist, world, step_e2e, K)
-    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * SEQ_LEN * 8       # ids + labels, int64, per rank
+    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * (SEQ_LEN // SEP_SIZE) * 8       # ids + labels, int64, per rank
     extra = {
         "e2e": {"value": tokens_per_step / (ms_e2e / K / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
                 "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
@@ -244,12 +279,15 @@ def run_reference(args) -> dict:
         flags.append("--use_compile")
     cfg = build_config(parse_args(flags))
     trainer = Trainer(cfg)
+    if cfg.model.use_moe and args.moe_fallback:
+        for blk in trainer.raw_model.blocks:
+            blk.mlp.grouped_gemm_supported = False
     # what Trainer.train() does before and inside its loop (training/trainer.py:308-351)
     trainer.results = {}
     trainer.train_loader_iter = enumerate(trainer.train_loader)
     trainer.start_step = 0
     trainer._init_profiler(cfg)
-    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * n
+    tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * (n // SEP_SIZE)
     counter = {"i": 0}
     losses = []
 
@@ -266,7 +304,7 @@ def run_reference(args) -> dict:
     sampler.start()
     ms, _ = _timed(torch, dist, world, step, K)
     clocks = sampler.stop()
-    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * SEQ_LEN * 8
+    h2d = 2 * GRAD_ACCUM * MICRO_BATCH * (SEQ_LEN // SEP_SIZE) * 8
     extra = {"e2e": {"value": tokens_per_step / (ms / K / 1e3), "unit": "tokens/s", "ms_per_step": ms / K,
                      "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
              "gpu_launches": None, "final_loss": losses[-1], "use_compile": bool(args.ref_compile)}
@@ -283,8 +321,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-compile", type=int, default=0,
                     help="reference arm: pass --use_compile to the reference (its CLI default is off)")
+    ap.add_argument("--config", default="B", choices=["B"] + sorted(CONFIGS),
+                    help="B (default) is the headline configuration; see CONFIGS for the others")
+    ap.add_argument("--moe-fallback", type=int, default=1,
+                    help="reference arm, MoE configs: force its padded-bmm expert path (its grouped path only "
+                         "type-checks for moe_intermediate_size == hidden_size)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    _select_config(args.config, args.gpus)
     if args.impl == "reference":
         try:
             out = run_reference(args)

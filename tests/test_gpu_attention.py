@@ -6,7 +6,8 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(2, 256, 4, 2, 64), (1, 384, 2, 1, 128), (1, 1024, 2, 2, 64), (2, 128, 2, 2, 64), (1, 512, 4, 1, 128)]
+CASES = [(2, 256, 4, 2, 64), (1, 384, 2, 1, 128), (1, 1024, 2, 2, 64), (2, 128, 2, 2, 64), (1, 512, 4, 1, 128),
+         (2, 320, 8, 2, 32), (1, 200, 4, 4, 32)]
 
 
 def _ref(qkv, n_q, n_kv):

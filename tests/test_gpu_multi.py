@@ -55,6 +55,14 @@ def test_peer_collectives_multimem():
     _close(ref["norms"], mc["norms"], 2e-2)
 
 
+def test_bf16_gradient_wire_tracks_fp32_wire():
+    ref = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, FLAGS + ["--sep_size", "1"])
+    for nvls in ("0", "1"):
+        bf = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": nvls}, FLAGS + ["--sep_size", "1", "--grad_wire_dtype", "bf16"])
+        _close(ref["losses"], bf["losses"], 3e-3)
+        _close(ref["norms"], bf["norms"], 2e-2)
+
+
 def test_sequence_parallel_matches_data_parallel_on_gpu():
     dp = _run(2, {}, FLAGS + ["--sep_size", "1"])
     sp = _run(2, {}, [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)] + ["--sep_size", "2"])

@@ -38,11 +38,15 @@ struct AttnBwdParams {
   int B, T, Hq, Hkv;
   float scale, scale_log2;
   unsigned int* status;
+  int hd;                   // head dim in memory; 32 runs on the HD = 64 kernel with zero-filled upper columns
 };
 
 template <int HD>
 struct AttnBwdCfg {
-  static constexpr int STAGES = HD == 64 ? 2 : 1;
+  // Q / dO ring. Three stages for hd 64: the MMA warp issues S / dP of step it+1 before dV / dK / dQ of step
+  // it, so the load of step it+1 must have been started a whole step earlier (when step it-2 retired) for its
+  // latency to stay off the tensor pipe's critical path.
+  static constexpr int STAGES = HD == 64 ? 3 : 1;
   static constexpr bool PIPELINED = HD == 64;            // dQ has its own TMEM columns
   static constexpr int TILE_BYTES = AB_TILE * HD * 2;
   static constexpr int PD_BYTES = AB_TILE * AB_TILE * 2;
@@ -57,7 +61,10 @@ struct AttnBwdCfg {
   static constexpr int OFF_BAR = OFF_DQS + DQS_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
   static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
-  static constexpr uint32_t DQ_COL = HD == 64 ? 384 : 0;  // hd 128: dQ reuses the S columns
+  // hd 64: dQ has two 64-column buffers (steps alternate), so dQ of step it can be issued while the softmax
+  // warps still drain dQ of step it-1. hd 128: dQ reuses the S columns (no spare tensor memory).
+  static constexpr uint32_t DQ_COL = HD == 64 ? 384 : 0;
+  static constexpr uint32_t DQ_BUF_COLS = HD == 64 ? 64 : 0;
 };
 
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
@@ -109,7 +116,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sal = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bar0 = sbase + C::OFF_BAR;
-  // barriers: 0,1 qdo_full  2,3 qdo_empty  4 kv_full  5 sdp_full  6 sdp_consumed  7 pds_full  8 dq_full  9 dq_consumed
+  // barriers: 0,1 dq_consumed[buffer] (hd 64)  4 kv_full  5 sdp_full  6 sdp_consumed  7 pds_full  8 dq_full
+  //           9 dq_consumed (hd 128)  10.. qdo_full[stage]  13.. qdo_empty[stage]
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sal + C::OFF_BAR + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -124,7 +132,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const int heads_total = p.Hq + 2 * p.Hkv;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(bar(i), (i == 6 || i == 7 || i == 9) ? 8 : 1);
+    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == 0 || i == 1 || i == 6 || i == 7 || i == 9) ? 8 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -149,13 +157,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       for (int it = 0; it < n_it; ++it) {
         const int st = it % C::STAGES;
         const uint32_t ph = (uint32_t)(it / C::STAGES) & 1u;
-        if (!mbar_wait(bar(2 + st), ph ^ 1u, 21, abort_flag, p.status)) break;
+        if (!mbar_wait(bar(13 + st), ph ^ 1u, 21, abort_flag, p.status)) break;
         const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
-        mbar_expect_tx(bar(st), 2 * C::TILE_BYTES);
+        mbar_expect_tx(bar(10 + st), 2 * C::TILE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
-          tma_load_4d(sbase + C::OFF_Q + st * C::TILE_BYTES + kb * 16384, &tm_qkv, bar(st), kb * 64, hq, qi * AB_TILE, b);
-          tma_load_4d(sbase + C::OFF_DO + st * C::TILE_BYTES + kb * 16384, &tm_do, bar(st), kb * 64, hq, qi * AB_TILE, b);
+          tma_load_4d(sbase + C::OFF_Q + st * C::TILE_BYTES + kb * 16384, &tm_qkv, bar(10 + st), kb * 64, hq, qi * AB_TILE, b);
+          tma_load_4d(sbase + C::OFF_DO + st * C::TILE_BYTES + kb * 16384, &tm_do, bar(10 + st), kb * 64, hq, qi * AB_TILE, b);
         }
       }
     }
@@ -166,20 +174,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       constexpr uint32_t idesc_t = umma_idesc_bf16(AB_TILE, HD, 1, 1);          // dV, dK: A, B MN-major
       constexpr uint32_t idesc_q = umma_idesc_bf16(AB_TILE, HD, 0, 1);          // dQ    : A K-major, B MN-major
       const uint32_t sk = sbase + C::OFF_K, sv = sbase + C::OFF_V, sp = sbase + C::OFF_P, sds = sbase + C::OFF_DS;
+      // descriptors of the resident K / V tiles and of the P / dS tiles, built once
+      const uint64_t dk_k = umma_smem_desc(sk, 16, 1024), dv_k = umma_smem_desc(sv, 16, 1024);     // K-major views
+      const uint64_t dk_mn = umma_smem_desc(sk, 16384, 1024);                                      // K as MN-major B (dQ)
+      const uint64_t dp_mn = umma_smem_desc(sp, 16384, 1024), dds_mn = umma_smem_desc(sds, 16384, 1024);
+      const uint64_t dds_k = umma_smem_desc(sds, 16, 1024);
       auto issue_s_dp = [&](int it) -> bool {
         const int st = it % C::STAGES;
-        if (!mbar_wait(bar(st), (uint32_t)(it / C::STAGES) & 1u, 22, abort_flag, p.status)) return false;
+        if (!mbar_wait(bar(10 + st), (uint32_t)(it / C::STAGES) & 1u, 22, abort_flag, p.status)) return false;
         tc_fence_after();
-        const uint32_t sq = sbase + C::OFF_Q + st * C::TILE_BYTES, sdo = sbase + C::OFF_DO + st * C::TILE_BYTES;
+        const uint64_t dq_k = umma_smem_desc(sbase + C::OFF_Q + st * C::TILE_BYTES, 16, 1024);
+        const uint64_t ddo_k = umma_smem_desc(sbase + C::OFF_DO + st * C::TILE_BYTES, 16, 1024);
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t) {
           const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
-          umma_bf16(tmem + C::S_COL, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), idesc_s, t > 0);
+          if (t == 0) umma_bf16(tmem + C::S_COL, dq_k, dk_k, idesc_s, 0);
+          else umma_bf16_acc(tmem + C::S_COL, umma_desc_advance(dq_k, off), umma_desc_advance(dk_k, off), idesc_s);
         }
 #pragma unroll
         for (int t = 0; t < HD / 16; ++t) {
           const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
-          umma_bf16(tmem + C::DP_COL, umma_smem_desc(sdo + off, 16, 1024), umma_smem_desc(sv + off, 16, 1024), idesc_s, t > 0);
+          if (t == 0) umma_bf16(tmem + C::DP_COL, ddo_k, dv_k, idesc_s, 0);
+          else umma_bf16_acc(tmem + C::DP_COL, umma_desc_advance(ddo_k, off), umma_desc_advance(dv_k, off), idesc_s);
         }
         umma_commit(bar(5));
         return true;
@@ -199,21 +215,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           if (!issue_s_dp(it)) break;
         }
         if (!mbar_wait(bar(7), par, 26, abort_flag, p.status)) break;              // P, dS published
-        if (C::PIPELINED && it > 0 && !mbar_wait(bar(9), par ^ 1u, 27, abort_flag, p.status)) break;   // dQ columns free
+        // this step's dQ buffer was last used by step it-2: its flush is phase (it>>1)-1 of that buffer's barrier
+        if (C::PIPELINED && it > 1 && !mbar_wait(bar(it & 1), ((uint32_t)(it >> 1) & 1u) ^ 1u, 27, abort_flag, p.status)) break;
         tc_fence_after();
-        const uint32_t sq = sbase + C::OFF_Q + st * C::TILE_BYTES, sdo = sbase + C::OFF_DO + st * C::TILE_BYTES;
-        const uint32_t acc = it > 0;
+        const uint64_t dq_mn = umma_smem_desc(sbase + C::OFF_Q + st * C::TILE_BYTES, 16384, 1024);
+        const uint64_t ddo_mn = umma_smem_desc(sbase + C::OFF_DO + st * C::TILE_BYTES, 16384, 1024);
+        // dV += P^T dO, dK += dS^T Q : reduction over 16 query rows per step (2048 bytes further in both tiles)
+        if (it == 0) {
+          umma_bf16(tmem + C::DV_COL, dp_mn, ddo_mn, idesc_t, 0);
+          umma_bf16(tmem + C::DK_COL, dds_mn, dq_mn, idesc_t, 0);
+        } else {
+          umma_bf16_acc(tmem + C::DV_COL, dp_mn, ddo_mn, idesc_t);
+          umma_bf16_acc(tmem + C::DK_COL, dds_mn, dq_mn, idesc_t);
+        }
 #pragma unroll
-        for (int t = 0; t < AB_TILE / 16; ++t)      // dV += P^T dO : reduction over 16 query rows per step
-          umma_bf16(tmem + C::DV_COL, umma_smem_desc(sp + t * 2048, 16384, 1024), umma_smem_desc(sdo + t * 2048, 16384, 1024), idesc_t, acc | (t > 0));
+        for (int t = 1; t < AB_TILE / 16; ++t) {
+          umma_bf16_acc(tmem + C::DV_COL, umma_desc_advance(dp_mn, t * 2048), umma_desc_advance(ddo_mn, t * 2048), idesc_t);
+          umma_bf16_acc(tmem + C::DK_COL, umma_desc_advance(dds_mn, t * 2048), umma_desc_advance(dq_mn, t * 2048), idesc_t);
+        }
+        // dQ = dS K : reduction over 16 kv rows per step
+        const uint32_t t_dq = tmem + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS;
+        umma_bf16(t_dq, dds_k, dk_mn, idesc_q, 0);
 #pragma unroll
-        for (int t = 0; t < AB_TILE / 16; ++t)      // dK += dS^T Q
-          umma_bf16(tmem + C::DK_COL, umma_smem_desc(sds + t * 2048, 16384, 1024), umma_smem_desc(sq + t * 2048, 16384, 1024), idesc_t, acc | (t > 0));
-#pragma unroll
-        for (int t = 0; t < AB_TILE / 16; ++t)      // dQ = dS K : reduction over 16 kv rows per step
-          umma_bf16(tmem + C::DQ_COL, umma_smem_desc(sds + (t >> 2) * 16384 + (t & 3) * 32, 16, 1024), umma_smem_desc(sk + t * 2048, 16384, 1024), idesc_q, t > 0);
+        for (int t = 1; t < AB_TILE / 16; ++t)
+          umma_bf16_acc(t_dq, umma_desc_advance(dds_k, (t >> 2) * 16384 + (t & 3) * 32),
+                        umma_desc_advance(dk_mn, t * 2048), idesc_q);
         umma_commit(bar(8));                        // dQ ready; P / dS and this Q / dO stage are free
-        umma_commit(bar(2 + st));
+        umma_commit(bar(13 + st));
       }
     }
   } else {
@@ -236,7 +264,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 #pragma unroll
       for (int c = 0; c < HD / 2; c += 32) {
         uint32_t r[32];
-        tmem_ld32(t_lane + C::DQ_COL + half * (HD / 2) + c, r);
+        tmem_ld32(t_lane + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS + half * (HD / 2) + c, r);
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging box free again
         __syncwarp();
         tmem_ld_wait();
@@ -247,7 +275,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (y0 < p.T)
+          if (y0 < p.T && half * (HD / 2) + c < p.hd)
             asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
                          ::"l"((uint64_t)&tm_dq), "r"(stg_s), "r"(half * (HD / 2) + c), "r"(y0), "r"(b * p.Hq + hq) : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -255,7 +283,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(9));
+      if (lane == 0) mbar_arrive(C::PIPELINED ? bar(it & 1) : bar(9));
     };
 
     for (int it = 0; it < n_it; ++it) {
@@ -329,13 +357,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
           const float osc = which == 0 ? 1.f : p.scale;
           const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
-          __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * HD + half * (HD / 2);
+          __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * p.hd + half * (HD / 2);
 #pragma unroll
           for (int c = 0; c < HD / 2; c += 32) {
             uint32_t r[32];
             tmem_ld32(t_lane + col0 + c, r);
             tmem_ld_wait();
-            if (t_row < p.T) {
+            if (t_row < p.T && half * (HD / 2) + c < p.hd) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint4 v;
@@ -382,7 +410,7 @@ using namespace tlm;
 TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
                          float* dq_acc, float* delta, int B, int T, int Hq, int Hkv, int hd, float scale,
                          cudaStream_t st) {
-  if (hd != 64 && hd != 128) return -4;
+  if (hd != 32 && hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
   const long long rows = (long long)B * T * Hq;
   int blocks = (int)((rows * 32 + 255) / 256);
@@ -396,7 +424,7 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   if (e) return e;
   e = make_qkv_map(&mdo, dout, B, T, Hq, hd, AB_TILE);
   if (e) return e;
-  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word()};
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word(), hd};
   CUtensorMap mdq;                                     // fp32 [B*Hq, T, hd] accumulator, box 32 x 32 x 1
   {
     uint64_t dims[3] = {(uint64_t)hd, (uint64_t)T, (uint64_t)B * Hq};
@@ -405,7 +433,7 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
     e = make_tmap_f32(&mdq, dq_acc, 3, dims, strides, box);
     if (e) return e;
   }
-  e = hd == 64 ? launch_bwd<64>(mq, mdo, mdq, p, st) : launch_bwd<128>(mq, mdo, mdq, p, st);
+  e = hd == 128 ? launch_bwd<128>(mq, mdo, mdq, p, st) : launch_bwd<64>(mq, mdo, mdq, p, st);
   if (e) return e;
   long long items = rows * (hd / 8);
   int cb = (int)((items + 255) / 256);

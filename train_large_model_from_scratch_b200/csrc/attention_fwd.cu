@@ -39,6 +39,10 @@ struct AttnFwdParams {
   // peer-mapped addresses, plain 16-byte stores). n_dst == 0 disables it.
   __nv_bfloat16* o_dst[AT_MAX_DST];
   int n_dst, dst_rows, dst_heads, dst_head0;
+  // Head dim of the tensors in memory. It equals the kernel's HD except for hd = 32, which runs on the
+  // HD = 64 kernel: the TMA boxes stay 64 wide and the 32 columns past the end of a head are
+  // out-of-bounds zero fill, so Q K^T is unchanged and the upper half of O is never stored.
+  int hd;
 };
 
 template <int HD>
@@ -76,7 +80,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
     return;
   }
   const uint32_t bar0 = sbase + L::OFF_BAR;
-  // barriers: 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 kv_empty, 7 s_full, 8 p_full, 9 o_done, 10 s_consumed
+  // barriers: 0 q_full, 1..2 k_full, 3..4 v_full, 5..6 v_empty, 7 s_full, 8 p_full, 9 o_done, 10 s_consumed,
+  //           11..12 k_empty. A K stage is free as soon as its S = Q K^T has run, long before the stage's V is
+  //           consumed, so K tiles are loaded one step ahead of V tiles and their latency stays hidden.
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sal + L::OFF_BAR + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -90,7 +96,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
   const int n_kv = qt + 1;                            // causal: KV tiles 0..qt
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) mbar_init(bar(i), (i == 8 || i == 10) ? 4 : 1);
+    for (int i = 0; i < 13; ++i) mbar_init(bar(i), (i == 8 || i == 10) ? 4 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -106,14 +112,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
       mbar_expect_tx(bar(0), L::Q_BYTES);
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb) tma_load_4d(sbase + L::OFF_Q + kb * 16384, &tm_qkv, bar(0), kb * 64, h, q0, b);
-      for (int j = 0; j < n_kv; ++j) {
+      auto load_k = [&](int j) -> bool {
         const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(bar(5 + st), ph ^ 1u, 11, abort_flag, p.status)) break;
+        if (!mbar_wait(bar(11 + st), ((uint32_t)(j >> 1) & 1u) ^ 1u, 11, abort_flag, p.status)) return false;
         mbar_expect_tx(bar(1 + st), L::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
           tma_load_4d(sbase + L::OFF_K + st * L::KV_BYTES + kb * 16384, &tm_qkv, bar(1 + st), kb * 64, p.Hq + kvh, j * AT_BKV, b);
+        return true;
+      };
+      bool ok = load_k(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_kv && !load_k(j + 1)) break;
+        if (!mbar_wait(bar(5 + st), ((uint32_t)(j >> 1) & 1u) ^ 1u, 20, abort_flag, p.status)) break;
         mbar_expect_tx(bar(3 + st), L::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
@@ -124,18 +136,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(AT_BQ, AT_BKV, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(AT_BQ, HD, 0, 1);
-      const uint32_t sq = sbase + L::OFF_Q, sp = sbase + L::OFF_P;
+      // descriptors are built once per tile and advanced with one add per MMA: this thread's instruction
+      // stream is what feeds the tensor pipe
+      const uint64_t dq = umma_smem_desc(sbase + L::OFF_Q, 16, 1024), dp = umma_smem_desc(sbase + L::OFF_P, 16, 1024);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(bar(1 + st), (uint32_t)(j >> 1) & 1u, 13, abort_flag, p.status)) return false;
         tc_fence_after();
-        const uint32_t sk = sbase + L::OFF_K + st * L::KV_BYTES;
+        const uint64_t dk = umma_smem_desc(sbase + L::OFF_K + st * L::KV_BYTES, 16, 1024);
+        umma_bf16(tmem + S_COL, dq, dk, idesc_s, 0);
 #pragma unroll
-        for (int t = 0; t < HD / 16; ++t) {
+        for (int t = 1; t < HD / 16; ++t) {
           const uint32_t off = (t >> 2) * 16384 + (t & 3) * 32;
-          umma_bf16(tmem + S_COL, umma_smem_desc(sq + off, 16, 1024), umma_smem_desc(sk + off, 16, 1024), idesc_s, t > 0);
+          umma_bf16_acc(tmem + S_COL, umma_desc_advance(dq, off), umma_desc_advance(dk, off), idesc_s);
         }
         umma_commit(bar(7));
+        umma_commit(bar(11 + st));                              // K stage free
         return true;
       };
       bool ok = mbar_wait(bar(0), 0, 12, abort_flag, p.status);
@@ -150,15 +166,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         if (!mbar_wait(bar(8), par, 14, abort_flag, p.status)) break;                        // P written
         if (!mbar_wait(bar(3 + st), (uint32_t)(j >> 1) & 1u, 15, abort_flag, p.status)) break;   // V landed
         tc_fence_after();
-        const uint32_t sv = sbase + L::OFF_V + st * L::KV_BYTES;
+        const uint64_t dv = umma_smem_desc(sbase + L::OFF_V + st * L::KV_BYTES, 16384, 1024);   // MN-major: 16 kv rows per step
+        umma_bf16(tmem + O_COL, dp, dv, idesc_o, j > 0);
 #pragma unroll
-        for (int t = 0; t < AT_BKV / 16; ++t) {
-          const uint64_t ad = umma_smem_desc(sp + (t >> 2) * 16384 + (t & 3) * 32, 16, 1024);
-          const uint64_t bd = umma_smem_desc(sv + t * 2048, 16384, 1024);      // MN-major: 16 kv rows per step
-          umma_bf16(tmem + O_COL, ad, bd, idesc_o, (j > 0) | (t > 0));
-        }
+        for (int t = 1; t < AT_BKV / 16; ++t)
+          umma_bf16_acc(tmem + O_COL, umma_desc_advance(dp, (t >> 2) * 16384 + (t & 3) * 32), umma_desc_advance(dv, t * 2048), idesc_o);
         umma_commit(bar(9));                                    // O updated, P free
-        umma_commit(bar(5 + st));                               // K/V stage free
+        umma_commit(bar(5 + st));                               // V stage free
       }
     }
   } else {
@@ -276,18 +290,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_run;
-      __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * HD;
+      __nv_bfloat16* out = p.o + (((long long)b * p.T + t_row) * p.Hq + h) * p.hd;
       __nv_bfloat16* out2 = nullptr;
       if (p.n_dst > 0 && t_row < p.T) {
         const int dest = t_row / p.dst_rows, tl = t_row - dest * p.dst_rows;
-        if (dest < p.n_dst) out2 = p.o_dst[dest] + (((long long)b * p.dst_rows + tl) * p.dst_heads + p.dst_head0 + h) * HD;
+        if (dest < p.n_dst) out2 = p.o_dst[dest] + (((long long)b * p.dst_rows + tl) * p.dst_heads + p.dst_head0 + h) * p.hd;
       }
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
         uint32_t r[32];
         tmem_ld32(t_lane + O_COL + c, r);
         tmem_ld_wait();
-        if (t_row < p.T) {
+        if (t_row < p.T && c < p.hd) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
@@ -309,7 +323,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-// 4-D map over the packed tensor: dims (hd, heads, T, B); box (64, 1, rows, 1).
+// 4-D map over the packed tensor: dims (hd, heads, T, B); box (64, 1, rows, 1). For hd = 32 the box is wider
+// than the tensor's inner extent; the excess columns are zero fill.
 int make_qkv_map(CUtensorMap* map, const void* base, int B, int T, int heads, int hd, int box_rows) {
   uint64_t dims[4] = {(uint64_t)hd, (uint64_t)heads, (uint64_t)T, (uint64_t)B};
   uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)heads * hd * 2, (uint64_t)T * heads * hd * 2};
@@ -338,7 +353,7 @@ using namespace tlm;
 
 static int attn_fwd_impl(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,
                          void* const* o_dst, int n_dst, int dst_rows, int dst_heads, int dst_head0, cudaStream_t st) {
-  if (hd != 64 && hd != 128) return -4;
+  if (hd != 32 && hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
   if (n_dst < 0 || n_dst > AT_MAX_DST || (n_dst > 0 && (dst_rows <= 0 || (long long)dst_rows * n_dst < T))) return -6;
   CUtensorMap map;
@@ -347,9 +362,9 @@ static int attn_fwd_impl(const void* qkv, void* o, float* lse, int B, int T, int
   AttnFwdParams p{};
   p.o = (__nv_bfloat16*)o; p.lse = lse; p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f; p.scale = scale; p.status = status_word();
-  p.n_dst = n_dst; p.dst_rows = dst_rows; p.dst_heads = dst_heads; p.dst_head0 = dst_head0;
+  p.n_dst = n_dst; p.dst_rows = dst_rows; p.dst_heads = dst_heads; p.dst_head0 = dst_head0; p.hd = hd;
   for (int i = 0; i < n_dst; ++i) p.o_dst[i] = (__nv_bfloat16*)o_dst[i];
-  return hd == 64 ? launch_fwd<64>(map, p, st) : launch_fwd<128>(map, p, st);
+  return hd == 128 ? launch_fwd<128>(map, p, st) : launch_fwd<64>(map, p, st);
 }
 
 TLM_API int tlm_attn_fwd(const void* qkv, void* o, float* lse, int B, int T, int Hq, int Hkv, int hd, float scale,

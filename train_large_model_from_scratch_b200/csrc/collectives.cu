@@ -1,8 +1,8 @@
 // Gradient reduce-scatter and fused AdamW + parameter all-gather over NVLink
 // peer memory (one process per GPU, buffers in symmetric memory).
 //
-//   reduce_scatter : each rank sums ITS slice of the flat fp32 gradient buffer
-//                    over all ranks, reading the peers' buffers directly
+//   reduce_scatter : each rank sums ITS slice of the flat fp32 gradient buffer (or of its
+//                    bf16 rounding, the "bf16 wire") over all ranks, reading the peers' buffers directly
 //                    (multimem.ld_reduce through the NVSwitch when a multicast
 //                    mapping is given, else one P2P load per peer), and emits
 //                    per-block sum-of-squares partials for the global grad norm.
@@ -131,6 +131,65 @@ __global__ void reduce_scatter_kernel(PeerPtrs grads, const float* mc_grads, Pee
   }
 }
 
+// bf16 wire format: every rank first rounds its fp32 gradients into a symmetric bf16 staging buffer
+// (cast_bf16_kernel, local), then each rank sums ITS slice over all ranks' staging buffers with fp32
+// accumulation. Half the NVLink bytes of the fp32 wire at the price of one rounding of each addend
+// (and, through the switch, of the sum: multimem.ld_reduce returns bf16 for bf16 operands).
+__global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long nvec = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(src)[2 * i], b = reinterpret_cast<const float4*>(src)[2 * i + 1];
+    reinterpret_cast<uint4*>(dst)[i] = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  }
+}
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
+__global__ void reduce_scatter_bf16_kernel(PeerPtrs wire, const __nv_bfloat16* mc_wire, PeerPtrs flags, float* __restrict__ out,
+                                           float* __restrict__ partials, long long lo, long long len, int rank, int n,
+                                           int epoch, unsigned int* status) {
+  __shared__ float red[32];
+  const bool ok = flag_exchange(flags, rank, n, epoch, blockIdx.x == 0, status, 43);
+  float acc = 0.f;
+  if (ok) {
+    const long long nvec = len / 8;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (mc_wire != nullptr) {
+        const uint4 v = multimem_ld_reduce_bf16x8(mc_wire + lo + i * 8);
+        const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
+        s[0] = a.x; s[1] = a.y; s[2] = b.x; s[3] = b.y; s[4] = c.x; s[5] = c.y; s[6] = d.x; s[7] = d.y;
+      } else {
+        for (int r = 0; r < n; ++r) {
+          const int src = (rank + r) % n;
+          const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(wire.p[src]) + lo + i * 8);
+          const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
+          s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
+        }
+      }
+      reinterpret_cast<float4*>(out)[2 * i] = make_float4(s[0], s[1], s[2], s[3]);
+      reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(s[4], s[5], s[6], s[7]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc += s[k] * s[k];
+    }
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) partials[blockIdx.x] = v;
+  }
+}
+
 __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out) {
   __shared__ double red[32];
   double acc = 0.0;
@@ -230,6 +289,24 @@ TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, vo
                                                 len, rank, n, epoch, status_word());
   sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out);
   count_launch(2);
+  return launch_status();
+}
+
+// bf16 wire: `grads` (this rank's fp32 buffer, n elements) is rounded into `wire_local` (this rank's symmetric
+// bf16 buffer), then the slice [lo, lo+len) is summed over all ranks' wire buffers into `out` (fp32).
+TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long long n_total, void* const* wire_ptrs,
+                                    const void* mc_wire, void* const* flag_ptrs, float* out, float* partials,
+                                    float* sumsq_out, long long lo, long long len, int rank, int n, int epoch,
+                                    cudaStream_t st) {
+  if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0 || n_total % 8 != 0) return -6;
+  long long cb = (n_total / 8 + 255) / 256;
+  if (cb > 8LL * num_sms()) cb = 8LL * num_sms();
+  cast_bf16_kernel<<<(int)(cb < 1 ? 1 : cb), 256, 0, st>>>(grads, (__nv_bfloat16*)wire_local, n_total);
+  const int blocks = tlm_reduce_scatter_blocks();
+  reduce_scatter_bf16_kernel<<<blocks, 512, 0, st>>>(to_ptrs(wire_ptrs, n), (const __nv_bfloat16*)mc_wire, to_ptrs(flag_ptrs, n),
+                                                     out, partials, lo, len, rank, n, epoch, status_word());
+  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out);
+  count_launch(3);
   return launch_status();
 }
 

@@ -93,18 +93,26 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Wait with a time limit. Returns false (after recording `site`) when the
-// phase did not complete within ~`limit_ns`; callers then leave their loops,
+// phase did not complete within the limit; callers then leave their loops,
 // skip further waits and fall through to the common teardown.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+// The limit is counted in SM cycles (`clock64`, a cheap register read) and only
+// looked at every 1024 failed polls: reading %globaltimer costs on the order of a
+// microsecond, which on a wait that sits on a pipeline's critical path (and
+// almost every wait fails its first poll) is more than the work between waits.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;            // 2 s (flag waits on peers, timed with %globaltimer)
+constexpr long long kWaitLimitCycles = 4000000000ll;        // ~2-3 s of SM cycles
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int site,
                                           volatile int* abort_flag, unsigned int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
+    if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         report_status(status, (site << 8) | 1u);
         return false;
@@ -231,6 +239,21 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   d |= (uint64_t)1 << 46;        // descriptor version (Blackwell)
   d |= (uint64_t)2 << 61;        // SWIZZLE_128B
   return d;
+}
+// Descriptor of the same tile `byte_off` bytes further on. The start-address field holds (addr >> 4) in its
+// low 14 bits and shared-memory addresses stay below 2^18, so the field cannot carry into its neighbours and
+// the whole update is one add. The thread that issues the MMAs is a serial bottleneck (one instruction
+// stream feeds the tensor pipe), so descriptors are built once per tile and advanced this way.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t byte_off) {
+  return desc + (uint64_t)(byte_off >> 4);
+}
+// D[tmem] += A[smem] * B[smem] (accumulate always on: no predicate set-up)
+__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
 }
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 D.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {

@@ -225,17 +225,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         }
         __syncwarp();
         if (lane == 0) {
+          // K-major: 16 bf16 = 32 B further along the 128 B row;
+          // MN-major: 16 k-rows = two 8-row groups = 2048 B further.
+          const uint64_t ad0 = A_MN ? umma_smem_desc(sa, BOX_MN_BYTES, 1024) : umma_smem_desc(sa, 16, 1024);
+          const uint64_t bd0 = B_MN ? umma_smem_desc(sb, BOX_MN_BYTES, 1024) : umma_smem_desc(sb, 16, 1024);
+          umma_bf16(tmem_d, ad0, bd0, idesc, accumulate);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            // K-major: 16 bf16 = 32 B further along the 128 B row;
-            // MN-major: 16 k-rows = two 8-row groups = 2048 B further.
-            const uint64_t ad = A_MN ? umma_smem_desc(sa + kk * 2048, BOX_MN_BYTES, 1024)
-                                     : umma_smem_desc(sa + kk * 32, 16, 1024);
-            const uint64_t bd = B_MN ? umma_smem_desc(sb + kk * 2048, BOX_MN_BYTES, 1024)
-                                     : umma_smem_desc(sb + kk * 32, 16, 1024);
-            umma_bf16(tmem_d, ad, bd, idesc, accumulate);
-            accumulate = 1;
-          }
+          for (int kk = 1; kk < BK / UMMA_K; ++kk)
+            umma_bf16_acc(tmem_d, umma_desc_advance(ad0, kk * (A_MN ? 2048 : 32)), umma_desc_advance(bd0, kk * (B_MN ? 2048 : 32)), idesc);
+          accumulate = 1;
           umma_commit(empty_bar(stage));          // stage reusable once these MMAs retire
         }
         __syncwarp();

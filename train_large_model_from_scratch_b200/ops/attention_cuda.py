@@ -1,8 +1,9 @@
 """CUDA attention entry points used by `ops.native`: the tcgen05 flash-attention
-kernels for head dims 64 and 128.
+kernels for head dims 32, 64 and 128 (32 runs on the 64-wide kernel with
+zero-filled upper columns).
 
-Head dims other than 64 / 128 (and non-causal calls) go to the library SDPA
-kernels through ATen (a library call, like a cuBLAS GEMM).
+Other head dims (and non-causal calls) go to the library SDPA kernels through
+ATen (a library call, like a cuBLAS GEMM).
 """
 from __future__ import annotations
 
@@ -14,7 +15,7 @@ from . import native
 
 
 def _native_ok(hd: int) -> bool:
-    return hd in (64, 128)
+    return hd in (32, 64, 128)
 
 
 def fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):

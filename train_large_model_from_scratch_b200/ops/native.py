@@ -69,6 +69,7 @@ _SIGS = {
     "tlm_wait_flag": (_I, [_P, _I, _c.c_ulonglong, _P]),
     "tlm_reduce_scatter_blocks": (_I, []),
     "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
+    "tlm_reduce_scatter_bf16": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
     "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P]),
     "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),

@@ -8,7 +8,9 @@ communication themselves:
 
   reduce-scatter   each rank reads its 1/n slice of every peer's fp32 gradient
                    buffer (`multimem.ld_reduce` or P2P loads) -> fp32 shard,
-                   with the sum of squares for the global norm;
+                   with the sum of squares for the global norm; with
+                   `--grad_wire_dtype bf16` the peers read a bf16 rounding of the
+                   gradients instead (half the NVLink bytes, fp32 accumulation);
   AdamW + gather   the optimizer kernel stores the updated bf16 parameters into
                    every rank's replica (`multimem.st` or P2P stores);
   barriers         symmetric flag arrays with bounded waits.
@@ -59,10 +61,12 @@ class _Peer:
 class PeerCollectives:
     def __init__(self):
         self.state = {}          # id(shard) -> dict
+        self.wire_dtype = "fp32"
 
     @classmethod
     def create(cls, fused, wire_dtype: str = "fp32") -> "PeerCollectives":
         self = cls()
+        self.wire_dtype = wire_dtype
         for s in fused.shards:
             if s.n == 1 or not s.sharded:
                 continue
@@ -77,6 +81,9 @@ class PeerCollectives:
                 "partials": torch.zeros(native.lib().tlm_reduce_scatter_blocks(), dtype=torch.float32, device=dev),
                 "sumsq": torch.zeros((), dtype=torch.float32, device=dev),
             }
+            if wire_dtype == "bf16":
+                wire = symm_alloc(s.buf.padded, torch.bfloat16, dev)
+                st["wire_t"], st["wire"] = wire, _Peer(wire, s.group)
             self.state[id(s)] = st
             dist.barrier(group=s.group)
         torch.cuda.synchronize()
@@ -98,6 +105,14 @@ class PeerCollectives:
         st = self.state[id(s)]
         st["epoch"] += 1
         g, f = st["grad"], st["flags"]
+        if "wire" in st:
+            w = st["wire"]
+            native._check(native.lib().tlm_reduce_scatter_bf16(
+                s.buf.main_grad.data_ptr(), st["wire_t"].data_ptr(), s.buf.padded, w.ptr_array,
+                ctypes.c_void_p(w.mc_ptr) if w.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
+                st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, st["epoch"],
+                native._stream()), "reduce_scatter_bf16")
+            return s.grad_shard
         native._check(native.lib().tlm_reduce_scatter(
             g.ptr_array, ctypes.c_void_p(g.mc_ptr) if g.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
             st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, st["epoch"],
