@@ -35,7 +35,7 @@ REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 MODEL = dict(num_layer=16, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
              intermediate_size=4096, vocab_size=50304, block_size=4096)
 SEQ_LEN, MICRO_BATCH, GRAD_ACCUM = 4096, 8, 2
-SEP_SIZE, EXTRA_FLAGS = 1, []
+SEP_SIZE, EXTRA_FLAGS, _CONFIG = 1, [], "B"
 MODEL_NAME = "dense GPT 16L/1024/16q-8kv/SwiGLU-4096/vocab 50304 tied (0.30B params)"
 BASELINE_TOKENS_PER_S = None          # the reference publishes no number
 
@@ -61,9 +61,10 @@ CONFIGS = {
 
 
 def _select_config(name: str, n_gpus: int) -> None:
-    global MODEL, SEQ_LEN, MICRO_BATCH, GRAD_ACCUM, SEP_SIZE, EXTRA_FLAGS, MODEL_NAME
+    global MODEL, SEQ_LEN, MICRO_BATCH, GRAD_ACCUM, SEP_SIZE, EXTRA_FLAGS, MODEL_NAME, _CONFIG
     if name == "B":
         return
+    _CONFIG = name
     c = CONFIGS[name]
     SEP_SIZE = n_gpus if c["sep"] == "all" else min(int(c["sep"]), n_gpus)
     SEQ_LEN = c["seq_per_rank"] * SEP_SIZE if "seq_per_rank" in c else c["seq"]
@@ -177,7 +178,8 @@ def _result(impl, n, steps, warmup, ms_total, tokens_per_step, clocks, extra):
     ms_step = ms_total / steps
     value = tokens_per_step / (ms_step / 1e3)
     out = {
-        "metric": "training throughput, 0.25B-class dense GPT (tokens/s, whole job, max over ranks)",
+        "metric": ("training throughput, 0.25B-class dense GPT (tokens/s, whole job, max over ranks)" if _CONFIG == "B"
+                   else f"training throughput, config {_CONFIG} (tokens/s, whole job, max over ranks)"),
         "value": value, "unit": "tokens/s", "n_gpus": n, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,

@@ -89,7 +89,10 @@ struct TileCoord {
 };
 
 __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n) {
-  const int ks = tile_in % p.split_k, tile = tile_in / p.split_k;
+  // split-major order: CTAs that run together work on different output tiles, so the red.global passes of
+  // the k-splits of one tile do not collide in time
+  const int n_out = tiles_m * tiles_n;
+  const int ks = tile_in / n_out, tile = tile_in - ks * n_out;
   // bands of 16 row-tiles, column-tiles fastest inside a band -> the CTAs that
   // run together share a handful of A and B tiles in L2
   constexpr int GROUP_M = 16;
@@ -619,13 +622,25 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   p.split_k = 1; p.k_chunk = K;
-  if (epi == EPI_F32_ACC && tiles * 2 <= num_sms()) {      // few output tiles, long reduction (weight gradients)
-    int want = num_sms() / tiles;
-    int kblocks = (K + BK - 1) / BK;
-    int max_split = kblocks / 8 > 0 ? kblocks / 8 : 1;      // keep at least 8 k-blocks per split
-    int split = want < max_split ? want : max_split;
-    if (split > 1) {
-      int per = (kblocks + split - 1) / split;
+  if (epi == EPI_F32_ACC) {
+    // Weight gradients: few output tiles, long reduction. The persistent grid runs work items (tile x k-split)
+    // of equal size, so throughput is items / (waves * SMs); pick the split that fills the last wave best,
+    // preferring fewer splits on ties (each split adds one pass of red.global over its tile). At least 16
+    // k-blocks per split keep the epilogue small against the main loop.
+    const int sms = num_sms();
+    const int kblocks = (K + BK - 1) / BK;
+    int max_split = kblocks / 16;
+    if (max_split > 16) max_split = 16;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int sp = 1; sp <= (max_split > 1 ? max_split : 1); ++sp) {
+      const long long items = (long long)tiles * sp;
+      const long long waves = (items + sms - 1) / sms;
+      const double eff = (double)items / (double)(waves * sms) - 0.004 * (sp - 1);
+      if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
+    }
+    if (best > 1) {
+      const int per = (kblocks + best - 1) / best;
       p.k_chunk = per * BK;
       p.split_k = (kblocks + per - 1) / per;
     }

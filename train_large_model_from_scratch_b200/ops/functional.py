@@ -299,7 +299,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 class _LinearCrossEntropy(torch.autograd.Function):
     """`sum_i CE(h_i @ W^T, target_i)` without keeping the `[M, V]` logits.
 
-    The forward walks over row chunks: logits chunk = GEMM, one kernel turns it
+    The forward walks over row chunks (8192 rows: a 0.8 GB bf16 logits workspace for a 50k vocabulary): logits chunk = GEMM, one kernel turns it
     in place into `grad_scale * (softmax - onehot)` while emitting the chunk's
     loss sum, then dgrad and wgrad GEMMs consume it. So the backward work is
     done during forward and `backward()` only hands out the stored `dh`.
@@ -308,7 +308,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
     accumulation steps)); it stays on the device, no host sync is needed.
     """
 
-    CHUNK_ROWS = 4096
+    CHUNK_ROWS = 8192
 
     @staticmethod
     def forward(ctx, h, weight, targets, grad_scale, ignore_index):
