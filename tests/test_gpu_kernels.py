@@ -137,7 +137,7 @@ def test_gemm_heads_rope_epilogue(nat, hd, Hq, Hkv, B, T, K):
     cos, sin = cos.contiguous(), sin.contiguous()
     out = torch.full((B, T, Ht, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     dst = (ctypes.c_void_p * 1)(out.data_ptr())
-    nat.gemm_heads(x, w, False, dst, 1, B, T, T, Ht, 0, Hq, Hkv, Hq, Hkv, hd, Hq + Hkv, cos, sin)
+    nat.gemm_heads(x, w, False, dst, 1, B, T, T, Ht, 0, Hq, Hkv, Hq, Hkv, hd, Hq + Hkv, nat.rope_table_fp16(cos, sin))
     ref = (x.float() @ w.float().t()).view(B, T, Ht, hd)
     ref[:, :, :Hq + Hkv] = oracle.rope(ref[:, :, :Hq + Hkv], cos, sin)
     assert torch.isfinite(out.float()).all()
@@ -153,7 +153,7 @@ def test_gemm_heads_scatter_plan(nat):
     dy, w = _rand(B * T_l, 192, seed=32), _rand(192, Hq * hd, scale=0.05, seed=33)     # dy @ w, w is [K, N]
     bufs = [torch.zeros(B, sp * T_l, q_l, hd, dtype=torch.bfloat16, device="cuda") for _ in range(sp)]
     dst = (ctypes.c_void_p * sp)(*[b.data_ptr() for b in bufs])
-    nat.gemm_heads(dy, w, True, dst, sp, B, T_l, sp * T_l, q_l, me * T_l, Hq, 0, q_l, 1, hd, 0, None, None)
+    nat.gemm_heads(dy, w, True, dst, sp, B, T_l, sp * T_l, q_l, me * T_l, Hq, 0, q_l, 1, hd, 0, None)
     ref = (dy.float() @ w.float()).view(B, T_l, Hq, hd)
     for r in range(sp):
         got = bufs[r][:, me * T_l:(me + 1) * T_l]

@@ -22,6 +22,7 @@
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code,
 // every role leaves its loop, and the CTA still frees its tensor memory.
 #include "common.cuh"
+#include <cuda_fp16.h>
 
 namespace tlm {
 
@@ -66,8 +67,8 @@ struct GemmParams {
   // (j / kv_l, q_l + j % kv_l), v head j -> (j / kv_l, q_l + kv_l + j % kv_l). With one destination and
   // q_l = Hq, kv_l = Hkv this is the identity layout [B, T, Hq + 2 Hkv, hd].
   int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot;
-  const float* cosT;        // [rows_per_batch, hd]
-  const float* sinT;
+  const __half2* cs;        // [rows_per_batch, hd] (cos, sin) pairs in fp16: |error| < 2^-11, below the bf16 rounding of
+                            // the rotated outputs, and half the table bytes of two fp32 tables
   // Row-scatter epilogue (bf16 store, grouped rows): output row r is not written to C but to
   //   rs_dst[rs_rank[r]] + rs_row[r] * ldc   (rows with rs_rank[r] < 0 are dropped).
   // This is the expert-parallel combine: the down-projection's accumulator goes straight to the
@@ -270,22 +271,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         const int bi = grow / p.rows_per_batch, t0 = grow - bi * p.rows_per_batch;
         const int hd = p.hd, half = hd >> 1;
         const int n_heads = p.Hq + 2 * p.Hkv;
-        const float* crow = p.cosT + (long long)(t0 + lane) * hd;
-        const float* srow = p.sinT + (long long)(t0 + lane) * hd;
-        // rotate 32 (lo, hi) column pairs: lo = columns [c, c+32), hi = [c+half, c+half+32) of the head
-        auto rotate = [&](uint32_t* lo, uint32_t* hi, int c) {
+        const uint4* csrow = reinterpret_cast<const uint4*>(p.cs + (long long)(t0 + lane) * hd);   // 4 (cos, sin) pairs per 16 bytes
+        // rotate 32 (lo, hi) column pairs with their (cos, sin) entries: lo = columns [c, c+32), hi = [c+half, c+half+32)
+        auto rotate = [&](uint32_t* lo, uint32_t* hi, const uint32_t* cs_lo, const uint32_t* cs_hi) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 cl = *reinterpret_cast<const float4*>(crow + c + i), sl = *reinterpret_cast<const float4*>(srow + c + i);
-            const float4 ch = *reinterpret_cast<const float4*>(crow + c + half + i), sh = *reinterpret_cast<const float4*>(srow + c + half + i);
-            const float clv[4] = {cl.x, cl.y, cl.z, cl.w}, slv[4] = {sl.x, sl.y, sl.z, sl.w};
-            const float chv[4] = {ch.x, ch.y, ch.z, ch.w}, shv[4] = {sh.x, sh.y, sh.z, sh.w};
+          for (int i = 0; i < 32; ++i) {
+            const float2 l = __half22float2(*reinterpret_cast<const __half2*>(&cs_lo[i]));
+            const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&cs_hi[i]));
+            const float a = __uint_as_float(lo[i]), b = __uint_as_float(hi[i]);
+            lo[i] = __float_as_uint(a * l.x - b * l.y);
+            hi[i] = __float_as_uint(b * h.x + a * h.y);
+          }
+        };
+        auto load_cs = [&](uint32_t* dst, int c) {          // entries [c, c+32) of this row
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float a = __uint_as_float(lo[i + k]), b = __uint_as_float(hi[i + k]);
-              lo[i + k] = __float_as_uint(a * clv[k] - b * slv[k]);
-              hi[i + k] = __float_as_uint(b * chv[k] + a * shv[k]);
-            }
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = csrow[(c >> 2) + i];
+            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
           }
         };
         // 32 fp32 columns -> bf16 -> 16-byte chunks [chunk0, chunk0 + 4) of this lane's 128-byte staging row
@@ -303,6 +305,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           }
         };
         const int heads_per_tile = BN / hd;
+        uint32_t cs_lo[32], cs_hi[32];                       // hd 64: the row's whole table, shared by the tile's heads
+        if (hd == 64 && rows_ok && t.n0 / hd < p.n_rot) { load_cs(cs_lo, 0); load_cs(cs_hi, 32); }
 #pragma unroll 1
         for (int hh = 0; hh < heads_per_tile; ++hh) {
           const int head = t.n0 / hd + hh;
@@ -321,7 +325,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             __syncwarp();
             tmem_ld_wait();
             if (live) {
-              if (rot) rotate(r0, r1, 0);
+              if (rot) rotate(r0, r1, cs_lo, cs_hi);
               stage32(r0, ebuf + bsel * EPI_BUF_BYTES, 0);
               stage32(r1, ebuf + bsel * EPI_BUF_BYTES, 4);
             }
@@ -344,7 +348,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
               tmem_ld32(taddr + hh * 128 + 64 + part * 32, r1);
               tmem_ld_wait();
               if (live) {
-                if (rot) rotate(r0, r1, part * 32);
+                if (rot) { load_cs(cs_lo, part * 32); load_cs(cs_hi, 64 + part * 32); rotate(r0, r1, cs_lo, cs_hi); }
                 stage32(r0, ebuf, part * 4);
                 stage32(r1, ebuf + EPI_BUF_BYTES, part * 4);
               }
@@ -572,18 +576,19 @@ using namespace tlm;
 // Projection GEMM whose epilogue applies RoPE and scatters heads (see GemmParams):
 //   A [M = batch * rows_per_batch, K] (lda);  B [N, K] K-major (b_mn = 0) or [K, N] MN-major (b_mn = 1),
 //   N = (Hq + 2 Hkv) * hd;  dst_ptrs[r]: bf16 [batch, dst_rows, dst_heads, hd] on rank r (peer-mapped
-//   addresses are fine: the stores are TMA tile stores without multicast).
+//   addresses are fine: the stores are TMA tile stores without multicast);  cs: fp16 (cos, sin) pairs
+//   [rows_per_batch, hd, 2] for the heads below n_rot.
 // Requirements: hd in {64, 128}, rows_per_batch % 32 == 0, n_dst <= 8, Hq % q_l == 0, Hkv % kv_l == 0.
 TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
                            void* const* dst_ptrs, int n_dst, int batch, int rows_per_batch, int dst_rows, int dst_heads,
-                           int row_off, int Hq, int Hkv, int q_l, int kv_l, int hd, int n_rot, const float* cosT,
-                           const float* sinT, cudaStream_t stream) {
+                           int row_off, int Hq, int Hkv, int q_l, int kv_l, int hd, int n_rot, const void* cs,
+                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((hd != 64 && hd != 128) || rows_per_batch % 32 != 0 || n_dst < 1 || n_dst > MAX_HEAD_DST) return -4;
   if (M != batch * rows_per_batch || N != (Hq + 2 * Hkv) * hd || q_l <= 0 || Hq % q_l != 0) return -5;
   if (Hkv > 0 && (kv_l <= 0 || Hkv % kv_l != 0)) return -5;
   if (Hq / q_l > n_dst || (Hkv > 0 && Hkv / kv_l > n_dst)) return -5;
-  if (n_rot > 0 && (cosT == nullptr || sinT == nullptr)) return -5;
+  if (n_rot > 0 && cs == nullptr) return -5;
   Operand oa{A, M, K, lda, false, 0, 0}, ob{B, N, K, ldb, b_mn != 0, 1, (long long)N * K};
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
@@ -600,7 +605,7 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
   p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
-  p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cosT = cosT; p.sinT = sinT;
+  p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cs = (const __half2*)cs;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return b_mn ? launch_heads<true>(ma, mb, dst, p, tiles, stream) : launch_heads<false>(ma, mb, dst, p, tiles, stream);
 }

@@ -82,6 +82,7 @@ class Attention(nn.Module):
         self._qkv_weight = None
         self._rope_cache: dict = {}
         self._rope_cache_full: dict = {}
+        self._rope_cache_fp16: dict = {}
 
     def _post_flatten(self) -> None:
         self._qkv_weight = fuse_adjacent([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
@@ -94,6 +95,14 @@ class Attention(nn.Module):
             self._rope_cache = {key: oracle.rope_tables(pos, self.head_dim, self.config.rope_theta,
                                                         self.config.rope_variant)}
         return self._rope_cache[key]
+
+    def _rope_fp16(self, T_local: int, device) -> torch.Tensor:
+        """(cos, sin) pairs in fp16 for the fused projection epilogue."""
+        from ...ops import native
+        key = (parallel_state.get_sep_rank() * T_local, T_local, str(device))
+        if key not in self._rope_cache_fp16:
+            self._rope_cache_fp16 = {key: native.rope_table_fp16(*self._rope(T_local, device))}
+        return self._rope_cache_fp16[key]
 
     def _rope_full(self, T_full: int, device) -> tuple[torch.Tensor, torch.Tensor]:
         key = ("full", T_full, str(device))
@@ -125,15 +134,16 @@ class Attention(nn.Module):
         if F_ops.qkv_project_fused_ok(h, self._qkv_weight, hd, T_local):
             # CUDA: projection + RoPE (+ the seq->head exchange) are one GEMM with a head-scatter epilogue
             if sp == 1:
-                qkv = F_ops.qkv_project(h, self._qkv_weight, cos, sin, B, T_local, Hq, Hkv, hd)
+                qkv = F_ops.qkv_project(h, self._qkv_weight, cos, sin, self._rope_fp16(T_local, h.device), B, T_local,
+                                        Hq, Hkv, hd)
                 o = F_ops.attention_packed(qkv, Hq, Hkv, True)
                 y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
                 return y.view(shape)
             from ...parallel.sequence_parallel import ulysses_peer
             if self._peer_path(h, sp) and ulysses_peer.fused_ok(Hq, Hkv, sp, hd, T_local):
                 cos_f, sin_f = self._rope_full(T_local * sp, h.device)
-                qkv_l = ulysses_peer.qkv_project_scatter(h, self._qkv_weight, Hq, Hkv, hd, B, T_local, cos, sin,
-                                                         cos_f, sin_f, id(self), group)
+                qkv_l = ulysses_peer.qkv_project_scatter(h, self._qkv_weight, Hq, Hkv, hd, B, T_local,
+                                                         self._rope_fp16(T_local, h.device), cos_f, sin_f, id(self), group)
                 y = ulysses_peer.attention_out_project(qkv_l, self.c_proj.weight, Hq, Hkv, id(self), group)
                 return y.view(shape)
         if self._qkv_weight is not None:

@@ -1,12 +1,14 @@
 """Per-kernel timing against the measured roofline.
 
-    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,attn,elementwise] [--small]
+    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,attn,elementwise,moe] [--small] [--once]
 
 Times each kernel with CUDA events on the launching stream after warm-up,
 flushing L2 (a 256 MB write) between timed launches, and prints one JSON line
 per case with achieved TFLOP/s or GB/s and, when a peaks file is present
 (`MEASURED_PEAKS.json`), the fraction of the measured cuBLAS / copy peak. The
 library GEMM (`torch.matmul`, cuBLAS) is timed on the same shapes for context.
+`--once` launches every kernel a single time without timing (the workload for a
+profiler capture).
 """
 from __future__ import annotations
 
@@ -30,8 +32,15 @@ def _peaks():
 _FLUSH = None
 
 
+_ONCE = False
+
+
 def _time(fn, iters=10, warmup=3):
     global _FLUSH
+    if _ONCE:
+        fn()
+        torch.cuda.synchronize()
+        return 1.0, 1.0
     if _FLUSH is None:
         _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
@@ -66,7 +75,7 @@ def bench_gemm(small: bool):
                  ("tn_acc", lambda: native.gemm_tn_accum(dy, x, acc), lambda: acc.addmm_(dy.t().float(), x.float()) if False else dy.t() @ x)]
         for kind, ours, lib in cases:
             med, best = _time(ours)
-            lmed, _ = _time(lib)
+            lmed, _ = (1.0, 1.0) if _ONCE else _time(lib)
             rec = {"kernel": f"gemm_{kind}", "case": name, "M": m, "N": n, "K": k, "ms": round(med, 4),
                    "ms_best": round(best, 4), "tflops": round(flops / med / 1e9, 1), "cublas_ms": round(lmed, 4),
                    "cublas_tflops": round(flops / lmed / 1e9, 1)}
@@ -128,12 +137,53 @@ def bench_attn(small: bool):
         print(json.dumps(rec), flush=True)
 
 
+def bench_moe(small: bool):
+    """Routing, gather / combine and the head-scatter (QKV + RoPE) GEMM epilogue."""
+    import ctypes
+    from . import oracle
+    bw = _peaks().get("hbm_gbs")
+    M, E, k, D = (4096 if small else 32768), 8, 2, 1024
+    logits = torch.randn(M, E, device="cuda").bfloat16()
+    x = torch.randn(M, D, device="cuda").bfloat16()
+    w, ex, counts, base, pos, order = native.moe_route(logits, k)
+    y = torch.randn(M * k, D, device="cuda").bfloat16()
+    cases = [("moe_route (3 kernels)", lambda: native.moe_route(logits, k), M * E * 2 + M * k * 16),
+             ("moe_gather", lambda: native.moe_gather(x, order, k), M * k * D * 4),
+             ("moe_combine", lambda: native.moe_combine(y, pos, w, M, k), M * k * D * 2 + M * D * 2),
+             ("moe_pair_dot", lambda: native.moe_pair_dot(x, y, pos, k), M * k * D * 4)]
+    for name, fn, nbytes in cases:
+        med, best = _time(fn)
+        rec = {"kernel": name, "ms": round(med, 4), "algorithmic_GB": round(nbytes / 1e9, 4), "GBps": round(nbytes / med / 1e6, 1)}
+        if bw:
+            rec["frac_of_measured_copy_bw"] = round(nbytes / med / 1e6 / bw, 3)
+        print(json.dumps(rec), flush=True)
+    B, T, Hq, Hkv, hd = (1 if small else 8), 4096, 16, 8, 64
+    h = torch.randn(B * T, D, device="cuda").bfloat16()
+    wq = (torch.randn((Hq + 2 * Hkv) * hd, D, device="cuda") * 0.02).bfloat16()
+    cos, sin = oracle.rope_tables(torch.arange(T, device="cuda"), hd, 10000.0, "reference")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    out = torch.empty(B, T, Hq + 2 * Hkv, hd, device="cuda", dtype=torch.bfloat16)
+    dst = (ctypes.c_void_p * 1)(out.data_ptr())
+    cs = native.rope_table_fp16(cos, sin)
+    fn = lambda: native.gemm_heads(h, wq, False, dst, 1, B, T, T, Hq + 2 * Hkv, 0, Hq, Hkv, Hq, Hkv, hd, Hq + Hkv, cs)
+    med, best = _time(fn)
+    fl = 2.0 * B * T * D * (Hq + 2 * Hkv) * hd
+    rec = {"kernel": "gemm_heads (QKV + RoPE epilogue)", "M": B * T, "N": (Hq + 2 * Hkv) * hd, "K": D, "ms": round(med, 4),
+           "tflops": round(fl / med / 1e9, 1)}
+    pk = _peaks().get("bf16_tflops")
+    if pk:
+        rec["frac_of_measured_peak"] = round(fl / med / 1e9 / pk, 3)
+    print(json.dumps(rec), flush=True)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,elementwise,attn")
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures)")
+    ap.add_argument("--once", action="store_true", help="launch each kernel once, no timing (profiler workload)")
     a = ap.parse_args()
+    _ONCE = a.once
     torch.cuda.set_device(0)
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise, "attn": bench_attn}[w](a.small)
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "attn": bench_attn, "moe": bench_moe}[w](a.small)
     native.raise_on_device_status()

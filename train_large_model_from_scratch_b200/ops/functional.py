@@ -171,7 +171,7 @@ class _QKVProject(torch.autograd.Function):
     and runs the weight- and data-gradient GEMMs on it."""
 
     @staticmethod
-    def forward(ctx, h, weight, cos, sin, B, T, n_q, n_kv, hd):
+    def forward(ctx, h, weight, cos, sin, cs, B, T, n_q, n_kv, hd):
         ctx.save_for_backward(h, cos, sin)
         ctx.weight, ctx.n_rot = weight, n_q + n_kv
         Ht = n_q + 2 * n_kv
@@ -179,7 +179,7 @@ class _QKVProject(torch.autograd.Function):
         import ctypes
         dst = (ctypes.c_void_p * 1)(out.data_ptr())
         native.gemm_heads(h, weight, False, dst, 1, B, T, T, Ht, 0, n_q, n_kv, n_q, max(n_kv, 1), hd,
-                          n_q + n_kv, cos, sin)
+                          n_q + n_kv, cs)
         return out
 
     @staticmethod
@@ -190,16 +190,16 @@ class _QKVProject(torch.autograd.Function):
         d2 = d.view(h.shape[0], -1)
         native.gemm_tn_accum(d2, h, _main_grad(w))
         dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
-        return dh, None, None, None, None, None, None, None, None
+        return dh, None, None, None, None, None, None, None, None, None
 
 
 def qkv_project_fused_ok(h: torch.Tensor, weight: torch.Tensor | None, hd: int, T: int) -> bool:
     return weight is not None and _use_native(h, weight) and native.heads_epilogue_ok(hd, T)
 
 
-def qkv_project(h, weight, cos, sin, B: int, T: int, n_q: int, n_kv: int, hd: int) -> torch.Tensor:
-    """CUDA only (check `qkv_project_fused_ok` first)."""
-    return _QKVProject.apply(h, weight, cos, sin, B, T, n_q, n_kv, hd)
+def qkv_project(h, weight, cos, sin, cs, B: int, T: int, n_q: int, n_kv: int, hd: int) -> torch.Tensor:
+    """CUDA only (check `qkv_project_fused_ok` first). `cs` = `native.rope_table_fp16(cos, sin)`."""
+    return _QKVProject.apply(h, weight, cos, sin, cs, B, T, n_q, n_kv, hd)
 
 
 # --------------------------------------------------------------------------- attention

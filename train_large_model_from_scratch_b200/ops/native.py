@@ -49,7 +49,7 @@ _SIGS = {
     "tlm_take_device_status": (_c.c_uint, []),
     "tlm_num_sms": (_I, []),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
-    "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
     "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
@@ -203,12 +203,19 @@ def heads_epilogue_ok(hd: int, rows_per_batch: int, n_dst: int = 1) -> bool:
     return hd in (64, 128) and rows_per_batch % 32 == 0 and 1 <= n_dst <= 8
 
 
+def rope_table_fp16(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """`[T, hd]` fp32 cos / sin tables -> `[T, hd, 2]` fp16 (cos, sin) pairs, the table format of the
+    head-scatter GEMM epilogue."""
+    return torch.stack([cos, sin], dim=-1).to(torch.float16).contiguous()
+
+
 def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: int, batch: int, rows_per_batch: int,
                dst_rows: int, dst_heads: int, row_off: int, n_q: int, n_kv: int, q_l: int, kv_l: int, hd: int,
-               n_rot: int, cos: torch.Tensor | None, sin: torch.Tensor | None) -> None:
+               n_rot: int, cs: torch.Tensor | None) -> None:
     """Projection GEMM with the head-scatter epilogue (`csrc/gemm.cu`, `tlm_gemm_heads`):
     `x [batch*rows_per_batch, K]` times `w` (`[N, K]`, or `[K, N]` when `b_mn`), N = (n_q + 2 n_kv) * hd;
-    head h of row (b, t) -> RoPE (heads < n_rot) -> `dst[owner(h)][b, row_off + t, slot(h), :]`.
+    head h of row (b, t) -> RoPE (heads < n_rot, table `cs` from `rope_table_fp16`) ->
+    `dst[owner(h)][b, row_off + t, slot(h), :]`.
     `dst_ptrs` is a ctypes array of `n_dst` device addresses (this rank's own tensor or peers' buffers)."""
     M, K, lda = _rows(x)
     if b_mn:
@@ -216,9 +223,10 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: in
     else:
         N, K2, ldb = _rows(w)
     assert K == K2 and M == batch * rows_per_batch
+    assert cs is None or (cs.dtype == torch.float16 and cs.shape == (rows_per_batch, hd, 2) and cs.is_contiguous())
     _check(lib().tlm_gemm_heads(x.data_ptr(), w.data_ptr(), M, N, K, lda, ldb, int(b_mn), dst_ptrs, n_dst, batch,
                                 rows_per_batch, dst_rows, dst_heads, row_off, n_q, n_kv, q_l, kv_l, hd, n_rot,
-                                _ptr(cos), _ptr(sin), _stream()), "gemm_heads")
+                                _ptr(cs), _stream()), "gemm_heads")
 
 
 def gemm_raw(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi) -> None:

@@ -187,14 +187,14 @@ class _QKVProjectScatter(torch.autograd.Function):
     feeds the weight- and data-gradient GEMMs."""
 
     @staticmethod
-    def forward(ctx, h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group):
+    def forward(ctx, h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
         st = PeerState.get(group)
         sp, me = st.sp, st.me
         _, q_l, kv_l = ulysses.head_plan(n_q, n_kv, sp)
         hpr = q_l + 2 * kv_l
         ex = st.buffer((layer_key, "qkv"), (B, sp * T_l, hpr, hd), h.device)
         native.gemm_heads(h, weight, False, ex.peer.ptr_array, sp, B, T_l, sp * T_l, hpr, me * T_l, n_q, n_kv,
-                          q_l, kv_l, hd, n_q + n_kv, cos_l, sin_l)
+                          q_l, kv_l, hd, n_q + n_kv, cs_l)
         st.barrier()
         ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
         ctx.weight = weight
@@ -214,7 +214,7 @@ class _QKVProjectScatter(torch.autograd.Function):
         d2 = ex.tensor.view(B * T_l, -1)
         native.gemm_tn_accum(d2, h, _main_grad(w))
         dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
-        return (dh,) + (None,) * 12
+        return (dh,) + (None,) * 11
 
 
 class _AttnOutProject(torch.autograd.Function):
@@ -255,7 +255,7 @@ class _AttnOutProject(torch.autograd.Function):
         native.gemm_tn_accum(dy, o_seq, _main_grad(w))
         ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), dy.device)
         native.gemm_heads(dy, w, True, ex.peer.ptr_array, st.sp, B, T_l, T_full, q_l, st.me * T_l, n_q, 0, q_l, 1,
-                          hd, 0, None, None)
+                          hd, 0, None)
         st.barrier()
         dqkv = attention_cuda.bwd(ex.tensor, qkv_l, o, lse, q_l, kv_l, True)
         return dqkv, None, None, None, None, None
@@ -268,8 +268,9 @@ def fused_ok(n_q: int, n_kv: int, sp: int, hd: int, T_l: int) -> bool:
             and os.environ.get("TLM_SP_FUSED", "1") != "0")       # 0: keep the stand-alone scatter kernels
 
 
-def qkv_project_scatter(h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group):
-    return _QKVProjectScatter.apply(h, weight, n_q, n_kv, hd, B, T_l, cos_l, sin_l, cos_f, sin_f, layer_key, group)
+def qkv_project_scatter(h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
+    """`cs_l` = `native.rope_table_fp16` of this rank's positions; `cos_f` / `sin_f`: fp32 tables of the full sequence."""
+    return _QKVProjectScatter.apply(h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group)
 
 
 def attention_out_project(qkv_l, weight, n_q, n_kv, layer_key, group):
