@@ -161,6 +161,25 @@ def test_gemm_heads_scatter_plan(nat):
         assert float(bufs[r][:, :me * T_l].abs().max()) == 0.0            # rows of the other source stay untouched
 
 
+@pytest.mark.parametrize("M,I,K", [(200, 128, 64), (512, 384, 256), (4096, 1024, 512)])
+def test_gemm_swiglu_epilogues(nat, M, I, K):
+    """gate|up GEMM that also emits act, and the down-projection dgrad that emits d(gate|up), against the
+    separate GEMM and SwiGLU kernels' math in fp32."""
+    x, w = _rand(M, K, seed=50), _rand(2 * I, K, scale=0.1, seed=51)
+    gu, act = nat.gemm_swiglu(x, w)
+    ref_gu = x.float() @ w.float().t()
+    assert _rel_err(gu, ref_gu) < 6e-3
+    g, u = gu.float().chunk(2, -1)                        # act is defined on the bf16-rounded gate / up
+    assert _rel_err(act, torch.nn.functional.silu(g) * u) < 5e-3
+    D = K
+    dy, wd = _rand(M, D, seed=52), _rand(D, I, scale=0.1, seed=53)
+    dgu = nat.gemm_swiglu_bwd(dy, wd, gu)
+    dact = (dy.float() @ wd.float()).to(torch.bfloat16).float()
+    sig = torch.sigmoid(g)
+    ref = torch.cat([dact * u * sig * (1 + g * (1 - sig)), dact * g * sig], -1)
+    assert _rel_err(dgu, ref) < 6e-3
+
+
 def test_swiglu(nat):
     gu = _rand(77, 2 * 384, seed=13)
     act = nat.swiglu_fwd(gu)

@@ -37,7 +37,7 @@ constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5 };
 
 // Destinations of the head-scatter epilogue: one 4-D map (hd, heads, T, B; box 64 x 1 x 32 x 1)
 // per rank of the sequence-parallel group; entry 0 alone when the output stays local.
@@ -69,6 +69,13 @@ struct GemmParams {
   int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot;
   const __half2* cs;        // [rows_per_batch, hd] (cos, sin) pairs in fp16: |error| < 2^-11, below the bf16 rounding of
                             // the rotated outputs, and half the table bytes of two fp32 tables
+  // EPI_SWIGLU (MLP forward): B is the fused [2 I, K] weight (gate rows, then up rows), N = I. A tile holds the
+  //   SAME 128 columns of gate and of up (two 128-row B boxes), and the epilogue writes three bf16 tiles:
+  //   gate and up into C = gate_up [M, 2 I] (kept for backward) and silu(gate) * up into act [M, I].
+  // EPI_SWIGLU_BWD (MLP backward): C' = dy W_down is d(act); the epilogue reads gate / up of the same rows and
+  //   columns from `aux` ([M, 2 I], row pitch 2 N) and writes d(gate), d(up) into C = d(gate_up) [M, 2 I].
+  // Both round their GEMM result to bf16 first, so the numbers equal the separate GEMM + SwiGLU kernels'.
+  const __nv_bfloat16* aux;
   // Row-scatter epilogue (bf16 store, grouped rows): output row r is not written to C but to
   //   rs_dst[rs_rank[r]] + rs_row[r] * ldc   (rows with rs_rank[r] < 0 are dropped).
   // This is the expert-parallel combine: the down-projection's accumulator goes straight to the
@@ -89,7 +96,7 @@ struct TileCoord {
   bool valid;
 };
 
-__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n) {
+__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n, int tile_n) {
   // split-major order: CTAs that run together work on different output tiles, so the red.global passes of
   // the k-splits of one tile do not collide in time
   const int n_out = tiles_m * tiles_n;
@@ -103,7 +110,7 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in
   int r = tile - band * GROUP_M * tiles_n;
   int tm = first_m + r % gm, tn = r / gm;
   TileCoord t;
-  t.m0 = tm * BM; t.n0 = tn * BN; t.a_row0 = t.m0; t.b_grp = 0;
+  t.m0 = tm * BM; t.n0 = tn * tile_n; t.a_row0 = t.m0; t.b_grp = 0;
   t.k_lo = ks * p.k_chunk; t.k_hi = min(p.K, t.k_lo + p.k_chunk); t.m_end = p.M; t.c_off = 0; t.valid = t.k_hi > t.k_lo;
   return t;
 }
@@ -143,14 +150,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_n = (p.N + BN - 1) / BN;
+  constexpr int TILE_N = EPI == EPI_SWIGLU ? 128 : BN;      // output columns per tile (SwiGLU: 128 gate + 128 up)
+  const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
   int tiles_m, total_tiles;
   if (p.groups == 0) { tiles_m = (p.M + BM - 1) / BM; total_tiles = tiles_m * tiles_n * p.split_k; }
   else if (p.group_mode == 1) { tiles_m = p.max_tiles_m; total_tiles = p.groups * tiles_m * tiles_n; }
   else { tiles_m = (p.M + BM - 1) / BM; total_tiles = p.groups * tiles_m * tiles_n; }
 
   auto get_tile = [&](int tile) -> TileCoord {
-    if (p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n);
+    if (p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n, TILE_N);
     TileCoord t;
     int per = tiles_m * tiles_n;
     int g = tile / per, r = tile - g * per;
@@ -187,6 +195,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * BOX_MN_BYTES, &tmB, full_bar(stage), t.n0 + 64 * j, k0, t.b_grp);
+          } else if (EPI == EPI_SWIGLU) {       // 128 gate rows, then the matching 128 up rows
+            tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, 0);
+            tma_load_3d(sb + B_BYTES / 2, &tmB, full_bar(stage), k0, p.N + t.n0, 0);
           } else {
             tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, t.b_grp);
           }
@@ -367,6 +378,92 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             }
           }
         }
+      } else if (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) {
+        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const int row0 = t.m0 + q * 32;
+        int bsel = 0;
+        // 64 bf16 columns (32 packed words) of this lane's row -> swizzled staging tile -> TMA store at (col, row0)
+        auto put = [&](const uint32_t* w, const CUtensorMap* map, int col) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          uint8_t* rowp = ebuf + bsel * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < p.M)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"((uint64_t)map), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(col), "r"(row0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          bsel ^= 1;
+        };
+        if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {                      // two 64-column halves of the tile's 128 act columns
+            uint32_t pg[32], pu[32], pa[32];
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              uint32_t g[32], u[32];
+              tmem_ld32(taddr + h * 64 + part * 32, g);
+              tmem_ld32(taddr + 128 + h * 64 + part * 32, u);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const uint32_t gw = pack_bf16(__uint_as_float(g[i]), __uint_as_float(g[i + 1]));
+                const uint32_t uw = pack_bf16(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+                const float2 gf = unpack_bf16(gw), uf = unpack_bf16(uw);
+                pg[part * 16 + (i >> 1)] = gw;
+                pu[part * 16 + (i >> 1)] = uw;
+                pa[part * 16 + (i >> 1)] = pack_bf16(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x,
+                                                     __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
+              }
+            }
+            const int col = t.n0 + h * 64;
+            put(pg, &tmC, col);
+            put(pu, &tmC, p.N + col);
+            put(pa, dst_maps, col);
+          }
+        } else {
+          const bool row_in = row < p.M;
+#pragma unroll 1
+          for (int slab = 0; slab < BN / 64; ++slab) {
+            const int col = t.n0 + slab * 64;
+            uint32_t d0[32], d1[32];
+            tmem_ld32(taddr + slab * 64, d0);
+            tmem_ld32(taddr + slab * 64 + 32, d1);
+            uint4 gv[8], uv[8];
+            if (row_in && col < p.N) {
+              const uint4* gp = reinterpret_cast<const uint4*>(p.aux + (long long)row * 2 * p.N + col);
+              const uint4* up = reinterpret_cast<const uint4*>(p.aux + (long long)row * 2 * p.N + p.N + col);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { gv[i] = gp[i]; uv[i] = up[i]; }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { gv[i] = make_uint4(0, 0, 0, 0); uv[i] = make_uint4(0, 0, 0, 0); }
+            }
+            tmem_ld_wait();
+            uint32_t pdg[32], pdu[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {                   // word i = columns 2i, 2i+1 of the slab
+              const uint32_t* dsrc = i < 16 ? d0 : d1;
+              const int j = (i & 15) * 2;
+              const float2 dd = unpack_bf16(pack_bf16(__uint_as_float(dsrc[j]), __uint_as_float(dsrc[j + 1])));
+              const uint32_t gw = reinterpret_cast<const uint32_t*>(gv)[i], uw = reinterpret_cast<const uint32_t*>(uv)[i];
+              const float2 a = unpack_bf16(gw), b = unpack_bf16(uw);
+              const float s0 = __fdividef(1.f, 1.f + __expf(-a.x)), s1 = __fdividef(1.f, 1.f + __expf(-a.y));
+              pdg[i] = pack_bf16(dd.x * b.x * s0 * (1.f + a.x * (1.f - s0)), dd.y * b.y * s1 * (1.f + a.y * (1.f - s1)));
+              pdu[i] = pack_bf16(dd.x * a.x * s0, dd.y * a.y * s1);
+            }
+            if (col < p.N) {                                 // warp-uniform
+              put(pdg, &tmC, col);
+              put(pdu, &tmC, p.N + col);
+            }
+          }
+        }
       } else if (EPI == EPI_BF16 && p.tma_store) {
         // 64-column slabs: TMEM -> bf16 -> swizzled staging tile -> TMA store (clips at the matrix edge).
         uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
@@ -462,7 +559,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       if (lane == 0) mbar_arrive(acce_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (((EPI == EPI_BF16 && p.tma_store) || EPI == EPI_HEADS) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (((EPI == EPI_BF16 && p.tma_store) || EPI == EPI_HEADS || EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) && lane == 0)
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ------------------------------------------------------------------ teardown
@@ -487,6 +585,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_heads_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ HeadDstMaps dst, const GemmParams p) {
   gemm_body<false, B_MN, EPI_HEADS>(tmA, tmB, tmA, p, dst.m);
+}
+
+// MLP forward / backward with the SwiGLU math in the epilogue: `tmC` is the [M, 2 I] tensor the epilogue
+// stores gate|up (forward) or d(gate)|d(up) (backward) into, `tmD` the forward's act [M, I].
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_swiglu_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  gemm_body<false, false, EPI_SWIGLU>(tmA, tmB, tmC, p, &tmD);
+}
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_swiglu_bwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  gemm_body<false, true, EPI_SWIGLU_BWD>(tmA, tmB, tmC, p, nullptr);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -610,6 +721,73 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   return b_mn ? launch_heads<true>(ma, mb, dst, p, tiles, stream) : launch_heads<false>(ma, mb, dst, p, tiles, stream);
 }
 
+static int store_map_bf16(CUtensorMap* m, void* base, long long rows, long long cols, long long ld) {
+  uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows}, strides[1] = {(uint64_t)ld * 2};
+  uint32_t box[2] = {64, 32};
+  return make_tmap_bf16(m, base, 2, dims, strides, box);
+}
+
+// gate_up[M, 2 I] = x[M, K] * w_gu[2 I, K]^T  and  act[M, I] = silu(gate) * up, in one kernel.
+// Requirements: I % 128 == 0, contiguous outputs (row pitches 2 I and I).
+TLM_API int tlm_gemm_swiglu(const void* x, const void* w_gu, void* gate_up, void* act, int M, int I, int K,
+                            long long lda, long long ldb, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if (I % 128 != 0) return -4;
+  Operand oa{x, M, K, lda, false, 0, 0}, ob{w_gu, 2LL * I, K, ldb, false, 1, 2LL * I * K};
+  CUtensorMap ma, mb, mc, md;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, 128);
+  if (e) return e;
+  e = store_map_bf16(&mc, gate_up, M, 2LL * I, 2LL * I);
+  if (e) return e;
+  e = store_map_bf16(&md, act, M, I, I);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * (I / 128);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_swiglu_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, mc, md, p);
+  count_launch();
+  return launch_status();
+}
+
+// d(gate_up)[M, 2 I] from dy[M, D], w_down[D, I] (row pitch ldb) and the saved gate_up[M, 2 I]:
+// d(act) = dy * w_down never reaches memory, the epilogue applies the SwiGLU derivative.
+TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* gate_up, void* d_gate_up, int M, int I,
+                                int D, long long lda, long long ldb, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || D <= 0) return 0;
+  if (I % 8 != 0) return -4;
+  Operand oa{dy, M, D, lda, false, 0, 0}, ob{w_down, I, D, ldb, true, 1, (long long)I * D};
+  CUtensorMap ma, mb, mc;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  e = store_map_bf16(&mc, d_gate_up, M, 2LL * I, 2LL * I);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
+  p.aux = (const __nv_bfloat16*)gate_up;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((I + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_swiglu_bwd_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, mc, p);
+  count_launch();
+  return launch_status();
+}
+
 // C[M,N] = A * B^T with arbitrary operand majors.
 //   a_mn = 0: A is [M,K] (lda); a_mn = 1: A is [K,M] (lda)
 //   b_mn = 0: B is [N,K] (ldb); b_mn = 1: B is [K,N] (ldb)
@@ -629,20 +807,20 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   p.split_k = 1; p.k_chunk = K;
   if (epi == EPI_F32_ACC) {
     // Weight gradients: few output tiles, long reduction. The persistent grid runs work items (tile x k-split)
-    // of equal size, so throughput is items / (waves * SMs); pick the split that fills the last wave best,
-    // preferring fewer splits on ties (each split adds one pass of red.global over its tile). At least 16
-    // k-blocks per split keep the epilogue small against the main loop.
+    // of equal size in waves of one item per SM, so time ~ waves * (k-blocks per item + E), E = cost of one
+    // epilogue pass (fp32 read-modify-write or red.global of a 128 KB tile) in k-block units (measured ~8).
+    // Items keep at least 64 k-blocks.
     const int sms = num_sms();
     const int kblocks = (K + BK - 1) / BK;
-    int max_split = kblocks / 16;
+    int max_split = kblocks / 64;
     if (max_split > 16) max_split = 16;
     int best = 1;
-    double best_eff = 0.0;
+    double best_cost = 1e30;
     for (int sp = 1; sp <= (max_split > 1 ? max_split : 1); ++sp) {
       const long long items = (long long)tiles * sp;
       const long long waves = (items + sms - 1) / sms;
-      const double eff = (double)items / (double)(waves * sms) - 0.004 * (sp - 1);
-      if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
+      const double cost = (double)waves * ((double)((kblocks + sp - 1) / sp) + 8.0);
+      if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
     }
     if (best > 1) {
       const int per = (kblocks + best - 1) / best;

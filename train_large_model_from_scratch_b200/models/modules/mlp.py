@@ -50,6 +50,8 @@ class MLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x = x.reshape(-1, shape[-1]).to(self.gate_proj.weight.dtype)
+        if F_ops.swiglu_mlp_fused_ok(x, self._gate_up_weight):
+            return F_ops.swiglu_mlp(x, self._gate_up_weight, self.down_proj.weight).view(shape)
         if self._gate_up_weight is not None:
             gu = F_ops.linear(x, self._gate_up_weight)
         else:

@@ -295,6 +295,40 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(gate_up)
 
 
+class _SwiGLUMLP(torch.autograd.Function):
+    """`down(silu(gate(x)) * up(x))` on CUDA with the SwiGLU math inside GEMM epilogues: the gate|up GEMM also
+    emits `act`, and in backward the data-gradient GEMM of the down projection turns d(act) into d(gate|up)
+    while the accumulator is still in registers. Five GEMMs forward + backward become the only kernels of the
+    MLP (no separate SwiGLU passes, d(act) never reaches memory)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down):
+        gu, act = native.gemm_swiglu(x, w_gu)
+        ctx.save_for_backward(x, gu, act)
+        ctx.w_gu, ctx.w_down = w_gu, w_down
+        return native.gemm_nt(act, w_down)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gu, act = ctx.saved_tensors
+        w_gu, w_down = ctx.w_gu, ctx.w_down
+        dy = dy.contiguous()
+        native.gemm_tn_accum(dy, act, _main_grad(w_down))
+        dgu = native.gemm_swiglu_bwd(dy, w_down, gu)
+        native.gemm_tn_accum(dgu, x, _main_grad(w_gu))
+        dx = native.gemm_nn(dgu, w_gu) if ctx.needs_input_grad[0] else None
+        return dx, None, None
+
+
+def swiglu_mlp_fused_ok(x: torch.Tensor, w_gu: torch.Tensor | None) -> bool:
+    return w_gu is not None and _use_native(x, w_gu) and native.swiglu_epilogue_ok(w_gu.shape[0] // 2)
+
+
+def swiglu_mlp(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """CUDA only (check `swiglu_mlp_fused_ok` first). `w_gu` is the fused `[2 I, D]` gate|up weight."""
+    return _SwiGLUMLP.apply(x, w_gu, w_down)
+
+
 # --------------------------------------------------------------------------- fused LM head + cross-entropy
 class _LinearCrossEntropy(torch.autograd.Function):
     """`sum_i CE(h_i @ W^T, target_i)` without keeping the `[M, V]` logits.

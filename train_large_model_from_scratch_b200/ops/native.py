@@ -50,6 +50,8 @@ _SIGS = {
     "tlm_num_sms": (_I, []),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
+    "tlm_gemm_swiglu": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
+    "tlm_gemm_swiglu_bwd": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
     "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
     "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
@@ -227,6 +229,36 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: in
     _check(lib().tlm_gemm_heads(x.data_ptr(), w.data_ptr(), M, N, K, lda, ldb, int(b_mn), dst_ptrs, n_dst, batch,
                                 rows_per_batch, dst_rows, dst_heads, row_off, n_q, n_kv, q_l, kv_l, hd, n_rot,
                                 _ptr(cs), _stream()), "gemm_heads")
+
+
+def swiglu_epilogue_ok(I: int) -> bool:
+    return I % 128 == 0
+
+
+def gemm_swiglu(x: torch.Tensor, w_gu: torch.Tensor):
+    """`gate_up = x @ w_gu^T` (`w_gu` = `[2 I, K]`, gate rows then up rows) and `act = silu(gate) * up`
+    from one kernel. Returns `(gate_up [M, 2 I], act [M, I])`, both bf16."""
+    M, K, lda = _rows(x)
+    N2, K2, ldb = _rows(w_gu)
+    I = N2 // 2
+    assert K == K2 and N2 % 2 == 0 and swiglu_epilogue_ok(I)
+    gu = torch.empty(M, N2, dtype=torch.bfloat16, device=x.device)
+    act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
+    _check(lib().tlm_gemm_swiglu(x.data_ptr(), w_gu.data_ptr(), gu.data_ptr(), act.data_ptr(), M, I, K, lda, ldb,
+                                 _stream()), "gemm_swiglu")
+    return gu, act
+
+
+def gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    """`d(gate_up) [M, 2 I]` from `dy [M, D]`, `w_down [D, I]` and the saved `gate_up`: the data-gradient
+    GEMM `dy @ w_down` with the SwiGLU derivative in its epilogue."""
+    M, D, lda = _rows(dy)
+    D2, I, ldb = _rows(w_down)
+    assert D == D2 and gu.shape == (M, 2 * I) and gu.is_contiguous() and gu.dtype == torch.bfloat16
+    dgu = torch.empty_like(gu)
+    _check(lib().tlm_gemm_swiglu_bwd(dy.data_ptr(), w_down.data_ptr(), gu.data_ptr(), dgu.data_ptr(), M, I, D, lda, ldb,
+                                     _stream()), "gemm_swiglu_bwd")
+    return dgu
 
 
 def gemm_raw(a, b, c, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi) -> None:
