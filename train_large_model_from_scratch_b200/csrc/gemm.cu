@@ -428,40 +428,74 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             put(pa, dst_maps, col);
           }
         } else {
-          const bool row_in = row < p.M;
+          // d(act) leaves tensor memory one row per lane, but the derivative is elementwise, so the warp stages
+          // the bf16 tile in shared memory and re-reads it with 8 lanes per row: gate / up then come from global
+          // memory as whole 128-byte rows (4 rows per load instruction instead of 32 scattered pieces) and the
+          // results go back the same way.
+          uint8_t* bufA = ebuf;
+          uint8_t* bufB = ebuf + EPI_BUF_BYTES;
+          const int sub_row = lane >> 3, chunk = lane & 7;    // this lane's (row within a group of 4, 16-byte chunk)
 #pragma unroll 1
           for (int slab = 0; slab < BN / 64; ++slab) {
             const int col = t.n0 + slab * 64;
+            if (col >= p.N) break;                             // warp-uniform
             uint32_t d0[32], d1[32];
             tmem_ld32(taddr + slab * 64, d0);
             tmem_ld32(taddr + slab * 64 + 32, d1);
-            uint4 gv[8], uv[8];
-            if (row_in && col < p.N) {
-              const uint4* gp = reinterpret_cast<const uint4*>(p.aux + (long long)row * 2 * p.N + col);
-              const uint4* up = reinterpret_cast<const uint4*>(p.aux + (long long)row * 2 * p.N + p.N + col);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) { gv[i] = gp[i]; uv[i] = up[i]; }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) { gv[i] = make_uint4(0, 0, 0, 0); uv[i] = make_uint4(0, 0, 0, 0); }
-            }
             tmem_ld_wait();
-            uint32_t pdg[32], pdu[32];
+            uint8_t* buf = (slab & 1) ? bufB : bufA;           // alternate, so staging slab s+1 cannot overtake readers of slab s
+            {
+              uint8_t* rowp = buf + lane * 128;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {                   // word i = columns 2i, 2i+1 of the slab
-              const uint32_t* dsrc = i < 16 ? d0 : d1;
-              const int j = (i & 15) * 2;
-              const float2 dd = unpack_bf16(pack_bf16(__uint_as_float(dsrc[j]), __uint_as_float(dsrc[j + 1])));
-              const uint32_t gw = reinterpret_cast<const uint32_t*>(gv)[i], uw = reinterpret_cast<const uint32_t*>(uv)[i];
-              const float2 a = unpack_bf16(gw), b = unpack_bf16(uw);
-              const float s0 = __fdividef(1.f, 1.f + __expf(-a.x)), s1 = __fdividef(1.f, 1.f + __expf(-a.y));
-              pdg[i] = pack_bf16(dd.x * b.x * s0 * (1.f + a.x * (1.f - s0)), dd.y * b.y * s1 * (1.f + a.y * (1.f - s1)));
-              pdu[i] = pack_bf16(dd.x * a.x * s0, dd.y * a.y * s1);
+              for (int ch = 0; ch < 8; ++ch) {
+                const uint32_t* r = ch < 4 ? d0 : d1;
+                const int j = (ch & 3) * 8;
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                v.y = pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                v.z = pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                v.w = pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = v;
+              }
             }
-            if (col < p.N) {                                 // warp-uniform
-              put(pdg, &tmC, col);
-              put(pdu, &tmC, p.N + col);
+            // all of this slab's gate / up loads are issued before the first store (the compiler must assume the
+            // stores may alias them, so it would not hoist them itself); they overlap the staging above
+            uint4 gv[8], uv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int grow = row0 + i * 4 + sub_row;
+              gv[i] = make_uint4(0, 0, 0, 0); uv[i] = gv[i];
+              if (grow < p.M && col + chunk * 8 < p.N) {
+                const __nv_bfloat16* gp = p.aux + (long long)grow * 2 * p.N + col + chunk * 8;
+                gv[i] = *reinterpret_cast<const uint4*>(gp);
+                uv[i] = *reinterpret_cast<const uint4*>(gp + p.N);
+              }
             }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + sub_row;                   // row within the warp's 32
+              const int grow = row0 + r;
+              const uint32_t off = r * 128 + ((chunk ^ (r & 7)) << 4);
+              const bool live = grow < p.M && col + chunk * 8 < p.N;
+              const uint4 dv = *reinterpret_cast<const uint4*>(buf + off);
+              const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w}, gw[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w},
+                             uw[4] = {uv[i].x, uv[i].y, uv[i].z, uv[i].w};
+              uint32_t og[4], ou[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float2 dd = unpack_bf16(dw[k]), a = unpack_bf16(gw[k]), bb = unpack_bf16(uw[k]);
+                const float s0 = __fdividef(1.f, 1.f + __expf(-a.x)), s1 = __fdividef(1.f, 1.f + __expf(-a.y));
+                og[k] = pack_bf16(dd.x * bb.x * s0 * (1.f + a.x * (1.f - s0)), dd.y * bb.y * s1 * (1.f + a.y * (1.f - s1)));
+                ou[k] = pack_bf16(dd.x * a.x * s0, dd.y * a.y * s1);
+              }
+              if (live) {                                      // 8 lanes write one 128-byte row piece of d(gate) and of d(up)
+                __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)grow * p.ldc + col + chunk * 8;
+                *reinterpret_cast<uint4*>(op) = make_uint4(og[0], og[1], og[2], og[3]);
+                *reinterpret_cast<uint4*>(op + p.N) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              }
+            }
+            __syncwarp();
           }
         }
       } else if (EPI == EPI_BF16 && p.tma_store) {
