@@ -326,3 +326,71 @@ def test_grouped_gemm_row_scatter_epilogue(nat):
         r += c
     for b in range(2):
         assert _rel_err(bufs[b], ref[b]) < 6e-3
+
+
+def test_grouped_pair_gemms(nat):
+    """gate | up of all experts in one grouped GEMM, and the data gradient of both in one GEMM with K = 2 I."""
+    E, I, D = 3, 256, 192
+    counts = [70, 0, 130]
+    R = sum(counts)
+    x = _rand(R + 8, D, seed=60)
+    w = _rand(2 * E, I, D, scale=0.1, seed=61)
+    rs = torch.tensor([0, 70, 70, 200], dtype=torch.int32, device="cuda")
+    dc = nat.DeviceCounts(rs, R)
+    gu = nat.grouped_gemm_pair_fwd(x, w, dc)
+    dgu = _rand(R + 8, 2 * I, seed=62)
+    dx = nat.grouped_gemm_pair_dgrad(dgu, w, dc)
+    r = 0
+    for e, c in enumerate(counts):
+        if c:
+            xs = x[r:r + c].float()
+            ref = torch.cat([xs @ w[e].float().t(), xs @ w[E + e].float().t()], -1)
+            assert _rel_err(gu[r:r + c], ref) < 6e-3
+            dref = dgu[r:r + c, :I].float() @ w[e].float() + dgu[r:r + c, I:].float() @ w[E + e].float()
+            assert _rel_err(dx[r:r + c], dref) < 6e-3
+        r += c
+    # row-limited SwiGLU: rows past the device-side count stay untouched
+    n = torch.tensor([150], dtype=torch.int64, device="cuda")
+    act = nat.swiglu_fwd(gu[:R].contiguous(), n)
+    g, u = gu[:150].float().chunk(2, -1)
+    assert _rel_err(act[:150], torch.nn.functional.silu(g) * u) < 5e-3
+
+
+def test_moe_plan_kernel_matches_table_arithmetic(nat):
+    """The expert-parallel plan kernel against the same routes derived with torch ops from the count table,
+    for every rank of an emulated group of 4 (the ranks are just four independent routings on this GPU)."""
+    ep, E, k, M = 4, 8, 2, 96
+    E_l = E // ep
+    g = torch.Generator(device="cuda").manual_seed(70)
+    routes = []
+    for r in range(ep):
+        logits = (torch.rand(M, E, device="cuda", generator=g).argsort(dim=1).float() * 0.25).to(torch.bfloat16)
+        routes.append(nat.moe_route(logits, k))
+    table = torch.stack([rt[2] for rt in routes]).to(torch.int32).contiguous()          # [ep, E]
+    C = table.long()
+    tot = C.sum(0)
+    base = (torch.cumsum(tot.view(ep, E_l), 1) - tot.view(ep, E_l)).view(E)
+    src_prefix = torch.cumsum(C, 0) - C
+    start_on_src = torch.cumsum(C, 1) - C
+    for me in range(ep):
+        w, ex, counts, my_start, pos, order = routes[me]
+        plan = nat.moe_plan(table, ep, me, ex, order, my_start)
+        P = order.numel()
+        sorted_e = ex.view(-1)[order.long()].long()
+        i = torch.arange(P, device="cuda")
+        assert torch.equal(plan["send_rank"].long(), sorted_e // E_l)
+        assert torch.equal(plan["send_row"], base[sorted_e] + src_prefix[me][sorted_e] + (i - my_start.long()[sorted_e]))
+        mine = slice(me * E_l, (me + 1) * E_l)
+        n_recv = int(tot[mine].sum())
+        assert int(plan["n_recv"]) == n_recv
+        assert torch.equal(plan["row_start"].long(), torch.cat([base[mine], base[mine][-1:] + tot[mine][-1:]]))
+        # every received row points back at the pair that was sent to it
+        back_rank, back_row = plan["back_rank"].long(), plan["back_row"]
+        assert bool((back_rank[n_recv:] == -1).all())
+        for s in range(ep):
+            ws, exs, cs, starts, poss, orders = routes[s]
+            ps = nat.moe_plan(table, ep, s, exs, orders, starts)
+            to_me = ps["send_rank"].long() == me
+            rows = ps["send_row"][to_me]
+            assert bool((back_rank[rows] == s).all())
+            assert torch.equal(back_row[rows], torch.arange(orders.numel(), device="cuda")[to_me])

@@ -279,8 +279,11 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __rest
 }
 
 // ------------------------------------------------------------------ SwiGLU
+// rows_ptr (optional, device): only the first min(*rows_ptr, rows) rows are processed. Used by the MoE layer,
+// whose expert-side buffers have a worst-case row count known on the host and a real one known on the device.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long rows,
-                                  int I) {
+                                  int I, const long long* __restrict__ rows_ptr) {
+  if (rows_ptr != nullptr && *rows_ptr < rows) rows = *rows_ptr;
   const int vec = I / 8;
   const long long total = rows * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -298,7 +301,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
 }
 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ dgu, long long rows, int I) {
+                                  __nv_bfloat16* __restrict__ dgu, long long rows, int I,
+                                  const long long* __restrict__ rows_ptr) {
+  if (rows_ptr != nullptr && *rows_ptr < rows) rows = *rows_ptr;
   const int vec = I / 8;
   const long long total = rows * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -533,15 +538,16 @@ TLM_API int tlm_rope(void* qkv, const float* cosT, const float* sinT, long long 
   return launch_status();
 }
 
-TLM_API int tlm_swiglu_fwd(const void* gu, void* act, long long rows, int I, cudaStream_t st) {
-  swiglu_fwd_kernel<<<grid_for(rows * I / 8, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, rows, I);
+TLM_API int tlm_swiglu_fwd(const void* gu, void* act, long long rows, int I, const long long* rows_ptr, cudaStream_t st) {
+  swiglu_fwd_kernel<<<grid_for(rows * I / 8, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, rows, I, rows_ptr);
   count_launch();
   return launch_status();
 }
 
-TLM_API int tlm_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long rows, int I, cudaStream_t st) {
+TLM_API int tlm_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long rows, int I, const long long* rows_ptr,
+                           cudaStream_t st) {
   swiglu_bwd_kernel<<<grid_for(rows * I / 8, 256), 256, 0, st>>>((const __nv_bfloat16*)dact, (const __nv_bfloat16*)gu,
-                                                                 (__nv_bfloat16*)dgu, rows, I);
+                                                                 (__nv_bfloat16*)dgu, rows, I, rows_ptr);
   count_launch();
   return launch_status();
 }

@@ -76,6 +76,11 @@ struct GemmParams {
   //   columns from `aux` ([M, 2 I], row pitch 2 N) and writes d(gate), d(up) into C = d(gate_up) [M, 2 I].
   // Both round their GEMM result to bf16 first, so the numbers equal the separate GEMM + SwiGLU kernels'.
   const __nv_bfloat16* aux;
+  // Paired groups (grouped rows, MoE gate|up): the B map has 2 * groups matrices, gate of group g at g and up at
+  // groups + g. pair_n > 0: output columns >= pair_n come from the second matrix (forward: one GEMM writes
+  // gate|up [R, 2 I]). pair_k > 0: reduction indices >= pair_k come from the second matrix (dgrad of both
+  // projections in one GEMM with K = 2 I, so their sum needs no extra pass).
+  int pair_n, pair_k;
   // Row-scatter epilogue (bf16 store, grouped rows): output row r is not written to C but to
   //   rs_dst[rs_rank[r]] + rs_row[r] * ldc   (rows with rs_rank[r] < 0 are dropped).
   // This is the expert-parallel combine: the down-projection's accumulator goes straight to the
@@ -90,6 +95,7 @@ struct TileCoord {
   int m0, n0;       // output tile origin (row within C / column)
   int a_row0;       // row coordinate for the A operand
   int b_grp;        // third coordinate of the B map (grouped) or 0
+  int b_n0;         // row (K-major) / column (MN-major) coordinate of the tile in the B matrix; n0 unless pair_n
   int k_lo, k_hi;   // reduction range
   int m_end;        // exclusive row bound for stores
   long long c_off;  // element offset added to C
@@ -110,7 +116,7 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in
   int r = tile - band * GROUP_M * tiles_n;
   int tm = first_m + r % gm, tn = r / gm;
   TileCoord t;
-  t.m0 = tm * BM; t.n0 = tn * tile_n; t.a_row0 = t.m0; t.b_grp = 0;
+  t.m0 = tm * BM; t.n0 = tn * tile_n; t.a_row0 = t.m0; t.b_grp = 0; t.b_n0 = t.n0;
   t.k_lo = ks * p.k_chunk; t.k_hi = min(p.K, t.k_lo + p.k_chunk); t.m_end = p.M; t.c_off = 0; t.valid = t.k_hi > t.k_lo;
   return t;
 }
@@ -165,10 +171,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     int tm = r % tiles_m, tn = r / tiles_m;
     int lo = p.row_start[g], hi = p.row_start[g + 1];
     if (p.group_mode == 1) {            // rows grouped: A rows [lo,hi), B = weight[g]
-      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = g;
+      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = g; t.b_n0 = t.n0;
+      if (p.pair_n > 0 && t.n0 >= p.pair_n) { t.b_grp = g + p.groups; t.b_n0 = t.n0 - p.pair_n; }
       t.k_lo = 0; t.k_hi = p.K; t.m_end = hi; t.c_off = 0; t.valid = t.m0 < hi;
     } else {                            // reduction grouped: K range [lo,hi), C = C_base + g * stride
-      t.m0 = tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = 0;
+      t.m0 = tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = 0; t.b_n0 = t.n0;
       t.k_lo = lo; t.k_hi = hi; t.m_end = p.M; t.c_off = (long long)g * p.c_group_stride; t.valid = hi > lo;
     }
     return t;
@@ -192,14 +199,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           } else {
             tma_load_2d(sa, &tmA, full_bar(stage), k0, t.a_row0);
           }
+          int bk = k0, bg = t.b_grp;
+          if (p.pair_k > 0 && k0 >= p.pair_k) { bk = k0 - p.pair_k; bg += p.groups; }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * BOX_MN_BYTES, &tmB, full_bar(stage), t.n0 + 64 * j, k0, t.b_grp);
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * BOX_MN_BYTES, &tmB, full_bar(stage), t.b_n0 + 64 * j, bk, bg);
           } else if (EPI == EPI_SWIGLU) {       // 128 gate rows, then the matching 128 up rows
             tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, 0);
             tma_load_3d(sb + B_BYTES / 2, &tmB, full_bar(stage), k0, p.N + t.n0, 0);
           } else {
-            tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, t.b_grp);
+            tma_load_3d(sb, &tmB, full_bar(stage), bk, t.b_n0, bg);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -886,6 +895,33 @@ TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const i
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
   return dispatch(false, b_mn != 0, epi, ma, mb, p, tiles, stream);
+}
+
+// Paired grouped GEMMs for the MoE gate / up projections. `W` holds 2 * groups matrices [I, D] (gate of
+// group g at g, up at groups + g), `w_group_stride` elements apart.
+//   dgrad == 0:  C[R, 2 I] (ldc) = A[R, D] * [W_g ; W_{groups+g}]^T      gate | up side by side, I % 256 == 0
+//   dgrad == 1:  C[R, D]  (ldc) = A[R, 2 I] * [W_g ; W_{groups+g}]       both data gradients summed, I % 64 == 0
+TLM_API int tlm_gemm_grouped_pair(const void* A, const void* W, void* C, const int* row_start, int groups, int R, int I,
+                                  int D, long long lda, long long w_group_stride, long long ldc, int dgrad,
+                                  int max_rows_per_group, cudaStream_t stream) {
+  if (R <= 0 || I <= 0 || D <= 0 || groups <= 0) return 0;
+  if ((!dgrad && I % BN != 0) || (dgrad && I % BK != 0)) return -4;
+  const int N = dgrad ? D : 2 * I, K = dgrad ? 2 * I : D;
+  Operand oa{A, R, K, lda, false, 0, 0};
+  // forward: B K-major [I rows, D]; dgrad: B MN-major, stored [I (reduction), D (output)]
+  Operand ob{W, dgrad ? D : I, dgrad ? I : D, D, dgrad != 0, 2LL * groups, w_group_stride};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = R; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
+  p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  if (dgrad) p.pair_k = I; else p.pair_n = I;
+  int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
+  return dispatch(false, dgrad != 0, EPI_BF16, ma, mb, p, tiles, stream);
 }
 
 // Same as tlm_gemm_grouped_rows with a bf16 store, but output row r goes to dst_ptrs[dest_rank[r]] row dest_row[r]

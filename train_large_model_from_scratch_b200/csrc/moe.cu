@@ -11,6 +11,7 @@
 //   moe_gather   out[i, :] = scale[i] * x[order[i] / k, :]               (pairs -> expert-major rows)
 //   moe_combine  out[t, :] = sum_s w[t, s] * y[pos[t, s], :]             (expert-major rows -> tokens)
 //   moe_pair_dot dw[t, s]  = < d_out[t, :], y[pos[t, s], :] >
+//   moe_plan     expert-parallel routing plan from the all-ranks count table (send route, row ranges, back route)
 // Expert parallelism over NVLink peer memory (symmetric buffers):
 //   peer_put_i32       publish a small int32 row (per-expert counts) into every peer's table
 //   peer_scatter_rows  out[dest_rank[i]][dest_row[i], :] = scale[j] * src[j / src_div, :],  j = src_idx ? src_idx[i] : i
@@ -256,6 +257,80 @@ __global__ void moe_pair_dot_kernel(const __nv_bfloat16* __restrict__ d_out, con
   }
 }
 
+// ---------------------------------------------------------------------------------------------- expert-parallel plan
+// From the all-ranks count table C[src][expert] (ep x E, every rank holds the same copy) derive both routes of
+// the token exchange, with no host involvement:
+//   receive buffers are laid out expert-major / source-minor, so
+//     first row of expert e on its owner      base_g[e]  = sum of tot[e'] over the owner's experts e' < e
+//     first row of source s inside expert e   + sum_{s' < s} C[s'][e]
+//   send route  (i < P, my sorted pairs)      send_rank[i] = e / E_l,  send_row[i] = that + (i - my_start[e])
+//   my experts' row ranges                    row_start[0..E_l], n_recv = row_start[E_l]
+//   back route  (r < R, rows I received)      back_rank[r] = source s (or -1 past n_recv),
+//                                             back_row[r]  = (first sorted pair of e on s) + offset inside the block
+constexpr int PLAN_MAX_EP = 8;
+
+__global__ void __launch_bounds__(256)
+moe_plan_kernel(const int* __restrict__ C, int ep, int E, int me, const int* __restrict__ experts, const int* __restrict__ order,
+                const int* __restrict__ my_start, int P, long long R, int* __restrict__ send_rank,
+                long long* __restrict__ send_row, int* __restrict__ row_start, long long* __restrict__ n_recv,
+                int* __restrict__ back_rank, long long* __restrict__ back_row) {
+  __shared__ int Cs[PLAN_MAX_EP * ROUTE_MAX_E];
+  __shared__ int tot[ROUTE_MAX_E], base_g[ROUTE_MAX_E], pre_me[ROUTE_MAX_E];
+  __shared__ int blk_start[ROUTE_MAX_E], blk_cnt[ROUTE_MAX_E], blk_src_start[ROUTE_MAX_E];   // E_l * ep <= E entries
+  __shared__ int n_recv_s;
+  const int E_l = E / ep, tid = threadIdx.x;
+  for (int i = tid; i < ep * E; i += blockDim.x) Cs[i] = C[i];
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    int t = 0, pm = 0;
+    for (int s2 = 0; s2 < ep; ++s2) { if (s2 == me) pm = t; t += Cs[s2 * E + e]; }
+    tot[e] = t; pre_me[e] = pm;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    int b = 0;
+    for (int e2 = (e / E_l) * E_l; e2 < e; ++e2) b += tot[e2];
+    base_g[e] = b;
+  }
+  __syncthreads();
+  for (int b = tid; b < E_l * ep; b += blockDim.x) {         // block b = (local expert, source), expert-major
+    const int el = b / ep, s2 = b - el * ep, e = me * E_l + el;
+    int st = base_g[e];
+    for (int s3 = 0; s3 < s2; ++s3) st += Cs[s3 * E + e];
+    int on_src = 0;
+    for (int e2 = 0; e2 < e; ++e2) on_src += Cs[s2 * E + e2];
+    blk_start[b] = st; blk_cnt[b] = Cs[s2 * E + e]; blk_src_start[b] = on_src;
+  }
+  if (tid == 0) {
+    int n = 0;
+    for (int el = 0; el < E_l; ++el) n += tot[me * E_l + el];
+    n_recv_s = n;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int el = tid; el <= E_l; el += blockDim.x) row_start[el] = el < E_l ? base_g[me * E_l + el] : n_recv_s;
+    if (tid == 0) *n_recv = n_recv_s;
+  }
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + tid; i < P; i += stride) {
+    const int e = experts[order[i]];
+    send_rank[i] = e / E_l;
+    send_row[i] = (long long)base_g[e] + pre_me[e] + (i - my_start[e]);
+  }
+  const int nb = E_l * ep;
+  for (long long r = (long long)blockIdx.x * blockDim.x + tid; r < R; r += stride) {
+    if (r >= n_recv_s) { back_rank[r] = -1; back_row[r] = 0; continue; }
+    // last block with blk_start <= r among non-empty blocks: blocks are contiguous and ascending, so search the ends
+    int lo = 0, hi = nb - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if ((long long)blk_start[mid] + blk_cnt[mid] > r) hi = mid; else lo = mid + 1;
+    }
+    back_rank[r] = lo % ep;
+    back_row[r] = (long long)blk_src_start[lo] + (r - blk_start[lo]);
+  }
+}
+
 static int row_blocks(long long rows) {
   long long blocks = (rows * 32 + 255) / 256;
   if (blocks > 16LL * num_sms()) blocks = 16LL * num_sms();
@@ -302,6 +377,23 @@ TLM_API int tlm_moe_route(const void* logits, long long ld, int M, int E, int k,
   moe_scan_kernel<<<1, ROUTE_MAX_E, 0, st>>>(block_hist, blocks, E, counts, base);
   moe_slot_kernel<<<blocks, 256, 0, st>>>(experts, M, E, k, block_hist, base, pos, order);
   count_launch(3);
+  return launch_status();
+}
+
+// Expert-parallel routing plan (see moe_plan_kernel). C: [ep, E] int32 counts of every rank; experts / order /
+// my_start: this rank's routing (`tlm_moe_route` outputs experts, order, base). Outputs: send_rank [P] int32,
+// send_row [P] int64, row_start [E/ep + 1] int32, n_recv [1] int64, back_rank [R] int32, back_row [R] int64.
+TLM_API int tlm_moe_plan(const int* C, int ep, int E, int me, const int* experts, const int* order, const int* my_start,
+                         int P, long long R, int* send_rank, long long* send_row, int* row_start, long long* n_recv,
+                         int* back_rank, long long* back_row, cudaStream_t st) {
+  if (ep < 1 || ep > PLAN_MAX_EP || E < ep || E > ROUTE_MAX_E || E % ep != 0 || me < 0 || me >= ep) return -6;
+  long long n = P > R ? P : R;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 2LL * num_sms()) blocks = 2LL * num_sms();
+  if (blocks < 1) blocks = 1;
+  moe_plan_kernel<<<(int)blocks, 256, 0, st>>>(C, ep, E, me, experts, order, my_start, P, R, send_rank, send_row, row_start,
+                                               n_recv, back_rank, back_row);
+  count_launch();
   return launch_status();
 }
 

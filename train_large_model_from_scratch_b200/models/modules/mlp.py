@@ -89,6 +89,19 @@ class MoE(nn.Module):
         self.experts_up_weights = nn.Parameter(torch.stack(u))
         self.experts_down_weights = nn.Parameter(torch.stack(d))
         self.aux_loss = None
+        self._pair_weight = None
+
+    def _post_flatten(self) -> None:
+        # gate and up matrices of all local experts as one [2 E_local, I, D] operand (a view: the two parameters
+        # are adjacent in the flat expert buffer)
+        g, u = self.experts_gate_weights, self.experts_up_weights
+        buf = getattr(g, "flat_buffer", None)
+        if buf is not None and getattr(u, "flat_buffer", None) is buf and u.flat_offset == g.flat_offset + g.numel():
+            w, mg = buf.view(g.flat_offset, (2 * g.shape[0], g.shape[1], g.shape[2]))
+            w = w.detach()
+            w.requires_grad_(g.requires_grad)
+            w.main_grad = mg
+            self._pair_weight = w
 
     def forward(self, x: torch.Tensor):
         """x `[..., D]` -> (output of the same shape, router logits `[M, E]`)."""
@@ -99,6 +112,6 @@ class MoE(nn.Module):
             x2, logits, self.experts_gate_weights, self.experts_up_weights, self.experts_down_weights,
             self.top_k, self.num_experts, parallel_state.get_ep_group(), self.ep_size,
             aux_coef=self.config.moe_aux_loss_coef, capacity_factor=self.config.moe_capacity_factor,
-            layer_key=id(self))
+            layer_key=id(self), w_pair=self._pair_weight)
         self.aux_loss = aux
         return out.view(shape), logits

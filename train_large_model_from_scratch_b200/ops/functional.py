@@ -271,28 +271,30 @@ def attention_packed(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool = True
 # --------------------------------------------------------------------------- SwiGLU
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gu):
+    def forward(ctx, gu, valid_rows):
         ctx.save_for_backward(gu)
+        ctx.valid_rows = valid_rows
         if _use_native(gu):
-            return native.swiglu_fwd(gu)
+            return native.swiglu_fwd(gu, valid_rows)
         return oracle.swiglu(gu).to(gu.dtype)
 
     @staticmethod
     def backward(ctx, dact):
         (gu,) = ctx.saved_tensors
         if _use_native(gu):
-            return native.swiglu_bwd(dact.contiguous(), gu)
+            return native.swiglu_bwd(dact.contiguous(), gu, ctx.valid_rows), None
         g, u = gu.float().chunk(2, dim=-1)
         sig = torch.sigmoid(g)
         d = dact.float()
         dg = d * u * sig * (1.0 + g * (1.0 - sig))
         du = d * g * sig
-        return torch.cat([dg, du], dim=-1).to(gu.dtype)
+        return torch.cat([dg, du], dim=-1).to(gu.dtype), None
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """`[M, 2I]` (gate | up) -> `silu(gate) * up` `[M, I]`."""
-    return _SwiGLU.apply(gate_up)
+def swiglu(gate_up: torch.Tensor, valid_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """`[M, 2I]` (gate | up) -> `silu(gate) * up` `[M, I]`. `valid_rows` (CUDA only, 1-element int64 device
+    tensor): rows past that count are neither read nor written (their content is undefined)."""
+    return _SwiGLU.apply(gate_up, valid_rows)
 
 
 class _SwiGLUMLP(torch.autograd.Function):

@@ -69,6 +69,30 @@ def grouped_linear(x: torch.Tensor, weight: torch.Tensor, counts: list[int]) -> 
     return _GroupedLinear.apply(x, weight, counts)
 
 
+class _GroupedGateUp(torch.autograd.Function):
+    """Gate and up projections of all local experts as ONE grouped GEMM writing `gate | up` side by side
+    (`w_pair [2E, I, D]`: the gate matrices, then the up matrices; they are adjacent in the flat expert buffer).
+    Backward: one grouped GEMM with the reduction running over both halves gives `dx` (no separate sum),
+    two grouped wgrad GEMMs accumulate into the two halves of the gradient buffer."""
+
+    @staticmethod
+    def forward(ctx, x, w_pair, counts):
+        ctx.counts, ctx.w_pair = counts, w_pair
+        ctx.save_for_backward(x)
+        return native.grouped_gemm_pair_fwd(x, w_pair, counts)
+
+    @staticmethod
+    def backward(ctx, dgu):
+        (x,) = ctx.saved_tensors
+        w, counts = ctx.w_pair, ctx.counts
+        E, I = w.shape[0] // 2, w.shape[1]
+        mg = F_ops._main_grad(w)
+        dgu = dgu.contiguous()
+        native.grouped_gemm_tn_accum(dgu[:, :I], x, mg[:E], counts)
+        native.grouped_gemm_tn_accum(dgu[:, I:], x, mg[E:], counts)
+        return native.grouped_gemm_pair_dgrad(dgu, w, counts), None, None
+
+
 def route(logits: torch.Tensor, k: int):
     """(weights [M,k] fp32, experts [M,k] int64); differentiable w.r.t. logits."""
     vals, experts = torch.topk(logits.float(), k, dim=-1)
@@ -133,7 +157,8 @@ class _CombineDevice(torch.autograd.Function):
         return d_y, dw, None, None, None
 
 
-def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_group, ep_size, aux_coef, layer_key):
+def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_group, ep_size, aux_coef, layer_key,
+                        w_pair=None):
     """bf16 CUDA path without token dropping. Nothing here reads a device value on the host: the expert
     row ranges go to the grouped GEMMs as a device array, and with expert parallelism the rows travel
     through peer memory (`parallel.expert_parallel.peer`)."""
@@ -146,12 +171,15 @@ def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_grou
     else:
         from ..parallel.expert_parallel import peer as ep_peer
         pm = ep_peer.PeerMoE.get(ep_group, num_experts)
-        plan = pm.plan(counts, experts.view(-1)[order.long()].long())
+        plan = pm.plan(counts, experts, order, base)
         per_expert = native.DeviceCounts(plan["row_start"], plan["R"])
         local_x = ep_peer.dispatch_tokens(x, pm, plan, order, pos, k, layer_key)
-    gate = grouped_linear(local_x, w_gate, per_expert)
-    up = grouped_linear(local_x, w_up, per_expert)
-    act = F_ops.swiglu(torch.cat([gate, up], dim=-1))
+    valid = None if ep_size == 1 else plan["n_recv"]        # rows of the expert-side buffers that hold real pairs
+    if w_pair is not None and native.grouped_pair_ok(w_pair.shape[1]):
+        gu = _GroupedGateUp.apply(local_x, w_pair, per_expert)
+    else:
+        gu = torch.cat([grouped_linear(local_x, w_gate, per_expert), grouped_linear(local_x, w_up, per_expert)], dim=-1)
+    act = F_ops.swiglu(gu, valid)
     if ep_size == 1:
         y = grouped_linear(act, w_down, per_expert)
         out = _CombineDevice.apply(y, weights, order, pos, k)
@@ -161,7 +189,7 @@ def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_grou
 
 
 def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_group, ep_size: int,
-                aux_coef: float = 0.0, capacity_factor: float = 0.0, layer_key=None):
+                aux_coef: float = 0.0, capacity_factor: float = 0.0, layer_key=None, w_pair=None):
     """x `[M, D]`, logits `[M, E]` -> (out `[M, D]`, aux loss or None).
 
     On CUDA (bf16) the routing never touches the host: expert row ranges stay in
@@ -172,7 +200,7 @@ def moe_forward(x, logits, w_gate, w_up, w_down, k: int, num_experts: int, ep_gr
     if (x.is_cuda and x.dtype == torch.bfloat16 and capacity_factor <= 0.0 and num_experts <= 256 and k <= 8
             and D % 8 == 0 and (ep_size == 1 or (_peer_enabled() and ep_size <= 8))):
         return _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_group, ep_size, aux_coef,
-                                   layer_key)
+                                   layer_key, w_pair)
     weights, experts = route(logits, k)                                    # [M,k]
     aux = aux_loss(logits, experts, num_experts) * aux_coef if aux_coef > 0.0 else None
 

@@ -59,8 +59,9 @@ _SIGS = {
     "tlm_add_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "tlm_add_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "tlm_rope": (_I, [_P, _P, _P, _LL, _I, _I, _I, _I, _I, _P]),
-    "tlm_swiglu_fwd": (_I, [_P, _P, _LL, _I, _P]),
-    "tlm_swiglu_bwd": (_I, [_P, _P, _P, _LL, _I, _P]),
+    "tlm_swiglu_fwd": (_I, [_P, _P, _LL, _I, _P, _P]),
+    "tlm_swiglu_bwd": (_I, [_P, _P, _P, _LL, _I, _P, _P]),
+    "tlm_gemm_grouped_pair": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _I, _I, _P]),
     "tlm_ce_inplace": (_I, [_P, _P, _P, _P, _I, _I, _LL, _LL, _I, _P]),
     "tlm_sumsq_scratch_floats": (_I, []),
     "tlm_sumsq": (_I, [_P, _LL, _P, _P, _P]),
@@ -78,6 +79,7 @@ _SIGS = {
     "tlm_peer_scatter_rows": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _P, _LL, _LL, _P]),
     "tlm_moe_route_blocks": (_I, [_I]),
     "tlm_moe_route": (_I, [_P, _LL, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "tlm_moe_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _I, _LL, _P, _P, _P, _P, _P, _P, _P]),
     "tlm_moe_route_bwd": (_I, [_P, _P, _P, _P, _LL, _I, _I, _P]),
     "tlm_moe_gather": (_I, [_P, _P, _I, _P, _P, _LL, _I, _P]),
     "tlm_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
@@ -318,18 +320,20 @@ def rope_qk(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_rot: int,
     return qkv
 
 
-def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+def swiglu_fwd(gu: torch.Tensor, valid_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """`valid_rows` (optional 1-element int64 device tensor): only that many leading rows are computed."""
     gu = gu.contiguous()
     rows, two_i = gu.shape
     act = torch.empty(rows, two_i // 2, dtype=torch.bfloat16, device=gu.device)
-    _check(lib().tlm_swiglu_fwd(gu.data_ptr(), act.data_ptr(), rows, two_i // 2, _stream()), "swiglu_fwd")
+    _check(lib().tlm_swiglu_fwd(gu.data_ptr(), act.data_ptr(), rows, two_i // 2, _ptr(valid_rows), _stream()), "swiglu_fwd")
     return act
 
 
-def swiglu_bwd(dact: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+def swiglu_bwd(dact: torch.Tensor, gu: torch.Tensor, valid_rows: torch.Tensor | None = None) -> torch.Tensor:
     rows, two_i = gu.shape
     dgu = torch.empty_like(gu)
-    _check(lib().tlm_swiglu_bwd(dact.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, two_i // 2, _stream()), "swiglu_bwd")
+    _check(lib().tlm_swiglu_bwd(dact.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, two_i // 2, _ptr(valid_rows),
+                                _stream()), "swiglu_bwd")
     return dgu
 
 
@@ -476,6 +480,27 @@ def moe_route(logits: torch.Tensor, k: int):
     return weights, experts, counts, base, pos, order
 
 
+def moe_plan(table: torch.Tensor, ep: int, me: int, experts: torch.Tensor, order: torch.Tensor, my_start: torch.Tensor):
+    """Expert-parallel routing plan from the all-ranks count table `[ep, E]` int32 (`csrc/moe.cu`,
+    `moe_plan_kernel`). Returns a dict: `send_rank [P]` int32, `send_row [P]` int64 (where each of this rank's
+    sorted pairs lands), `row_start [E/ep + 1]` int32 and `n_recv [1]` int64 (row ranges of this rank's experts in
+    its receive buffer), `back_rank [R]` int32 / `back_row [R]` int64 (the way back of every received row,
+    `R = ep * P`, rank -1 past `n_recv`)."""
+    E = table.numel() // ep
+    P = order.numel()
+    R = ep * P
+    dev = table.device
+    out = {"send_rank": torch.empty(P, dtype=torch.int32, device=dev), "send_row": torch.empty(P, dtype=torch.int64, device=dev),
+           "row_start": torch.empty(E // ep + 1, dtype=torch.int32, device=dev), "n_recv": torch.empty(1, dtype=torch.int64, device=dev),
+           "back_rank": torch.empty(R, dtype=torch.int32, device=dev), "back_row": torch.empty(R, dtype=torch.int64, device=dev),
+           "P": P, "R": R}
+    _check(lib().tlm_moe_plan(table.data_ptr(), ep, E, me, experts.data_ptr(), order.data_ptr(), my_start.data_ptr(), P, R,
+                              out["send_rank"].data_ptr(), out["send_row"].data_ptr(), out["row_start"].data_ptr(),
+                              out["n_recv"].data_ptr(), out["back_rank"].data_ptr(), out["back_row"].data_ptr(), _stream()),
+           "moe_plan")
+    return out
+
+
 def moe_route_bwd(dw: torch.Tensor, w: torch.Tensor, experts: torch.Tensor, M: int, E: int) -> torch.Tensor:
     d_logits = torch.zeros(M, E, dtype=torch.bfloat16, device=w.device)
     _check(lib().tlm_moe_route_bwd(dw.contiguous().data_ptr(), w.data_ptr(), experts.data_ptr(), d_logits.data_ptr(), E, M,
@@ -506,3 +531,36 @@ def moe_pair_dot(d_out: torch.Tensor, y: torch.Tensor, pos: torch.Tensor, k: int
     _check(lib().tlm_moe_pair_dot(d_out.data_ptr(), y.data_ptr(), pos.data_ptr(), dw.data_ptr(), P, D, k, _stream()),
            "moe_pair_dot")
     return dw
+
+
+def grouped_pair_ok(I: int) -> bool:
+    return I % 256 == 0
+
+
+def grouped_gemm_pair_fwd(x: torch.Tensor, w_pair: torch.Tensor, counts) -> torch.Tensor:
+    """MoE gate | up in one grouped GEMM: `w_pair [2E, I, D]` (gate matrices, then up matrices);
+    rows of group e -> `[x @ w_pair[e]^T | x @ w_pair[E + e]^T]`, result `[R, 2 I]`."""
+    R, D, lda = _rows(x)
+    E2, I, D2 = w_pair.shape
+    assert D == D2 and E2 % 2 == 0 and w_pair.is_contiguous() and grouped_pair_ok(I)
+    out = torch.empty(R, 2 * I, dtype=torch.bfloat16, device=x.device)
+    if R == 0:
+        return out
+    rs, bound = _grouping(counts, x.device)
+    _check(lib().tlm_gemm_grouped_pair(x.data_ptr(), w_pair.data_ptr(), out.data_ptr(), rs.data_ptr(), E2 // 2, R, I, D, lda,
+                                       I * D, 2 * I, 0, bound, _stream()), "grouped_gemm_pair_fwd")
+    return out
+
+
+def grouped_gemm_pair_dgrad(dgu: torch.Tensor, w_pair: torch.Tensor, counts) -> torch.Tensor:
+    """`dx [R, D] = dgu[:, :I] @ w_pair[e] + dgu[:, I:] @ w_pair[E + e]` for the rows of each group e."""
+    R, I2, lda = _rows(dgu)
+    E2, I, D = w_pair.shape
+    assert I2 == 2 * I and w_pair.is_contiguous()
+    out = torch.empty(R, D, dtype=torch.bfloat16, device=dgu.device)
+    if R == 0:
+        return out
+    rs, bound = _grouping(counts, dgu.device)
+    _check(lib().tlm_gemm_grouped_pair(dgu.data_ptr(), w_pair.data_ptr(), out.data_ptr(), rs.data_ptr(), E2 // 2, R, I, D, lda,
+                                       I * D, D, 1, bound, _stream()), "grouped_gemm_pair_dgrad")
+    return out

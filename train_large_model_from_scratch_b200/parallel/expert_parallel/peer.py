@@ -68,45 +68,18 @@ class PeerMoE:
         return b
 
     # ------------------------------------------------------------------ routing
-    def plan(self, my_counts: torch.Tensor, sorted_e: torch.Tensor):
-        """my_counts `[E]` (pairs per expert on this rank), sorted_e `[P]` (expert of each sorted pair).
-        Returns a dict of device tensors describing both routes."""
+    def plan(self, my_counts: torch.Tensor, experts: torch.Tensor, order: torch.Tensor, my_start: torch.Tensor):
+        """`my_counts [E]` int32 (pairs per expert on this rank), `experts [M*k]` / `order [P]` / `my_start [E+1]`
+        int32 from `native.moe_route`. Publishes the counts to every peer, then one kernel derives both routes.
+        Returns a dict of device tensors. No barrier is needed after the table has been read: the next write into
+        it (the next layer's counts) can only happen after the dispatch exchange, which this rank completes after
+        its plan kernel."""
         ep, E, E_l, me = self.ep, self.E, self.E_l, self.me
         c32 = my_counts.to(torch.int32).contiguous()
         native._check(native.lib().tlm_peer_put_i32(c32.data_ptr(), E, self.counts.ptr_array, ep, me * E,
                                                     native._stream()), "peer_put_i32")
         self.barrier()
-        C = self.counts_t.view(ep, E).to(torch.int64).clone()              # [src, expert]; clone: the table is reused
-        self.barrier()                                                      # nobody overwrites the table before all have read it
-        tot = C.sum(0)                                                      # [E]
-        base = (torch.cumsum(tot.view(ep, E_l), 1) - tot.view(ep, E_l)).view(E)     # expert's first row on its owner
-        src_prefix = torch.cumsum(C, 0) - C                                 # [src, E] rows of earlier sources
-        my_start = torch.cumsum(C[me], 0) - C[me]                           # first sorted-pair index of each expert here
-        P = sorted_e.numel()
-        pos = torch.arange(P, device=self.dev)
-        send_rank = torch.div(sorted_e, E_l, rounding_mode="floor").to(torch.int32)
-        send_row = base[sorted_e] + src_prefix[me][sorted_e] + (pos - my_start[sorted_e])
-        # my experts
-        mine = slice(me * E_l, (me + 1) * E_l)
-        row_start = torch.cat([base[mine], (base[mine][-1:] + tot[mine][-1:])]).to(torch.int32)
-        n_recv = tot[mine].sum().reshape(1)                                 # rows really received (device scalar)
-        # received row -> (source rank, slot in the source's sorted order)
-        R = ep * P
-        blk_start = (base[mine].view(E_l, 1) + src_prefix[:, mine].t()).reshape(-1)            # (e_l, s) blocks, ascending
-        blk_cnt = C[:, mine].t().reshape(-1)
-        r = torch.arange(R, device=self.dev)
-        # last block whose start <= r among NON-EMPTY blocks: search over block ends instead
-        blk_end = blk_start + blk_cnt
-        blk = torch.searchsorted(blk_end, r, right=True).clamp(max=ep * E_l - 1)
-        src = (blk % ep)
-        e_glob = me * E_l + torch.div(blk, ep, rounding_mode="floor")
-        start_on_src = (torch.cumsum(C, 1) - C)                             # [src, E]
-        back_row = start_on_src[src, e_glob] + (r - blk_start[blk])
-        valid = r < n_recv
-        back_rank = torch.where(valid, src, torch.full_like(src, -1)).to(torch.int32)
-        return {"send_rank": send_rank, "send_row": send_row.contiguous(), "row_start": row_start,
-                "n_recv": n_recv.contiguous(), "back_rank": back_rank, "back_row": back_row.contiguous(),
-                "P": P, "R": R}
+        return native.moe_plan(self.counts_t, ep, me, experts, order, my_start)
 
     def scatter(self, src: torch.Tensor, dest_rank, dest_row, dst, n_ptr, n_max: int, src_idx=None, src_div: int = 1,
                 row_scale=None) -> None:
