@@ -303,19 +303,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         tmem_ld32(t_lane + C::S_COL + half * 64 + c, s);
         tmem_ld32(t_lane + C::DP_COL + half * 64 + c, dp);
         tmem_ld_wait();
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
-          float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2));
+          const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
+          float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (diag) {
             const int col = half * 64 + c + i;
-            if (col > row) p0 = 0.f;
-            if (col + 1 > row) p1 = 0.f;
+            if (col > row) pr.x = 0.f;
+            if (col + 1 > row) pr.y = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(dp[i]) - dlt);        // the softmax scale is applied once, when
-          const float d1 = p1 * (__uint_as_float(dp[i + 1]) - dlt);    // dQ and dK leave their accumulators
-          pp[(c + i) >> 1] = pack_bf16(p0, p1);
-          dd[(c + i) >> 1] = pack_bf16(d0, d1);
+          // dS = P (dP - delta); the softmax scale is applied once, when dQ and dK leave their accumulators
+          const float2 ds = fmul2(pr, fadd2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), nd2));
+          pp[(c + i) >> 1] = pack_bf16(pr.x, pr.y);
+          dd[(c + i) >> 1] = pack_bf16(ds.x, ds.y);
         }
       }
       tc_fence_before();

@@ -12,12 +12,12 @@
 //              softmax warps have published P:  O_j = P V  (M128 N=hd; V is
 //              consumed as an MN-major operand straight from its row-major tile)
 //   warps 2-5  one thread per query row: tcgen05.ld S, running max / sum with
-//              exp2, P (bf16) written to shared memory in the swizzled K-major
-//              operand layout. O accumulates in TMEM across KV tiles; it is only
+//              exp2, P written back to tensor memory as packed bf16 pairs (the A
+//              operand of the P V MMA). O accumulates in TMEM across KV tiles; it is only
 //              rescaled (ld / multiply / st) when the row maximum grew by more
 //              than 2^8, and S of tile j+1 is issued while tile j's softmax runs
-// Shared memory is 112 KB (hd 64) so two CTAs share an SM and one CTA's
-// softmax overlaps the other's MMAs. All waits are bounded.
+// Shared memory is 80 KB and tensor memory 256 columns (hd 64), so two CTAs share an
+// SM and one CTA's softmax overlaps the other's MMAs. All waits are bounded.
 #include "common.cuh"
 
 namespace tlm {
@@ -50,12 +50,10 @@ struct AttnFwdSmem {
   static constexpr int KB = HD / 64;                   // 64-wide blocks along hd
   static constexpr int Q_BYTES = AT_BQ * HD * 2;
   static constexpr int KV_BYTES = AT_BKV * HD * 2;
-  static constexpr int P_BYTES = AT_BQ * AT_BKV * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + AT_KV_STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + AT_KV_STAGES * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + AT_KV_STAGES * KV_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256;          // + barriers; 2 CTAs (hd 64) must fit in 228 KB
 };
 
@@ -71,7 +69,10 @@ __global__ void __launch_bounds__(AT_THREADS)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams p) {
   using L = AttnFwdSmem<HD>;
   constexpr int KB = L::KB;
-  constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;
+  // tensor-memory columns: S (128 fp32), O (HD fp32) and the probabilities as packed bf16 pairs (64 columns),
+  // which the P V MMA reads as its A operand straight from tensor memory (P never touches shared memory)
+  constexpr uint32_t S_COL = 0, O_COL = 128, P_COL = 128 + HD;
+  constexpr uint32_t TMEM_COLS = HD == 128 ? 512 : 256;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t sbase = smem_u32(smem_raw);
   uint8_t* sal = smem_raw;
@@ -138,7 +139,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
       constexpr uint32_t idesc_o = umma_idesc_bf16(AT_BQ, HD, 0, 1);
       // descriptors are built once per tile and advanced with one add per MMA: this thread's instruction
       // stream is what feeds the tensor pipe
-      const uint64_t dq = umma_smem_desc(sbase + L::OFF_Q, 16, 1024), dp = umma_smem_desc(sbase + L::OFF_P, 16, 1024);
+      const uint64_t dq = umma_smem_desc(sbase + L::OFF_Q, 16, 1024);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(bar(1 + st), (uint32_t)(j >> 1) & 1u, 13, abort_flag, p.status)) return false;
@@ -167,10 +168,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         if (!mbar_wait(bar(3 + st), (uint32_t)(j >> 1) & 1u, 15, abort_flag, p.status)) break;   // V landed
         tc_fence_after();
         const uint64_t dv = umma_smem_desc(sbase + L::OFF_V + st * L::KV_BYTES, 16384, 1024);   // MN-major: 16 kv rows per step
-        umma_bf16(tmem + O_COL, dp, dv, idesc_o, j > 0);
 #pragma unroll
-        for (int t = 1; t < AT_BKV / 16; ++t)
-          umma_bf16_acc(tmem + O_COL, umma_desc_advance(dp, (t >> 2) * 16384 + (t & 3) * 32), umma_desc_advance(dv, t * 2048), idesc_o);
+        for (int t = 0; t < AT_BKV / 16; ++t)                   // 16 kv = 8 columns of packed pairs per step
+          umma_bf16_ts(tmem + O_COL, tmem + P_COL + t * 8, umma_desc_advance(dv, t * 2048), idesc_o, (j > 0) | (t > 0));
         umma_commit(bar(9));                                    // O updated, P free
         umma_commit(bar(5 + st));                               // V stage free
       }
@@ -242,24 +242,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         }
       }
       const float neg_m = -m_ref * p.scale_log2;
-      // ---- pass 2: probabilities -> shared memory (swizzled K-major operand layout)
-      float l_a = 0.f, l_b = 0.f;
+      // ---- pass 2: probabilities -> tensor memory (packed bf16 pairs, the A operand of the P V MMA)
+      float2 l2 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
       auto emit = [&](const uint32_t* r, int c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
-          if (diag) { if ((c + i) > row) p0 = 0.f; if ((c + i + 1) > row) p1 = 0.f; }
-          l_a += p0; l_b += p1;
-          pk[i >> 1] = pack_bf16(p0, p1);
+          const float2 x = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+          float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          if (diag) { if ((c + i) > row) pp.x = 0.f; if ((c + i + 1) > row) pp.y = 0.f; }
+          l2 = fadd2(l2, pp);
+          pk[i >> 1] = pack_bf16(pp.x, pp.y);
         }
-        uint8_t* prow = sal + L::OFF_P + (c >> 6) * 16384 + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int chunk = ((c & 63) >> 3) + ch;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-        }
+        tmem_st16(t_lane + P_COL + (c >> 1), pk);               // word i of the row = probabilities 2i, 2i+1
       };
       {
         uint32_t ra[32], rb[32];
@@ -279,9 +275,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         if (lane == 0) mbar_arrive(bar(10));                    // S columns may be overwritten by the next tile
         emit(rb, 96);
       }
-      l_run += l_a + l_b;
+      l_run += l2.x + l2.y;
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(8));
     }

@@ -16,6 +16,7 @@ namespace tlm {
 // Every launcher bumps this counter once per kernel launch; Python reads it to
 // report how many kernels of this library ran inside a timed region.
 extern unsigned long long g_launches;
+extern int g_deterministic;        // nonzero: no order-dependent floating-point atomics (see tlm_set_deterministic)
 inline void count_launch(int n = 1) { g_launches += (unsigned long long)n; }
 
 // Status word in mapped pinned host memory. Kernels that give up on a wait
@@ -227,6 +228,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 // ---- UMMA descriptors --------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
 //   K-major  : rows of 64 bf16 (128 B); 8-row groups 1024 B apart  -> SBO = 1024, LBO unused (1)
@@ -284,6 +294,31 @@ int num_sms();
 
 // 4-D bf16 map over a packed [B, T, heads, hd] tensor: dims (hd, heads, T, B), box (64, 1, box_rows, 1).
 int make_qkv_map(CUtensorMap* map, const void* base, int B, int T, int heads, int hd, int box_rows);
+
+// Packed fp32 pairs (sm_100: one issue slot for two lanes of fma / add / mul). The softmax warps of the attention
+// kernels are bound by instruction issue, so their scale-and-shift, row-sum and dS arithmetic runs on pairs.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<const unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+  return d;
+}
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

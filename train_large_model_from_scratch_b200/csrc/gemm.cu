@@ -848,7 +848,7 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   p.split_k = 1; p.k_chunk = K;
-  if (epi == EPI_F32_ACC) {
+  if (epi == EPI_F32_ACC && !g_deterministic) {
     // Weight gradients: few output tiles, long reduction. The persistent grid runs work items (tile x k-split)
     // of equal size in waves of one item per SM, so time ~ waves * (k-blocks per item + E), E = cost of one
     // epilogue pass (fp32 read-modify-write or red.global of a 128 KB tile) in k-block units (measured ~8).

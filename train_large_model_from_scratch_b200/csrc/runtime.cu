@@ -11,6 +11,7 @@
 namespace tlm {
 
 unsigned long long g_launches = 0;
+int g_deterministic = 0;
 
 static unsigned int* g_status_host = nullptr;
 static unsigned int* g_status_dev = nullptr;
@@ -136,3 +137,8 @@ TLM_API void tlm_reset_launch_count() { tlm::g_launches = 0; }
 TLM_API unsigned int tlm_take_device_status() { return tlm::read_status(true); }
 
 TLM_API int tlm_num_sms() { return tlm::num_sms(); }
+
+// Deterministic mode: kernels avoid floating-point atomics whose order depends on scheduling (the split-K
+// weight-gradient epilogue). Slower on small outputs; bit-reproducible runs on the same hardware.
+TLM_API void tlm_set_deterministic(int on) { tlm::g_deterministic = on; }
+TLM_API int tlm_get_deterministic() { return tlm::g_deterministic; }

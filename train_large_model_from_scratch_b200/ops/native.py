@@ -48,6 +48,8 @@ _SIGS = {
     "tlm_reset_launch_count": (None, []),
     "tlm_take_device_status": (_c.c_uint, []),
     "tlm_num_sms": (_I, []),
+    "tlm_set_deterministic": (None, [_I]),
+    "tlm_get_deterministic": (_I, []),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "tlm_gemm_swiglu": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
@@ -117,6 +119,13 @@ def launch_count() -> int:
 
 def reset_launch_count() -> None:
     lib().tlm_reset_launch_count()
+
+
+def set_deterministic(on: bool) -> None:
+    """Deterministic kernels: the split-K weight-gradient GEMM (fp32 `red.global`, order-dependent rounding) is
+    replaced by the single-pass accumulate. The attention backward's dQ reduction and the MoE / embedding
+    scatter-adds still sum in hardware order."""
+    lib().tlm_set_deterministic(int(bool(on)))
 
 
 def take_device_status() -> int:

@@ -63,6 +63,9 @@ def set_seed(seed: int, deterministic: bool = False) -> None:
         torch.cuda.manual_seed_all(seed)
     if deterministic:
         torch.use_deterministic_algorithms(True, warn_only=True)
+        from ..ops import native
+        if native.available():
+            native.set_deterministic(True)            # no split-K atomics in the weight-gradient GEMMs
 
 
 def torch_version_ge(torch_version: str = "2.10") -> bool:
