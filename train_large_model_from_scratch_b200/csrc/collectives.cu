@@ -63,8 +63,44 @@ __device__ __forceinline__ bool flag_exchange(const PeerPtrs& flags, int rank, i
   return s_ok != 0;
 }
 
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int n, int epoch, unsigned int* status) {
+// Epochs. Every exchange on a flag array uses the next integer. A caller may pass it (epoch > 0) or let the
+// kernels count themselves (epoch == 0): word EPOCH_SLOT of the rank's OWN flag array holds the last epoch used,
+// read at kernel start and advanced by the kernel (or its single-block follow-up) at the end. All ranks run the
+// same sequence of exchanges, so their counters agree, and since no launch argument changes from step to step
+// the launches can be recorded in a CUDA graph and replayed.
+constexpr int EPOCH_SLOT = 32;
+__device__ __forceinline__ int resolve_epoch(const PeerPtrs& flags, int rank, int epoch) {
+  return epoch > 0 ? epoch : reinterpret_cast<volatile int*>(flags.p[rank])[EPOCH_SLOT] + 1;
+}
+__device__ __forceinline__ void commit_epoch(const PeerPtrs& flags, int rank, int epoch_arg, int epoch_used) {
+  if (epoch_arg <= 0) reinterpret_cast<volatile int*>(flags.p[rank])[EPOCH_SLOT] = epoch_used;
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int n, int epoch_arg, unsigned int* status) {
+  const int epoch = resolve_epoch(flags, rank, epoch_arg);
   flag_exchange(flags, rank, n, epoch, true, status, 40);
+  if (threadIdx.x == 0) commit_epoch(flags, rank, epoch_arg, epoch);
+}
+
+// Sum of one fp32 value over the ranks: each rank stores its value into slot `rank` of every peer's `slots`
+// array (symmetric memory, n floats), a flag exchange follows, then every rank adds the n slots in rank order
+// (so all ranks get the same bits). One block of >= n threads. Slots are double-buffered by epoch parity: a
+// fast rank's next store cannot overwrite a value a slow rank has not summed yet.
+__global__ void peer_allreduce_scalar_kernel(PeerPtrs slots, PeerPtrs flags, const float* __restrict__ in, float* __restrict__ out,
+                                             float scale, int rank, int n, int epoch_arg, unsigned int* status) {
+  const int epoch = resolve_epoch(flags, rank, epoch_arg);
+  const int par = (epoch & 1) * MAX_PEERS;
+  if ((int)threadIdx.x < n) reinterpret_cast<volatile float*>(slots.p[threadIdx.x])[par + rank] = *in;
+  const bool ok = flag_exchange(flags, rank, n, epoch, true, status, 44);
+  if (threadIdx.x == 0) {
+    float acc = 0.f;
+    if (ok) {
+      const volatile float* mine = reinterpret_cast<const volatile float*>(slots.p[rank]) + par;
+      for (int r = 0; r < n; ++r) acc += mine[r];
+    }
+    *out = acc * scale;
+    commit_epoch(flags, rank, epoch_arg, epoch);
+  }
 }
 
 // Waits until *flag >= expect or `limit_ns` elapse; a timeout is reported through the status word
@@ -99,9 +135,9 @@ __device__ __forceinline__ void multimem_st_b32x4(void* mc_addr, uint4 v) {
 // backward pass, which precedes this kernel in stream order, is complete).
 __global__ void reduce_scatter_kernel(PeerPtrs grads, const float* mc_grads, PeerPtrs flags, float* __restrict__ out,
                                       float* __restrict__ partials, long long lo, long long len, int rank, int n,
-                                      int epoch, unsigned int* status) {
+                                      int epoch_arg, unsigned int* status) {
   __shared__ float red[32];
-  const bool ok = flag_exchange(flags, rank, n, epoch, blockIdx.x == 0, status, 41);
+  const bool ok = flag_exchange(flags, rank, n, resolve_epoch(flags, rank, epoch_arg), blockIdx.x == 0, status, 41);
   float acc = 0.f;
   if (ok) {
     const long long nvec = len / 4;
@@ -154,9 +190,9 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* 
 
 __global__ void reduce_scatter_bf16_kernel(PeerPtrs wire, const __nv_bfloat16* mc_wire, PeerPtrs flags, float* __restrict__ out,
                                            float* __restrict__ partials, long long lo, long long len, int rank, int n,
-                                           int epoch, unsigned int* status) {
+                                           int epoch_arg, unsigned int* status) {
   __shared__ float red[32];
-  const bool ok = flag_exchange(flags, rank, n, epoch, blockIdx.x == 0, status, 43);
+  const bool ok = flag_exchange(flags, rank, n, resolve_epoch(flags, rank, epoch_arg), blockIdx.x == 0, status, 43);
   float acc = 0.f;
   if (ok) {
     const long long nvec = len / 8;
@@ -190,7 +226,9 @@ __global__ void reduce_scatter_bf16_kernel(PeerPtrs wire, const __nv_bfloat16* m
   }
 }
 
-__global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out) {
+// Also advances the self-counted epoch of the reduce-scatter that ran before it (all of whose blocks read it).
+__global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out, PeerPtrs flags,
+                                    int rank, int epoch_arg) {
   __shared__ double red[32];
   double acc = 0.0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) acc += (double)partials[i];
@@ -202,6 +240,7 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
     double t = 0.0;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
     out[0] = (float)t;
+    if (epoch_arg <= 0) commit_epoch(flags, rank, epoch_arg, resolve_epoch(flags, rank, epoch_arg));
   }
 }
 
@@ -210,7 +249,8 @@ __global__ void adamw_gather_kernel(float* __restrict__ p, float* __restrict__ m
                                     const float* __restrict__ g, PeerPtrs params, __nv_bfloat16* mc_params,
                                     const float* __restrict__ scale_ptr, long long lo, long long len, int rank, int n,
                                     float lr, float beta1, float beta2, float eps, float wd, float inv_bc1,
-                                    float inv_sqrt_bc2) {
+                                    float inv_sqrt_bc2, const float* __restrict__ hyper) {
+  if (hyper != nullptr) { lr = hyper[0]; inv_bc1 = hyper[1]; inv_sqrt_bc2 = hyper[2]; }   // per-step values from device memory
   const float scale = *scale_ptr;
   const long long nvec = len / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
@@ -287,7 +327,7 @@ TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, vo
   const int blocks = tlm_reduce_scatter_blocks();
   reduce_scatter_kernel<<<blocks, 512, 0, st>>>(to_ptrs(grad_ptrs, n), mc_grads, to_ptrs(flag_ptrs, n), out, partials, lo,
                                                 len, rank, n, epoch, status_word());
-  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out);
+  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
   count_launch(2);
   return launch_status();
 }
@@ -305,20 +345,33 @@ TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long l
   const int blocks = tlm_reduce_scatter_blocks();
   reduce_scatter_bf16_kernel<<<blocks, 512, 0, st>>>(to_ptrs(wire_ptrs, n), (const __nv_bfloat16*)mc_wire, to_ptrs(flag_ptrs, n),
                                                      out, partials, lo, len, rank, n, epoch, status_word());
-  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out);
+  sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
   count_launch(3);
   return launch_status();
 }
 
+// `hyper` (optional, device, 3 floats: lr, 1/(1-beta1^t), 1/sqrt(1-beta2^t)) overrides the by-value arguments, so
+// that the launch is identical from step to step.
 TLM_API int tlm_adamw_gather(float* p, float* m, float* v, const float* g, void* const* param_ptrs, void* mc_params,
                              const float* scale, long long lo, long long len, int rank, int n, float lr, float beta1,
-                             float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2, cudaStream_t st) {
+                             float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2, const float* hyper,
+                             cudaStream_t st) {
   if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0) return -6;
   long long blocks = (len / 8 + 255) / 256;
   if (blocks > 8LL * num_sms()) blocks = 8LL * num_sms();
   if (blocks < 1) blocks = 1;
   adamw_gather_kernel<<<(int)blocks, 256, 0, st>>>(p, m, v, g, to_ptrs(param_ptrs, n), (__nv_bfloat16*)mc_params, scale, lo,
-                                                   len, rank, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2);
+                                                   len, rank, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, hyper);
+  count_launch();
+  return launch_status();
+}
+
+// out = scale * sum over ranks of *in (fp32). slots: symmetric array of 2 * 16 floats, flags: symmetric flag array.
+TLM_API int tlm_peer_allreduce_scalar(void* const* slot_ptrs, void* const* flag_ptrs, const float* in, float* out, float scale,
+                                      int rank, int n, int epoch, cudaStream_t st) {
+  if (n > MAX_PEERS) return -6;
+  peer_allreduce_scalar_kernel<<<1, 32, 0, st>>>(to_ptrs(slot_ptrs, n), to_ptrs(flag_ptrs, n), in, out, scale, rank, n, epoch,
+                                                 status_word());
   count_launch();
   return launch_status();
 }

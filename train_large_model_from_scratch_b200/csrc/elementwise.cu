@@ -432,11 +432,13 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partials, int n, fl
 // ------------------------------------------------------------------ fused AdamW
 // p (fp32 master), m, v updated in place from g * (*scale_ptr); the new value
 // is also written as bf16 to `p_out`. Decoupled weight decay, bias-corrected,
-// same update order as torch.optim.AdamW.
+// same update order as torch.optim.AdamW. `hyper` (optional, device: lr, 1/(1-beta1^t), 1/sqrt(1-beta2^t))
+// overrides the by-value arguments so that the launch does not change from step to step.
 __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
                              const float* __restrict__ g, __nv_bfloat16* __restrict__ p_out,
                              const float* __restrict__ scale_ptr, long long n, float lr, float beta1, float beta2,
-                             float eps, float wd, float inv_bc1, float inv_sqrt_bc2) {
+                             float eps, float wd, float inv_bc1, float inv_sqrt_bc2, const float* __restrict__ hyper) {
+  if (hyper != nullptr) { lr = hyper[0]; inv_bc1 = hyper[1]; inv_sqrt_bc2 = hyper[2]; }   // per-step values from device memory
   const float scale = *scale_ptr;
   const long long nvec = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
@@ -574,10 +576,10 @@ TLM_API int tlm_sumsq(const float* x, long long n, float* scratch, float* out, c
 
 TLM_API int tlm_adamw(float* p, float* m, float* v, const float* g, void* p_out, const float* scale, long long n,
                       float lr, float beta1, float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2,
-                      cudaStream_t st) {
+                      const float* hyper, cudaStream_t st) {
   if (n % 4 != 0) return -3;
   adamw_kernel<<<grid_for(n / 4, 256), 256, 0, st>>>(p, m, v, g, (__nv_bfloat16*)p_out, scale, n, lr, beta1, beta2, eps, wd,
-                                                     inv_bc1, inv_sqrt_bc2);
+                                                     inv_bc1, inv_sqrt_bc2, hyper);
   count_launch();
   return launch_status();
 }

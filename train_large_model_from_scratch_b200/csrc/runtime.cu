@@ -131,6 +131,8 @@ int num_sms() {
 
 TLM_API unsigned long long tlm_launch_count() { return tlm::g_launches; }
 TLM_API void tlm_reset_launch_count() { tlm::g_launches = 0; }
+// Launches that the launchers did not see: a recorded step replayed as a CUDA graph runs the same kernels again.
+TLM_API void tlm_add_launch_count(unsigned long long n) { tlm::g_launches += n; }
 
 // Reads (and clears) the status word; 0 = no kernel gave up on a wait. Does not
 // synchronise: call after the work of interest has completed.

@@ -21,14 +21,15 @@ def sp_valid_count(targets: torch.Tensor, ignore_index: int = -100) -> torch.Ten
     """Number of non-ignored targets over the SP group, clamped to >= 1 (fp32, 0-d)."""
     cnt = (targets != ignore_index).sum().float()
     if parallel_state.get_sp_world_size() > 1:
-        dist.all_reduce(cnt, op=dist.ReduceOp.SUM, group=parallel_state.get_sp_group())
+        from ...parallel.symm import scalar_all_reduce
+        cnt = scalar_all_reduce(cnt, parallel_state.get_sp_group())
     return cnt.clamp(min=1.0)
 
 
 def sp_sum(x: torch.Tensor) -> torch.Tensor:
     if parallel_state.get_sp_world_size() > 1:
-        x = x.clone()
-        dist.all_reduce(x, op=dist.ReduceOp.SUM, group=parallel_state.get_sp_group())
+        from ...parallel.symm import scalar_all_reduce
+        x = scalar_all_reduce(x, parallel_state.get_sp_group())
     return x
 
 

@@ -46,6 +46,7 @@ _P, _I, _LL, _F = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float
 _SIGS = {
     "tlm_launch_count": (_c.c_ulonglong, []),
     "tlm_reset_launch_count": (None, []),
+    "tlm_add_launch_count": (None, [_c.c_ulonglong]),
     "tlm_take_device_status": (_c.c_uint, []),
     "tlm_num_sms": (_I, []),
     "tlm_set_deterministic": (None, [_I]),
@@ -75,7 +76,8 @@ _SIGS = {
     "tlm_reduce_scatter_blocks": (_I, []),
     "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
     "tlm_reduce_scatter_bf16": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
-    "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P]),
+    "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P, _P]),
+    "tlm_peer_allreduce_scalar": (_I, [_P, _P, _P, _P, _F, _I, _I, _I, _P]),
     "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),
     "tlm_peer_scatter_rows": (_I, [_P, _P, _I, _P, _P, _P, _P, _I, _I, _P, _LL, _LL, _P]),
@@ -87,7 +89,7 @@ _SIGS = {
     "tlm_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "tlm_moe_pair_dot": (_I, [_P, _P, _P, _P, _LL, _I, _I, _P]),
     "tlm_gemm_grouped_rows_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _P, _P, _P, _I, _LL, _P]),
-    "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P]),
+    "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P, _P]),
 }
 
 
@@ -119,6 +121,11 @@ def launch_count() -> int:
 
 def reset_launch_count() -> None:
     lib().tlm_reset_launch_count()
+
+
+def add_launch_count(n: int) -> None:
+    """Account for kernels launched by replaying a recorded CUDA graph."""
+    lib().tlm_add_launch_count(int(n))
 
 
 def set_deterministic(on: bool) -> None:
@@ -367,13 +374,19 @@ def sumsq(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, scale, step: int, lr, beta1, beta2, eps, wd) -> None:
+def adam_hyper(step: int, lr: float, beta1: float, beta2: float) -> tuple[float, float, float]:
+    """(lr, 1/(1-beta1^t), 1/sqrt(1-beta2^t)): the per-step scalars of the AdamW kernels."""
     import math
-    inv_bc1 = 1.0 / (1.0 - beta1 ** step)
-    inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - beta2 ** step)
+    return float(lr), 1.0 / (1.0 - beta1 ** step), 1.0 / math.sqrt(1.0 - beta2 ** step)
+
+
+def adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, scale, step: int, lr, beta1, beta2, eps, wd,
+               hyper: torch.Tensor | None = None) -> None:
+    """`hyper` (3 fp32 on the device, see `adam_hyper`) replaces lr and the bias corrections when given."""
+    lr_, inv_bc1, inv_sqrt_bc2 = adam_hyper(max(step, 1), lr, beta1, beta2)
     _check(lib().tlm_adamw(master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(),
-                           param_out.data_ptr(), scale.data_ptr(), master.numel(), lr, beta1, beta2, eps, wd,
-                           inv_bc1, inv_sqrt_bc2, _stream()), "adamw")
+                           param_out.data_ptr(), scale.data_ptr(), master.numel(), lr_, beta1, beta2, eps, wd,
+                           inv_bc1, inv_sqrt_bc2, _ptr(hyper), _stream()), "adamw")
 
 
 # --------------------------------------------------------------------------- attention

@@ -91,7 +91,7 @@ def main():
     def ag(mc):
         native._check(native.lib().tlm_adamw_gather(
             master.data_ptr(), m.data_ptr(), v.data_ptr(), out.data_ptr(), pp.ptr_array, vp(pp.mc_ptr if mc else 0),
-            scale.data_ptr(), lo, shard, rank, world, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1.0, 1.0, st()), "adamw_gather")
+            scale.data_ptr(), lo, shard, rank, world, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1.0, 1.0, None, st()), "adamw_gather")
         epoch[0] += 1
         native._check(native.lib().tlm_peer_barrier(pf.ptr_array, rank, world, epoch[0], st()), "barrier")
 

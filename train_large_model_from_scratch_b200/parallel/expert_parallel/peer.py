@@ -28,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ...ops import native
+from ..sequence_parallel.ulysses_peer import _fresh
 
 
 class PeerMoE:
@@ -43,7 +44,6 @@ class PeerMoE:
         self.flags = _Peer(symm_alloc(64, torch.int32, dev), group)
         self.counts_t = symm_alloc(self.ep * num_experts, torch.int32, dev)
         self.counts = _Peer(self.counts_t, group)
-        self.epoch = 0
         self.buffers: dict = {}
         dist.barrier(group=group)
 
@@ -54,9 +54,8 @@ class PeerMoE:
         return cls._instance
 
     def barrier(self) -> None:
-        self.epoch += 1
         f = self.flags
-        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, self.epoch, native._stream()), "peer_barrier")
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, 0, native._stream()), "peer_barrier")
 
     def buffer(self, key, rows: int, D: int):
         from ..symm import symm_alloc, _Peer
@@ -101,14 +100,14 @@ class _Dispatch(torch.autograd.Function):
         dst = pm.buffer((key, "disp"), plan["R"], x_sorted.shape[1])
         pm.scatter(x_sorted.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"])
         ctx.pm, ctx.plan, ctx.key = pm, plan, key
-        return dst[0]
+        return _fresh(dst[0])
 
     @staticmethod
     def backward(ctx, d_local):
         pm, plan = ctx.pm, ctx.plan
         dst = pm.buffer((ctx.key, "disp_bwd"), plan["P"], d_local.shape[1])
         pm.scatter(d_local.contiguous(), plan["back_rank"], plan["back_row"], dst, plan["n_recv"], plan["R"])
-        return dst[0], None, None, None
+        return _fresh(dst[0]), None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -119,14 +118,14 @@ class _Combine(torch.autograd.Function):
         dst = pm.buffer((key, "comb"), plan["P"], y_local.shape[1])
         pm.scatter(y_local.contiguous(), plan["back_rank"], plan["back_row"], dst, plan["n_recv"], plan["R"])
         ctx.pm, ctx.plan, ctx.key = pm, plan, key
-        return dst[0]
+        return _fresh(dst[0])
 
     @staticmethod
     def backward(ctx, d_comb):
         pm, plan = ctx.pm, ctx.plan
         dst = pm.buffer((ctx.key, "comb_bwd"), plan["R"], d_comb.shape[1])
         pm.scatter(d_comb.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"])
-        return dst[0], None, None, None
+        return _fresh(dst[0]), None, None, None
 
 
 def dispatch(x_sorted, pm, plan, key):
@@ -149,7 +148,7 @@ class _DispatchTokens(torch.autograd.Function):
         pm.scatter(x.contiguous(), plan["send_rank"], plan["send_row"], dst, None, plan["P"], src_idx=order, src_div=k)
         ctx.pm, ctx.plan, ctx.key, ctx.k, ctx.M = pm, plan, key, k, x.shape[0]
         ctx.save_for_backward(pos)
-        return dst[0]
+        return _fresh(dst[0])
 
     @staticmethod
     def backward(ctx, d_local):

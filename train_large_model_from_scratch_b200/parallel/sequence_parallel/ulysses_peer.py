@@ -37,6 +37,13 @@ from ...ops import native
 from . import ulysses
 
 
+def _fresh(t: torch.Tensor) -> torch.Tensor:
+    """A new tensor object over the same storage. The receive buffers live for the whole run; handing the
+    cached object itself to autograd as a Function's output would tie it to one step's graph (history set on
+    it in one step is still there in the next, with that step's stream)."""
+    return t.view(t.shape)
+
+
 class _Exchange:
     """One symmetric receive buffer + its peers' addresses."""
 
@@ -62,7 +69,6 @@ class PeerState:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.flags_t = symm_alloc(64, torch.int32, dev)
         self.flags = _Peer(self.flags_t, group)
-        self.epoch = 0
         self.buffers: dict = {}
         self.tables: dict = {}
         dist.barrier(group=group)
@@ -88,10 +94,8 @@ class PeerState:
         return t
 
     def barrier(self) -> None:
-        self.epoch += 1
         f = self.flags
-        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, self.epoch, native._stream()),
-                      "peer_barrier")
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, 0, native._stream()), "peer_barrier")
 
 
 def supported(n_q: int, n_kv: int, sp: int, hd: int) -> bool:
@@ -126,7 +130,7 @@ class _SeqToHead(torch.autograd.Function):
         _scatter(st, qkv.contiguous(), ex, table, 0, cos_l, sin_l, 0)
         ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
         ctx.save_for_backward(cos_f, sin_f)
-        return ex.tensor
+        return _fresh(ex.tensor)
 
     @staticmethod
     def backward(ctx, d_full):
@@ -136,7 +140,7 @@ class _SeqToHead(torch.autograd.Function):
         table = _dqkv_table(st, n_q, n_kv, q_l, kv_l, d_full.device)
         ex = st.buffer((layer_key, "dqkv"), (B, T_l, n_q + 2 * n_kv, hd), d_full.device)
         _scatter(st, d_full.contiguous(), ex, table, 1, cos_f, sin_f, 0)
-        return ex.tensor, None, None, None, None, None, None, None, None
+        return _fresh(ex.tensor), None, None, None, None, None, None, None, None
 
 
 class _HeadToSeq(torch.autograd.Function):
@@ -152,7 +156,7 @@ class _HeadToSeq(torch.autograd.Function):
         ex = st.buffer((layer_key, "o"), (B, T_full // sp, n_q, hd), o.device)
         _scatter(st, o.contiguous(), ex, table, 1, None, None, 0)
         ctx.meta = (n_q, q_l, layer_key, group, B, T_full, hd)
-        return ex.tensor
+        return _fresh(ex.tensor)
 
     @staticmethod
     def backward(ctx, d_seq):
@@ -166,7 +170,7 @@ class _HeadToSeq(torch.autograd.Function):
         table = st.table(("s2h_do", n_q), rows, d_seq.device)
         ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), d_seq.device)
         _scatter(st, d_seq.contiguous(), ex, table, 0, None, None, 0)
-        return ex.tensor, None, None, None
+        return _fresh(ex.tensor), None, None, None
 
 
 def _dqkv_table(st: PeerState, n_q, n_kv, q_l, kv_l, device) -> torch.Tensor:
@@ -199,7 +203,7 @@ class _QKVProjectScatter(torch.autograd.Function):
         ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
         ctx.weight = weight
         ctx.save_for_backward(h, cos_f, sin_f)
-        return ex.tensor
+        return _fresh(ex.tensor)
 
     @staticmethod
     def backward(ctx, d_full):

@@ -82,7 +82,6 @@ class PeerCollectives:
                 "param": _Peer(s.buf.params, s.group),
                 "flags": _Peer(flags, s.group),
                 "flags_t": flags,
-                "epoch": 0,
                 "partials": torch.zeros(native.lib().tlm_reduce_scatter_blocks(), dtype=torch.float32, device=dev),
                 "sumsq": torch.zeros((), dtype=torch.float32, device=dev),
             }
@@ -98,46 +97,87 @@ class PeerCollectives:
         return id(s) in self.state
 
     def barrier(self, s) -> None:
-        st = self.state[id(s)]
-        st["epoch"] += 1
-        f = st["flags"]
-        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, st["epoch"], native._stream()),
-                      "peer_barrier")
+        f = self.state[id(s)]["flags"]
+        native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, 0, native._stream()), "peer_barrier")
 
     def reduce_grads(self, s) -> torch.Tensor:
         """Sum of every rank's gradient slice -> `s.grad_shard`; also leaves the
-        slice's sum of squares in `self.last_sumsq(s)`."""
+        slice's sum of squares in `self.last_sumsq(s)`. (Epoch argument 0: the kernels count their own
+        flag epochs, so the launch is the same every step.)"""
         st = self.state[id(s)]
-        st["epoch"] += 1
         g, f = st["grad"], st["flags"]
         if "wire" in st:
             w = st["wire"]
             native._check(native.lib().tlm_reduce_scatter_bf16(
                 s.buf.main_grad.data_ptr(), st["wire_t"].data_ptr(), s.buf.padded, w.ptr_array,
                 ctypes.c_void_p(w.mc_ptr) if w.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
-                st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, st["epoch"],
+                st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, 0,
                 native._stream()), "reduce_scatter_bf16")
             return s.grad_shard
         native._check(native.lib().tlm_reduce_scatter(
             g.ptr_array, ctypes.c_void_p(g.mc_ptr) if g.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
-            st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, st["epoch"],
+            st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, 0,
             native._stream()), "reduce_scatter")
         return s.grad_shard
 
     def last_sumsq(self, s) -> torch.Tensor:
         return self.state[id(s)]["sumsq"]
 
-    def update_and_gather(self, s, grad, scale, step: int, g: dict) -> None:
+    def update_and_gather(self, s, grad, scale, step: int, g: dict, hyper=None) -> None:
         st = self.state[id(s)]
         b1, b2 = g["betas"]
         pr = st["param"]
+        lr, inv_bc1, inv_sqrt_bc2 = native.adam_hyper(max(step, 1), g["lr"], b1, b2)
         native._check(native.lib().tlm_adamw_gather(
             s.master.data_ptr(), s.exp_avg.data_ptr(), s.exp_avg_sq.data_ptr(), grad.data_ptr(), pr.ptr_array,
             ctypes.c_void_p(pr.mc_ptr) if pr.mc_ptr else None, scale.data_ptr(), s.lo, s.len, pr.rank, pr.n,
-            g["lr"], b1, b2, g["eps"], g["weight_decay"], 1.0 / (1.0 - b1 ** step),
-            1.0 / math.sqrt(1.0 - b2 ** step), native._stream()), "adamw_gather")
+            lr, b1, b2, g["eps"], g["weight_decay"], inv_bc1, inv_sqrt_bc2, native._ptr(hyper), native._stream()),
+            "adamw_gather")
         self.barrier(s)          # every replica complete before anyone's next forward reads it
 
     def gather_params(self, s) -> None:
         """Parameters were already distributed by `update_and_gather`."""
         return None
+
+
+class PeerScalar:
+    """Sum of one fp32 value over a process group through symmetric memory (one kernel: store to every peer's
+    slot, flag exchange, ordered sum). Replaces NCCL for the two per-step scalars (gradient norm², loss), so a
+    training step contains no library collective at all."""
+
+    def __init__(self, group, device):
+        self.group = group
+        self.slots_t = symm_alloc(32, torch.float32, device)
+        self.flags_t = symm_alloc(64, torch.int32, device)
+        self.slots, self.flags = _Peer(self.slots_t, group), _Peer(self.flags_t, group)
+        dist.barrier(group=group)
+
+    def all_reduce(self, x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """`scale * sum_ranks(x)` for a 0-d fp32 CUDA tensor; returns a new 0-d tensor."""
+        x = x.reshape(()).float().contiguous()
+        out = torch.empty((), dtype=torch.float32, device=x.device)
+        f = self.flags
+        native._check(native.lib().tlm_peer_allreduce_scalar(self.slots.ptr_array, f.ptr_array, x.data_ptr(), out.data_ptr(),
+                                                             float(scale), f.rank, f.n, 0, native._stream()),
+                      "peer_allreduce_scalar")
+        return out
+
+
+_SCALARS: dict = {}
+
+
+def scalar_all_reduce(x: torch.Tensor, group, scale: float = 1.0) -> torch.Tensor:
+    """`scale * sum over group of x` for a 0-d tensor. On CUDA with the peer-memory path enabled this is one kernel
+    of this package (`PeerScalar`); otherwise `dist.all_reduce`. Returns a new tensor; not differentiable."""
+    n = dist.get_world_size(group) if group is not None else 1
+    if n == 1:
+        return x * scale if scale != 1.0 else x
+    if x.is_cuda and use_symm() and n <= 16:
+        key = id(group)
+        ps = _SCALARS.get(key)
+        if ps is None:
+            ps = _SCALARS[key] = PeerScalar(group, x.device)
+        return ps.all_reduce(x.detach(), scale).to(x.dtype)
+    y = x.detach().clone()
+    dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+    return y * scale if scale != 1.0 else y

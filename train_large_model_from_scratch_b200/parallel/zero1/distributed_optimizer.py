@@ -107,18 +107,36 @@ class FusedAdamW:
         self.step_count = 0
         self.grad_norm = None
         self._comm = None              # optional peer-memory collective engine (CUDA)
+        # per-step scalars of the AdamW kernels (lr, bias corrections) in device memory, fed from pinned memory
+        dev = self.buffers[0].params.device if self.buffers else torch.device("cpu")
+        if dev.type == "cuda":
+            self._hyper = torch.zeros(4, dtype=torch.float32, device=dev)
+            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+        else:
+            self._hyper = self._hyper_host = None
 
     # -- the reference-style surface ------------------------------------------------
     def zero_grad(self, set_to_none: bool = True) -> None:
         for b in self.buffers:
             b.zero_grad()
 
+    def prepare_step(self) -> None:
+        """Host part of a step: advance the step counter and publish this step's scalars (learning rate, bias
+        corrections) to the device buffer the kernels read. Kept apart from `step_device` so that the device
+        part is launch-for-launch identical every step (it can be recorded once and replayed)."""
+        g = self.param_groups[0]
+        self.step_count += 1
+        if self._hyper is not None:
+            b1, b2 = g["betas"]
+            vals = native.adam_hyper(self.step_count, g["lr"], b1, b2)
+            self._hyper_host[0], self._hyper_host[1], self._hyper_host[2] = vals
+            self._hyper.copy_(self._hyper_host, non_blocking=True)
+
     @torch.no_grad()
-    def step(self, grad_clip_value: float | None = None):
+    def step_device(self, grad_clip_value: float | None = None):
         """Reduce gradients, clip by global norm, update, re-assemble parameters.
         Returns the global gradient norm (0-d tensor, before clipping)."""
         g = self.param_groups[0]
-        self.step_count += 1
         inv = 1.0 / self.grad_divisor
         norm_sq = None
         for s in self.shards:
@@ -130,7 +148,11 @@ class FusedAdamW:
             norm_sq = part if norm_sq is None else norm_sq + part
         norm_sq = norm_sq * (inv * inv)
         if self.norm_group is not None and dist.get_world_size(self.norm_group) > 1:
-            dist.all_reduce(norm_sq, op=dist.ReduceOp.SUM, group=self.norm_group)
+            if norm_sq.is_cuda:
+                from ..symm import scalar_all_reduce
+                norm_sq = scalar_all_reduce(norm_sq, self.norm_group)
+            else:
+                dist.all_reduce(norm_sq, op=dist.ReduceOp.SUM, group=self.norm_group)
         norm = norm_sq.sqrt()
         if grad_clip_value is not None and grad_clip_value > 0:
             scale = torch.clamp(grad_clip_value / (norm + 1e-6), max=1.0) * inv
@@ -142,6 +164,10 @@ class FusedAdamW:
             self._gather(s)
         self.grad_norm = norm
         return norm
+
+    def step(self, grad_clip_value: float | None = None):
+        self.prepare_step()
+        return self.step_device(grad_clip_value)
 
     # -- stages -----------------------------------------------------------------------
     def _reduce(self, s: _Shard) -> torch.Tensor:
@@ -170,10 +196,10 @@ class FusedAdamW:
         b1, b2 = g["betas"]
         out = s.buf.params[s.lo:s.hi]
         if self._comm is not None and self._comm.handles(s):
-            self._comm.update_and_gather(s, grad, scale, self.step_count, g)
+            self._comm.update_and_gather(s, grad, scale, self.step_count, g, hyper=self._hyper)
         elif grad.is_cuda:
             native.adamw_step(s.master, s.exp_avg, s.exp_avg_sq, grad, out, scale, self.step_count,
-                              g["lr"], b1, b2, g["eps"], g["weight_decay"])
+                              g["lr"], b1, b2, g["eps"], g["weight_decay"], hyper=self._hyper)
         else:
             oracle.adamw_step(s.master, grad, s.exp_avg, s.exp_avg_sq, self.step_count, g["lr"], b1, b2,
                               g["eps"], g["weight_decay"], grad_scale=float(scale))

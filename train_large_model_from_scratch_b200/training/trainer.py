@@ -84,6 +84,13 @@ class Trainer:
         self.profiler = None
         self.profiler_record_fn = self._null_record
         self.step_ms_device = None
+        # CUDA-graph execution of the step (see `_train_step_graphed`)
+        self._graph = None
+        self._graph_in = None
+        self._graph_out = None
+        self._graph_launches = 0
+        self._graph_eager_steps = 0
+        self._graph_disabled = False
 
     # ------------------------------------------------------------------ init hooks
     def _init_distributed(self, config: Config) -> None:
@@ -307,6 +314,96 @@ class Trainer:
         self.one_step_results["loss"] = loss_accum
         self.one_step_results["grad_norm"] = norm
 
+    # ------------------------------------------------------------------ the step as a CUDA graph
+    def _graph_eligible(self) -> bool:
+        """The whole step (zero-grad, every micro-step's forward and backward, reduce-scatter, clipped AdamW,
+        all-gather, loss reduction) is recorded once and replayed when nothing in it needs the host: CUDA, bf16,
+        and either one rank or the peer-memory collectives (library collectives stay un-recorded). The reference's
+        `--use_compile` asks for its tracing compiler (`training/trainer.py:130-131`); here the flag is accepted
+        and this launch-free replay is what speeds the step up, whether or not the flag is given.
+        `TLM_CUDA_GRAPH=0` turns it off."""
+        if self._graph_disabled or not self.use_cuda or os.environ.get("TLM_CUDA_GRAPH", "1") == "0":
+            return False
+        if self._compute_dtype(self.config.train.precision) != torch.bfloat16:
+            return False
+        if self.world_size > 1 and not getattr(self, "_symm", False):
+            return False
+        return not self.config.train.use_profiler
+
+    def _device_step(self):
+        """Everything of one optimizer step that runs on the device, reading the static input buffers."""
+        cfg = self.config
+        ga = self.training_info["grad_accum_steps"]
+        self.model.train()
+        self.optimizer.zero_grad()
+        loss_accum = None
+        for ms in range(ga):
+            b = self._graph_in[ms]
+            _, loss, logging_loss = self.model(b["input_ids"], b["labels"], loss_scale=1.0 / ga)
+            loss.backward()
+            l = logging_loss.detach()
+            loss_accum = l if loss_accum is None else loss_accum + l
+        norm = self.optimizer.step_device(grad_clip_value=cfg.train.grad_clip_value)
+        if self.dp_world_size > 1:
+            from ..parallel.symm import scalar_all_reduce
+            loss_accum = scalar_all_reduce(loss_accum, self.dp_group, 1.0 / self.dp_world_size)
+        return loss_accum, norm
+
+    def _train_step_graphed(self, step: int, batches: list | None) -> bool:
+        """Runs the step from static buffers: eagerly for the first two calls (lazy set-up: symmetric buffers,
+        kernel attributes, tables), then records it and replays the recording. Returns False if this step has to
+        take the ordinary path (shape change, recording failed)."""
+        from ..ops import native
+        cfg = self.config
+        ga = self.training_info["grad_accum_steps"]
+        host = batches if batches is not None else [self._next_batch() for _ in range(ga)]
+        xs = [(self._sp_slice(b["input_ids"]), self._sp_slice(b["labels"])) for b in host]
+        if self._graph_in is None:
+            self._graph_in = [{"input_ids": torch.empty(x.shape, dtype=torch.int64, device=self.device),
+                               "labels": torch.empty(y.shape, dtype=torch.int64, device=self.device)} for x, y in xs]
+        if len(xs) != len(self._graph_in) or any(x.shape != g["input_ids"].shape for (x, _), g in zip(xs, self._graph_in)):
+            self._pending_batches = host
+            return False
+        for (x, y), g in zip(xs, self._graph_in):
+            if cfg.data.pin_memory and not x.is_cuda and not x.is_pinned():
+                x, y = x.contiguous().pin_memory(), y.contiguous().pin_memory()
+            g["input_ids"].copy_(x, non_blocking=True)
+            g["labels"].copy_(y, non_blocking=True)
+        lr = self._lr_scheduler(step, self.training_info["max_steps"], cfg.optim.warmup_steps, cfg.optim.max_lr,
+                                cfg.optim.min_lr)
+        for group in self.optimizer.param_groups:
+            group["lr"] = lr
+        self.optimizer.prepare_step()
+        if self._graph is None and self._graph_eager_steps < 2:
+            self._graph_eager_steps += 1
+            loss, norm = self._device_step()
+        else:
+            if self._graph is None:
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                before = native.launch_count()
+                try:
+                    with torch.cuda.graph(graph, capture_error_mode=os.environ.get("TLM_GRAPH_CAPTURE_MODE", "thread_local")):
+                        self._graph_out = self._device_step()
+                except Exception as e:                                   # keep training on the ordinary path
+                    self._graph_disabled = True
+                    if self.master_process:
+                        import traceback
+                        where = "".join(traceback.format_exc().splitlines(keepends=True)[-14:])
+                        print(f"[warn] recording the step as a CUDA graph failed ({type(e).__name__}: "
+                              f"{str(e).splitlines()[0]}); continuing without it\n{where}")
+                    torch.cuda.synchronize()
+                    loss, norm = self._device_step()
+                    self.one_step_results.update(lr=lr, loss=loss, grad_norm=norm)
+                    return True
+                self._graph_launches = native.launch_count() - before
+                self._graph = graph
+            self._graph.replay()
+            native.add_launch_count(self._graph_launches)
+            loss, norm = self._graph_out
+        self.one_step_results.update(lr=lr, loss=loss, grad_norm=norm)
+        return True
+
     def train_step(self, step: int, batches: list | None = None) -> dict:
         """One optimizer step (all micro-steps). Public entry for callers that
         drive the loop themselves; returns `{lr, loss, grad_norm}` with `loss`
@@ -319,7 +416,11 @@ class Trainer:
             # learn about a dead or stalled peer on the host, before any kernel or collective of this step
             hb.enter_step(step)
         try:
-            self._one_training_step(self.config, step, batches)
+            done = self._graph_eligible() and self._train_step_graphed(step, batches)
+            if not done:
+                pend = getattr(self, "_pending_batches", None)
+                self._pending_batches = None
+                self._one_training_step(self.config, step, batches if pend is None else pend)
         except BaseException as e:
             if hb is not None:
                 hb.announce_failure(f"{type(e).__name__}: {e}")
