@@ -82,7 +82,8 @@ def test_embedding(nat):
     torch.testing.assert_close(g, ref, rtol=1e-5, atol=1e-5)
 
 
-@pytest.mark.parametrize("rows,D,has_delta", [(37, 256, True), (64, 1024, True), (5, 3072, False), (130, 64, True)])
+@pytest.mark.parametrize("rows,D,has_delta", [(37, 256, True), (64, 1024, True), (5, 3072, False), (130, 64, True), (9, 2048, True),
+                                                (7, 1280, True), (11, 1536, False)])
 def test_add_rmsnorm(nat, rows, D, has_delta):
     x = torch.randn(rows, D, device="cuda")
     delta = _rand(rows, D, seed=10) if has_delta else None
@@ -192,7 +193,7 @@ def test_swiglu(nat):
     assert _rel_err(dgu, ref) < 4e-3
 
 
-@pytest.mark.parametrize("V", [50304, 2048])
+@pytest.mark.parametrize("V", [50304, 2048, 131072])      # the last one exceeds the row-resident kernel's shared memory
 def test_ce_inplace(nat, V):
     rows = 33
     logits = _rand(rows, V, scale=2.0, seed=15)

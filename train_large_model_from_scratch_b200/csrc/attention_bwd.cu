@@ -67,24 +67,51 @@ struct AttnBwdCfg {
   static constexpr uint32_t DQ_BUF_COLS = HD == 64 ? 64 : 0;
 };
 
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                  float* __restrict__ delta, int B, int T, int Hq, int hd) {
-  // one warp per (b, t, h) row of hd elements
-  const long long rows = (long long)B * T * Hq;
-  const int lane = threadIdx.x & 31;
-  for (long long r = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; r < rows; r += ((long long)gridDim.x * blockDim.x) >> 5) {
-    float acc = 0.f;
-    for (int c = lane * 2; c < hd; c += 64) {
-      const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(o + r * hd + c));
-      const float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + r * hd + c));
-      acc += a.x * d.x + a.y * d.y;
+// delta[b, h, t] = sum_c o[b, t, h, c] * dout[b, t, h, c]. One block per (b, 32 consecutive t): that slab of o
+// and dout is contiguous, hd / 8 lanes share a row with 16-byte loads (four rows in flight per lane), the row sums
+// are staged in shared memory so that the [B, Hq, T] output is written as whole 128-byte lines.
+constexpr int DELTA_T = 32, DELTA_THREADS = 256;
+
+__global__ void __launch_bounds__(DELTA_THREADS)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                  float* __restrict__ delta, int B, int T, int Hq, int hd) {
+  extern __shared__ float delta_s[];                       // [Hq][DELTA_T + 1]
+  const int tiles_t = (T + DELTA_T - 1) / DELTA_T;
+  const int b = blockIdx.x / tiles_t, t0 = (blockIdx.x % tiles_t) * DELTA_T;
+  const int nt = min(DELTA_T, T - t0);
+  const int lpr = hd >> 3;                                 // lanes per row: 4, 8 or 16
+  const int sub = threadIdx.x % lpr, slot = threadIdx.x / lpr, slots = DELTA_THREADS / lpr;
+  const int rows = nt * Hq;                                // row rr = tl * Hq + h
+  const long long base = ((long long)b * T + t0) * Hq * hd;
+  const uint4* op = reinterpret_cast<const uint4*>(o + base) + sub;
+  const uint4* dp = reinterpret_cast<const uint4*>(dout + base) + sub;
+  for (int rb = 0; rb < rows; rb += 4 * slots) {          // trip count is uniform: the shuffles below need whole warps
+    const int r0 = rb + slot;
+    uint4 a[4], d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int rr = r0 + u * slots;
+      if (rr < rows) { a[u] = op[(long long)rr * lpr]; d[u] = dp[(long long)rr * lpr]; }
+      else { a[u] = make_uint4(0, 0, 0, 0); d[u] = a[u]; }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const long long bt = r / Hq; const int h = (int)(r % Hq);
-      const long long b = bt / T; const int t = (int)(bt % T);
-      delta[(b * Hq + h) * T + t] = acc;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, dw[4] = {d[u].x, d[u].y, d[u].z, d[u].w};
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = unpack_bf16(aw[k]), y = unpack_bf16(dw[k]);
+        acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+      }
+      for (int off = lpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      const int rr = r0 + u * slots;
+      if (sub == 0 && rr < rows) delta_s[(rr % Hq) * (DELTA_T + 1) + rr / Hq] = acc;
     }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < Hq * DELTA_T; i += DELTA_THREADS) {
+    const int h = i / DELTA_T, tl = i % DELTA_T;
+    if (tl < nt) delta[((long long)b * Hq + h) * T + t0 + tl] = delta_s[h * (DELTA_T + 1) + tl];
   }
 }
 
@@ -414,9 +441,9 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   if (hd != 32 && hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
   const long long rows = (long long)B * T * Hq;
-  int blocks = (int)((rows * 32 + 255) / 256);
-  if (blocks > num_sms() * 16) blocks = num_sms() * 16;
-  attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, T, Hq, hd);
+  if ((size_t)Hq * (DELTA_T + 1) * 4 > 48 * 1024) return -6;
+  attn_delta_kernel<<<B * ((T + DELTA_T - 1) / DELTA_T), DELTA_THREADS, (size_t)Hq * (DELTA_T + 1) * 4, st>>>(
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, T, Hq, hd);
   count_launch();
   cudaError_t ce = cudaMemsetAsync(dq_acc, 0, (size_t)rows * hd * 4, st);
   if (ce != cudaSuccess) return (int)ce;

@@ -65,7 +65,7 @@ struct AttnFwdSmem {
 constexpr float RESCALE_LOG2 = 8.0f;
 
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS)
+__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams p) {
   using L = AttnFwdSmem<HD>;
   constexpr int KB = L::KB;
@@ -187,34 +187,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
       if (!mbar_wait(bar(7), par, 16, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (j == qt);
-      // ---- pass 1: row maximum; the next chunk's load is in flight while one is reduced
+      // ---- the whole S row (128 fp32) moves to registers in one go; S may then be overwritten by the next
+      // tile's Q K^T, which therefore overlaps all of this tile's softmax
+      uint32_t sr[AT_BKV];
+#pragma unroll
+      for (int c = 0; c < AT_BKV; c += 32) tmem_ld32(t_lane + S_COL + c, sr + c);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(10));
+      // ---- row maximum
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      auto fold = [&](const uint32_t* r, int c) {
-        if (!diag) {
+      if (!diag) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(r[i]));     mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(r[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (c + i <= row) mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+        for (int i = 0; i < AT_BKV; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));     mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
         }
-      };
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld32(t_lane + S_COL, ra);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 32, rb);
-        fold(ra, 0);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 64, ra);
-        fold(rb, 32);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 96, rb);
-        fold(ra, 64);
-        tmem_ld_wait();
-        fold(rb, 96);
+      } else {
+#pragma unroll
+        for (int i = 0; i < AT_BKV; ++i) if (i <= row) mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // ---- move the reference (and rescale O in TMEM) only when the maximum grew a lot
@@ -228,13 +220,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         if (__any_sync(0xffffffffu, grow)) {
           const float alpha = grow ? ex2_approx((m_ref - mx) * p.scale_log2) : 1.f;
 #pragma unroll
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(t_lane + O_COL + c, r);
+          for (int c = 0; c < HD; c += 8) {                    // rare path; narrow chunks keep the S row in registers
+            uint32_t r[8];
+            tmem_ld8(t_lane + O_COL + c, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(t_lane + O_COL + c, r);
+            for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st8(t_lane + O_COL + c, r);
           }
           tmem_st_wait();
           l_run *= alpha;
@@ -242,38 +234,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         }
       }
       const float neg_m = -m_ref * p.scale_log2;
-      // ---- pass 2: probabilities -> tensor memory (packed bf16 pairs, the A operand of the P V MMA)
+      // ---- probabilities -> tensor memory (packed bf16 pairs, the A operand of the P V MMA)
       float2 l2 = make_float2(0.f, 0.f);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
-      auto emit = [&](const uint32_t* r, int c) {
+#pragma unroll
+      for (int c = 0; c < AT_BKV; c += 32) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float2 x = ffma2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nm2);
+          const float2 x = ffma2(make_float2(__uint_as_float(sr[c + i]), __uint_as_float(sr[c + i + 1])), sc2, nm2);
           float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (diag) { if ((c + i) > row) pp.x = 0.f; if ((c + i + 1) > row) pp.y = 0.f; }
           l2 = fadd2(l2, pp);
           pk[i >> 1] = pack_bf16(pp.x, pp.y);
         }
         tmem_st16(t_lane + P_COL + (c >> 1), pk);               // word i of the row = probabilities 2i, 2i+1
-      };
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld32(t_lane + S_COL, ra);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 32, rb);
-        emit(ra, 0);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 64, ra);
-        emit(rb, 32);
-        tmem_ld_wait();
-        tmem_ld32(t_lane + S_COL + 96, rb);
-        emit(ra, 64);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(10));                    // S columns may be overwritten by the next tile
-        emit(rb, 96);
       }
       l_run += l2.x + l2.y;
       tmem_st_wait();

@@ -87,6 +87,58 @@ __global__ void add_rmsnorm_fwd_kernel(const float* __restrict__ x, const __nv_b
   }
 }
 
+// Register-resident variant for D = NV * 256: each lane owns NV groups of 8 columns and issues all loads of its
+// row before the first use, so one warp keeps NV * 3 sixteen-byte loads in flight; no shared memory.
+template <int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_fwd_reg_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                           const __nv_bfloat16* __restrict__ w, float* __restrict__ x_new,
+                           __nv_bfloat16* __restrict__ h, float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int D = NV * 256;
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * warps + warp; r < rows; r += gridDim.x * warps) {
+    const float* xr = x + (long long)r * D;
+    float4 a[NV], b[NV];
+    uint4 d[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      a[k] = *reinterpret_cast<const float4*>(xr + c);
+      b[k] = *reinterpret_cast<const float4*>(xr + c + 4);
+      if (delta != nullptr) d[k] = *reinterpret_cast<const uint4*>(delta + (long long)r * D + c);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (delta != nullptr) {
+        const int c = (lane + 32 * k) * 8;
+        const float2 d0 = unpack_bf16(d[k].x), d1 = unpack_bf16(d[k].y), d2 = unpack_bf16(d[k].z), d3 = unpack_bf16(d[k].w);
+        a[k].x += d0.x; a[k].y += d0.y; a[k].z += d1.x; a[k].w += d1.y;
+        b[k].x += d2.x; b[k].y += d2.y; b[k].z += d3.x; b[k].w += d3.y;
+        float4* o = reinterpret_cast<float4*>(x_new + (long long)r * D + c);
+        o[0] = a[k]; o[1] = b[k];
+      }
+      ss += a[k].x * a[k].x + a[k].y * a[k].y + a[k].z * a[k].z + a[k].w * a[k].w +
+            b[k].x * b[k].x + b[k].y * b[k].y + b[k].z * b[k].z + b[k].w * b[k].w;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss * (1.f / (float)D) + eps);
+    if (lane == 0) rstd_out[r] = rstd;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + c);            // D * 2 bytes, stays in L1
+      const float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+      uint4 o;
+      o.x = pack_bf16(a[k].x * rstd * w0.x, a[k].y * rstd * w0.y);
+      o.y = pack_bf16(a[k].z * rstd * w1.x, a[k].w * rstd * w1.y);
+      o.z = pack_bf16(b[k].x * rstd * w2.x, b[k].y * rstd * w2.y);
+      o.w = pack_bf16(b[k].z * rstd * w3.x, b[k].w * rstd * w3.y);
+      *reinterpret_cast<uint4*>(h + (long long)r * D + c) = o;
+    }
+  }
+}
+
 // g_x = g_xnew + rstd * (gh*w - xhat * mean(gh*w*xhat)); g_delta = bf16(g_x);
 // dw[c] += sum_rows gh*xhat. Each warp keeps a private dw row in shared memory;
 // the block folds them and issues one atomicAdd per column.
@@ -392,6 +444,98 @@ __global__ void ce_inplace_kernel(__nv_bfloat16* __restrict__ logits, const long
   }
 }
 
+// Row-resident variant: the block keeps its row in shared memory (two blocks per SM for V <= 57 K), so global
+// memory is read once and written once and every element costs one exp: pass 1 stages the row and takes the
+// maximum (packed bf16 max), pass 2 replaces each logit by bf16(exp(logit - max)) and sums it, pass 3 scales.
+// Each thread only ever touches the 16-byte vectors it staged itself.
+constexpr int CE_ROW_THREADS = 512;
+
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+__global__ void __launch_bounds__(CE_ROW_THREADS, 2)
+ce_inplace_row_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                      const float* __restrict__ scale_ptr, float* __restrict__ loss_sum, int V, long long ld,
+                      long long ignore_index, int write_grad) {
+  extern __shared__ uint4 ce_row[];                        // [V / 8]
+  __shared__ float red[CE_ROW_THREADS / 32];
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __nv_bfloat16* row = logits + (long long)r * ld;
+  const long long tgt = targets[r];
+  const int nvec = V / 8;
+  if (tgt == ignore_index || (unsigned long long)tgt >= (unsigned long long)V) {   // never index outside the row
+    if (write_grad) for (int v = tid; v < nvec; v += CE_ROW_THREADS) *reinterpret_cast<uint4*>(row + v * 8) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const float tgt_logit = tid == 0 ? __bfloat162float(row[tgt]) : 0.f;
+  constexpr uint32_t NEG_INF2 = 0xff80ff80u;
+  uint32_t m2 = NEG_INF2;
+  for (int v0 = tid; v0 < nvec; v0 += 4 * CE_ROW_THREADS) {
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * CE_ROW_THREADS;
+      q[u] = v < nvec ? *reinterpret_cast<const uint4*>(row + (long long)v * 8) : make_uint4(NEG_INF2, NEG_INF2, NEG_INF2, NEG_INF2);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * CE_ROW_THREADS;
+      if (v < nvec) ce_row[v] = q[u];
+      m2 = bf16x2_max(m2, bf16x2_max(bf16x2_max(q[u].x, q[u].y), bf16x2_max(q[u].z, q[u].w)));
+    }
+  }
+  const float2 mm = unpack_bf16(m2);
+  float m = warp_max(fmaxf(mm.x, mm.y));
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < CE_ROW_THREADS / 32; ++i) m = fmaxf(m, red[i]);
+  __syncthreads();
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float nml = -m * LOG2E;
+  float s = 0.f;
+  for (int v = tid; v < nvec; v += CE_ROW_THREADS) {
+    const uint4 q = ce_row[v];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16(w[k]);
+      const float e0 = ex2_approx(fmaf(a.x, LOG2E, nml)), e1 = ex2_approx(fmaf(a.y, LOG2E, nml));
+      s += e0 + e1;
+      o[k] = pack_bf16(e0, e1);
+    }
+    ce_row[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  s = warp_sum(s);
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  s = 0.f;
+#pragma unroll
+  for (int i = 0; i < CE_ROW_THREADS / 32; ++i) s += red[i];
+  if (tid == 0) atomicAdd(loss_sum, m + __logf(s) - tgt_logit);
+  if (!write_grad) return;
+  const float scale = *scale_ptr, f = scale / s;
+  const int vt = (int)(tgt >> 3), et = (int)(tgt & 7);
+  for (int v = tid; v < nvec; v += CE_ROW_THREADS) {
+    const uint4 q = ce_row[v];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float g[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 a = unpack_bf16(w[k]); g[2 * k] = a.x * f; g[2 * k + 1] = a.y * f; }
+    if (v == vt) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (k == et) g[k] -= scale;
+    }
+    *reinterpret_cast<uint4*>(row + (long long)v * 8) =
+        make_uint4(pack_bf16(g[0], g[1]), pack_bf16(g[2], g[3]), pack_bf16(g[4], g[5]), pack_bf16(g[6], g[7]));
+  }
+}
+
 // ------------------------------------------------------------------ sum of squares (two stages, deterministic)
 constexpr int SUMSQ_BLOCKS = 1024, SUMSQ_THREADS = 256;
 
@@ -487,6 +631,15 @@ TLM_API int tlm_embedding_bwd(const long long* idx, const float* dx, float* grad
 
 TLM_API int tlm_add_rmsnorm_fwd(const float* x, const void* delta, const void* w, float* x_new, void* h, float* rstd,
                                 int rows, int D, float eps, cudaStream_t st) {
+  if (D % 256 == 0 && D / 256 <= 8 && D / 256 != 5 && D / 256 != 7) {
+    const int grid = grid_for((rows + 7) / 8, 1, 8);
+#define TLM_RMS_CASE(NV) case NV: add_rmsnorm_fwd_reg_kernel<NV><<<grid, 256, 0, st>>>(x, (const __nv_bfloat16*)delta, \
+      (const __nv_bfloat16*)w, x_new, (__nv_bfloat16*)h, rstd, rows, eps); break;
+    switch (D / 256) { TLM_RMS_CASE(1) TLM_RMS_CASE(2) TLM_RMS_CASE(3) TLM_RMS_CASE(4) TLM_RMS_CASE(6) TLM_RMS_CASE(8) }
+#undef TLM_RMS_CASE
+    count_launch();
+    return launch_status();
+  }
   int warps = 8;
   while (warps > 1 && (size_t)warps * D * 4 > 200 * 1024) warps >>= 1;
   size_t smem = (size_t)warps * D * 4;
@@ -557,6 +710,19 @@ TLM_API int tlm_swiglu_bwd(const void* dact, const void* gu, void* dgu, long lon
 TLM_API int tlm_ce_inplace(void* logits, const long long* targets, const float* scale, float* loss_sum, int rows, int V,
                            long long ld, long long ignore_index, int write_grad, cudaStream_t st) {
   if (rows <= 0) return 0;
+  const size_t row_bytes = (size_t)(V / 8) * 16;
+  if (row_bytes <= 200 * 1024) {
+    static size_t configured = 0;
+    if (row_bytes > 48 * 1024 && row_bytes > configured) {
+      cudaError_t e = cudaFuncSetAttribute(ce_inplace_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+      if (e != cudaSuccess) return (int)e;
+      configured = row_bytes;
+    }
+    ce_inplace_row_kernel<<<rows, CE_ROW_THREADS, row_bytes, st>>>((__nv_bfloat16*)logits, targets, scale, loss_sum, V, ld,
+                                                                   ignore_index, write_grad);
+    count_launch();
+    return launch_status();
+  }
   ce_inplace_kernel<<<rows, 512, 0, st>>>((__nv_bfloat16*)logits, targets, scale, loss_sum, V, ld, ignore_index, write_grad);
   count_launch();
   return launch_status();

@@ -383,7 +383,7 @@ class Trainer:
                 graph = torch.cuda.CUDAGraph()
                 before = native.launch_count()
                 try:
-                    with torch.cuda.graph(graph, capture_error_mode=os.environ.get("TLM_GRAPH_CAPTURE_MODE", "thread_local")):
+                    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                         self._graph_out = self._device_step()
                 except Exception as e:                                   # keep training on the ordinary path
                     self._graph_disabled = True
