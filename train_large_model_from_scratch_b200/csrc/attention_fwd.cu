@@ -209,18 +209,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
         for (int i = 0; i < AT_BKV; ++i) if (i <= row) mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // ---- move the reference (and rescale O in TMEM) only when the maximum grew a lot
-      const bool grow = mx > m_ref + tau;
-      if (j == 0) {
-        m_ref = mx;
-      } else {
-        // PV of the previous tile must be complete before P is overwritten and before O is touched
+      // ---- the reference only moves when the maximum grew a lot (O is then rescaled below)
+      const bool grow = j > 0 && mx > m_ref + tau;
+      float alpha = 1.f;
+      if (j == 0) m_ref = mx;
+      else if (grow) { alpha = ex2_approx((m_ref - mx) * p.scale_log2); m_ref = mx; }
+      const float neg_m = -m_ref * p.scale_log2;
+      // ---- probabilities as packed bf16 pairs, still in registers (they take the place of the S row)
+      float2 l2 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+      uint32_t pk[AT_BKV / 2];
+#pragma unroll
+      for (int i = 0; i < AT_BKV; i += 2) {
+        const float2 x = ffma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2);
+        float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+        if (diag) { if (i > row) pp.x = 0.f; if (i + 1 > row) pp.y = 0.f; }
+        l2 = fadd2(l2, pp);
+        pk[i >> 1] = pack_bf16(pp.x, pp.y);
+      }
+      // ---- only now is the previous tile's P V needed to be complete (P is overwritten, O may be rescaled):
+      // by this time it is, so the wait costs nothing
+      if (j > 0) {
         if (!mbar_wait(bar(9), par ^ 1u, 17, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, grow)) {
-          const float alpha = grow ? ex2_approx((m_ref - mx) * p.scale_log2) : 1.f;
 #pragma unroll
-          for (int c = 0; c < HD; c += 8) {                    // rare path; narrow chunks keep the S row in registers
+          for (int c = 0; c < HD; c += 8) {                    // rare path; narrow chunks keep registers free
             uint32_t r[8];
             tmem_ld8(t_lane + O_COL + c, r);
             tmem_ld_wait();
@@ -228,29 +242,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnFwdParams 
             for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
             tmem_st8(t_lane + O_COL + c, r);
           }
-          tmem_st_wait();
-          l_run *= alpha;
-          if (grow) m_ref = mx;
         }
       }
-      const float neg_m = -m_ref * p.scale_log2;
-      // ---- probabilities -> tensor memory (packed bf16 pairs, the A operand of the P V MMA)
-      float2 l2 = make_float2(0.f, 0.f);
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+      l_run = fmaf(l_run, alpha, l2.x + l2.y);
 #pragma unroll
-      for (int c = 0; c < AT_BKV; c += 32) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 x = ffma2(make_float2(__uint_as_float(sr[c + i]), __uint_as_float(sr[c + i + 1])), sc2, nm2);
-          float2 pp = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-          if (diag) { if ((c + i) > row) pp.x = 0.f; if ((c + i + 1) > row) pp.y = 0.f; }
-          l2 = fadd2(l2, pp);
-          pk[i >> 1] = pack_bf16(pp.x, pp.y);
-        }
-        tmem_st16(t_lane + P_COL + (c >> 1), pk);               // word i of the row = probabilities 2i, 2i+1
-      }
-      l_run += l2.x + l2.y;
+      for (int c = 0; c < AT_BKV; c += 32)
+        tmem_st16(t_lane + P_COL + (c >> 1), pk + (c >> 1));    // word i of the row = probabilities 2i, 2i+1
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
