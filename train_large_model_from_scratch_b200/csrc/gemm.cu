@@ -33,6 +33,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int BOX_MN_BYTES = 64 * BK * 2;            // one 64(mn) x 64(k) MN-major box = 8 KB
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS_WIDE = 320;               // 8 epilogue warps (two per TMEM lane quarter) for the heavy epilogue
 constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 bf16 staging tile
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
@@ -138,10 +139,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The SwiGLU-backward epilogue reads gate / up from global memory and is as long as the main loop of its
+  // K = hidden-size tiles, so it runs on 8 warps: warps 2-5 take the left 128 columns, warps 6-9 the right.
+  constexpr int EPI_WARPS = EPI == EPI_SWIGLU_BWD ? 8 : 4;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -276,6 +280,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       TileCoord t = get_tile(tile);
       if (!t.valid) continue;
+      if (EPI == EPI_SWIGLU_BWD) {
+        // gate / up of the NEXT tile start moving into L2 now, a whole tile time before they are read
+        auto prefetch_aux = [&](const TileCoord& tt) {
+          const int prow = tt.m0 + q * 32 + lane, pcol = tt.n0 + ((warp - 2) >> 2) * (BN / 2);
+          if (prow < p.M) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = pcol + (i & 1) * 64;
+              if (c < p.N)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.aux + (long long)prow * 2 * p.N + (i >> 1) * p.N + c));
+            }
+          }
+        };
+        if (tile == (int)blockIdx.x) prefetch_aux(t);
+        const int nxt = tile + gridDim.x;
+        if (nxt < total_tiles) { const TileCoord tn = get_tile(nxt); if (tn.valid) prefetch_aux(tn); }
+      }
       if (!mbar_wait(accf_bar(acc), acc_phase, 4, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       const int row = t.m0 + q * 32 + lane;
@@ -388,8 +409,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           }
         }
       } else if (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) {
-        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
-        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        // forward: two 4 KB staging tiles per warp (4 warps); backward: one per warp (8 warps)
+        constexpr int EBUF_PER_WARP = EPI == EPI_SWIGLU_BWD ? EPI_BUF_BYTES : 2 * EPI_BUF_BYTES;
+        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * EBUF_PER_WARP;
+        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * EBUF_PER_WARP;
         const int row0 = t.m0 + q * 32;
         int bsel = 0;
         // 64 bf16 columns (32 packed words) of this lane's row -> swizzled staging tile -> TMA store at (col, row0)
@@ -441,18 +464,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           // the bf16 tile in shared memory and re-reads it with 8 lanes per row: gate / up then come from global
           // memory as whole 128-byte rows (4 rows per load instruction instead of 32 scattered pieces) and the
           // results go back the same way.
-          uint8_t* bufA = ebuf;
-          uint8_t* bufB = ebuf + EPI_BUF_BYTES;
+          uint8_t* buf = ebuf;
           const int sub_row = lane >> 3, chunk = lane & 7;    // this lane's (row within a group of 4, 16-byte chunk)
+          const int slab0 = ((warp - 2) >> 2) * (BN / 128);    // this warp's half of the tile's four 64-column slabs
 #pragma unroll 1
-          for (int slab = 0; slab < BN / 64; ++slab) {
+          for (int slab = slab0; slab < slab0 + BN / 128; ++slab) {
             const int col = t.n0 + slab * 64;
             if (col >= p.N) break;                             // warp-uniform
             uint32_t d0[32], d1[32];
             tmem_ld32(taddr + slab * 64, d0);
             tmem_ld32(taddr + slab * 64 + 32, d1);
             tmem_ld_wait();
-            uint8_t* buf = (slab & 1) ? bufB : bufA;           // alternate, so staging slab s+1 cannot overtake readers of slab s
             {
               uint8_t* rowp = buf + lane * 128;
 #pragma unroll
@@ -637,7 +659,7 @@ gemm_swiglu_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
   gemm_body<false, false, EPI_SWIGLU>(tmA, tmB, tmC, p, &tmD);
 }
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_WIDE, 1)
 gemm_swiglu_bwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   gemm_body<false, true, EPI_SWIGLU_BWD>(tmA, tmB, tmC, p, nullptr);
@@ -826,7 +848,7 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   }
   const int tiles = ((M + BM - 1) / BM) * ((I + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  gemm_swiglu_bwd_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, mc, p);
+  gemm_swiglu_bwd_kernel<<<grid, GEMM_THREADS_WIDE, GEMM_SMEM, stream>>>(ma, mb, mc, p);
   count_launch();
   return launch_status();
 }

@@ -1,6 +1,6 @@
 """Per-kernel timing against the measured roofline.
 
-    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,attn,elementwise,moe] [--small] [--once]
+    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
 
 Times each kernel with CUDA events on the launching stream after warm-up,
 flushing L2 (a 256 MB write) between timed launches, and prints one JSON line
@@ -82,6 +82,26 @@ def bench_gemm(small: bool):
             if pk:
                 rec["frac_of_measured_peak"] = round(flops / med / 1e9 / pk, 3)
             print(json.dumps(rec), flush=True)
+
+
+def bench_mlp(small: bool):
+    """The two MLP GEMMs that carry the SwiGLU math in their epilogue."""
+    pk = _peaks().get("bf16_tflops")
+    M, D, I = (4096 if small else 32768), 1024, 4096
+    x = torch.randn(M, D, device="cuda").bfloat16()
+    w_gu = (torch.randn(2 * I, D, device="cuda") * 0.02).bfloat16()
+    w_down = (torch.randn(D, I, device="cuda") * 0.02).bfloat16()
+    dy = torch.randn(M, D, device="cuda").bfloat16()
+    gu, _ = native.gemm_swiglu(x, w_gu)
+    for name, fn, flops in (("gemm_swiglu (gate|up GEMM + SwiGLU)", lambda: native.gemm_swiglu(x, w_gu), 2.0 * M * 2 * I * D),
+                            ("gemm_swiglu_bwd (down dgrad + SwiGLU backward)", lambda: native.gemm_swiglu_bwd(dy, w_down, gu),
+                             2.0 * M * I * D)):
+        med, best = _time(fn)
+        rec = {"kernel": name, "M": M, "D": D, "I": I, "ms": round(med, 4), "ms_best": round(best, 4),
+               "tflops": round(flops / med / 1e9, 1)}
+        if pk:
+            rec["frac_of_measured_peak"] = round(flops / med / 1e9 / pk, 3)
+        print(json.dumps(rec), flush=True)
 
 
 def bench_elementwise(small: bool):
@@ -185,5 +205,5 @@ if __name__ == "__main__":
     _ONCE = a.once
     torch.cuda.set_device(0)
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise, "attn": bench_attn, "moe": bench_moe}[w](a.small)
+        {"gemm": bench_gemm, "mlp": bench_mlp, "elementwise": bench_elementwise, "attn": bench_attn, "moe": bench_moe}[w](a.small)
     native.raise_on_device_status()
