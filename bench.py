@@ -206,6 +206,8 @@ def run_ours(args) -> dict:
 
     n, K, W = args.gpus, args.steps, args.warmup
     assert world == n, f"--gpus {n} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {n}"
+    if not torch.cuda.is_available():                  # the CPU path runs, but it is the oracle, not the benchmark
+        raise SystemExit("bench.py measures the sm_100a kernels: no CUDA device is visible")
     log_dir = tempfile.mkdtemp(prefix="tlm_bench_")
     cfg = build_config(parse_args(_flags(n, 2 * (K + W), log_dir)))
     trainer = Trainer(cfg)
