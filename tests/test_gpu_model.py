@@ -77,3 +77,22 @@ def test_moe_model_matches_cpu_oracle():
     for a, b in ((gpu.dense_buf, cpu.dense_buf), (gpu.expert_buf, cpu.expert_buf)):
         cos = torch.nn.functional.cosine_similarity(a.main_grad.cpu(), b.main_grad, dim=0).item()
         assert cos > 0.98, cos
+
+
+def test_lm_head_cross_entropy_is_chunk_invariant(monkeypatch):
+    """The fused LM-head + cross-entropy gives the same loss and gradients in one chunk and in several."""
+    from train_large_model_from_scratch_b200.ops import functional as Fo
+    from train_large_model_from_scratch_b200.ops import native
+    data = torch.randint(0, 4096, (2, 257), generator=torch.Generator().manual_seed(3))
+    x, y = data[:, :-1].contiguous().cuda(), data[:, 1:].contiguous().cuda()
+    out = []
+    for chunk in (32768, 192):                       # 512 rows: one chunk, then three (the last one ragged)
+        monkeypatch.setattr(Fo._LinearCrossEntropy, "CHUNK_ROWS", chunk)
+        m = _build("cuda", torch.bfloat16)
+        _, loss, _ = m(x, y)
+        loss.backward()
+        native.raise_on_device_status()
+        out.append((loss.item(), m.dense_buf.main_grad.clone()))
+    assert abs(out[0][0] - out[1][0]) < 1e-4, (out[0][0], out[1][0])
+    cos = torch.nn.functional.cosine_similarity(out[0][1], out[1][1], dim=0).item()
+    assert cos > 0.9999, cos

@@ -122,6 +122,7 @@ def test_swiglu_grad():
 @pytest.mark.parametrize("chunk", [4096, 3])
 def test_linear_cross_entropy(chunk, monkeypatch):
     monkeypatch.setattr(Fo._LinearCrossEntropy, "CHUNK_ROWS", chunk)
+    monkeypatch.setattr(Fo._LinearCrossEntropy, "CHUNK_ROWS_CPU", chunk)
     M, D, V = 10, 16, 37
     h = torch.randn(M, D, requires_grad=True)
     w = _param(V, D).float().detach().requires_grad_()

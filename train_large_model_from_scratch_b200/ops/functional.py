@@ -335,7 +335,7 @@ def swiglu_mlp(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> tor
 class _LinearCrossEntropy(torch.autograd.Function):
     """`sum_i CE(h_i @ W^T, target_i)` without keeping the `[M, V]` logits.
 
-    The forward walks over row chunks (8192 rows: a 0.8 GB bf16 logits workspace for a 50k vocabulary): logits chunk = GEMM, one kernel turns it
+    The forward walks over row chunks (up to 32768 rows on the GPU: a 3.3 GB bf16 logits workspace for a 50k vocabulary, overwritten in place by its own gradient): logits chunk = GEMM, one kernel turns it
     in place into `grad_scale * (softmax - onehot)` while emitting the chunk's
     loss sum, then dgrad and wgrad GEMMs consume it. So the backward work is
     done during forward and `backward()` only hands out the stored `dh`.
@@ -344,7 +344,9 @@ class _LinearCrossEntropy(torch.autograd.Function):
     accumulation steps)); it stays on the device, no host sync is needed.
     """
 
-    CHUNK_ROWS = 8192
+    CHUNK_ROWS = 32768         # rows of logits alive at once on the GPU (3.3 GB of bf16 at V = 50304); measured on the
+                               # headline step: 8192 rows 176.5 ms, 16384 rows 175.5 ms, 32768 rows 174.8 ms
+    CHUNK_ROWS_CPU = 8192      # the fp32 path keeps its transient logits small
 
     @staticmethod
     def forward(ctx, h, weight, targets, grad_scale, ignore_index):
@@ -354,7 +356,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         dh = torch.empty_like(h) if need_grad else None
         loss_sum = torch.zeros((), dtype=torch.float32, device=h.device)
         use_nat = _use_native(h, weight)
-        step = _LinearCrossEntropy.CHUNK_ROWS
+        step = _LinearCrossEntropy.CHUNK_ROWS if use_nat else _LinearCrossEntropy.CHUNK_ROWS_CPU
         for r0 in range(0, M, step):
             r1 = min(M, r0 + step)
             hc, tc = h[r0:r1], targets[r0:r1]
