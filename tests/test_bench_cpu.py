@@ -1,0 +1,53 @@
+"""Host side of `bench.py`: configuration selection, the flags it hands to the real CLI, the JSON line."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load_bench():
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("name,n,sep,seq", [("B", 8, 1, 4096), ("C", 8, 8, 32768), ("C", 2, 2, 8192), ("D", 8, 8, 4096),
+                                            ("E", 8, 2, 4096), ("E", 1, 1, 4096), ("S", 1, 1, 4096)])
+def test_config_selection_and_flags_parse(name, n, sep, seq, tmp_path):
+    from train_large_model_from_scratch_b200.training import build_config, parse_args
+    b = _load_bench()
+    b._select_config(name, n)
+    assert (b.SEP_SIZE, b.SEQ_LEN) == (sep, seq)
+    cfg = build_config(parse_args(b._flags(n, 10, str(tmp_path))))
+    assert cfg.parallel.sep_size == sep and cfg.train.seq_len == seq
+    assert cfg.train.total_batch_size == seq * b.MICRO_BATCH * b.GRAD_ACCUM * (n // sep)
+    assert cfg.model.block_size >= seq and cfg.model.use_moe == (name == "D")
+
+
+def test_result_line_has_the_contract_keys():
+    b = _load_bench()
+    out = b._result("ours", 2, 4, 3, 800.0, 131072, {"sm_mhz": 1500.0, "sm_max_mhz": 1965.0, "reasons": []},
+                    {"gpu_launches": 10, "e2e": {"value": 1.0, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4}})
+    for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+              "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches"):
+        assert k in out, k
+    assert out["ms_per_step"] == 200.0 and abs(out["value"] - 131072 / 0.2) < 1e-6
+    assert out["n_gpus"] == 2 and out["higher_is_better"] is True and out["scaling"] == "weak"
+    json.dumps(out)
+
+
+def test_reference_arm_reports_unavailable_without_cuda():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("needs a box without CUDA")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1"],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-500:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
