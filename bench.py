@@ -16,6 +16,14 @@ For N > 1 launch with torchrun (one rank per GPU). Rank 0 prints ONE JSON line.
            from pinned host memory and reads the loss back to the host.
 `--impl reference` runs the unmodified reference from `baseline/_ref` through
 its own `Trainer` for the same model and batch shape.
+
+The default run (configuration B, the headline) is followed by the other half
+of the benchmark: the 0.3B-class MoE (`--config D`, SEP = EP = N) and the same
+dense model under Ulysses sequence parallelism (`--config C`, SEP = N), each
+measured in a fresh child job on the same GPUs after the headline job has
+released them, with its own warm-up, timing and clock samples; their results
+are the `moe` and `ulysses` entries of the JSON line (both arms do this, so the
+two lines can be compared entry by entry). `--no-extras` skips them.
 """
 from __future__ import annotations
 
@@ -259,7 +267,13 @@ def run_ours(args) -> dict:
         "final_loss": losses[-1] if losses else None,
     }
     out = _result("ours", n, K, W, ms_dev, tokens_per_step, clocks, extra)
+    if world > 1:
+        dist.barrier()
     trainer.close()
+    del trainer, pool, step_device, step_e2e              # release the GPUs for the jobs that follow
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
     return out if rank == 0 else None
 
 
@@ -312,9 +326,72 @@ def run_reference(args) -> dict:
     extra = {"e2e": {"value": tokens_per_step / (ms / K / 1e3), "unit": "tokens/s", "ms_per_step": ms / K,
                      "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
              "gpu_launches": None, "final_loss": losses[-1], "use_compile": bool(args.ref_compile)}
+    if cfg.model.use_moe:
+        extra["moe_expert_path"] = ("padded bmm (grouped_gemm_supported forced off: its grouped_mm call needs "
+                                    "moe_intermediate_size == hidden_size)" if args.moe_fallback else "grouped_mm")
     out = _result("reference", n, K, W, ms, tokens_per_step, clocks, extra)
     dist.destroy_process_group()
+    del trainer, step
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
     return out if rank == 0 else None
+
+
+def _free_port() -> int:
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+EXTRAS = (("moe", "D"), ("ulysses", "C"))
+_KEEP = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "impl", "config", "clocks", "e2e", "gpu_launches",
+         "final_loss", "use_compile", "unavailable", "moe_expert_path")
+
+
+def run_extras(args) -> dict:
+    """Measure the other configurations of the benchmark, one child job each, on the GPUs the finished headline
+    job has released. Called by rank 0 only, after its process group is gone. A child that fails or exceeds its
+    time limit is reported as `{"unavailable": ...}`; it never takes the headline result with it."""
+    out = {}
+    env = {k: v for k, v in os.environ.items()
+           if not (k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_NAME",
+                         "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS")
+                   or k.startswith("TORCHELASTIC_") or k.startswith("TORCH_NCCL_ASYNC"))}
+    steps = min(args.steps, 20)
+    for key, cfg in EXTRAS:
+        tail = [os.path.join(ROOT, "bench.py"), "--gpus", str(args.gpus), "--steps", str(steps), "--warmup", str(args.warmup),
+                "--config", cfg, "--impl", args.impl, "--no-extras", "--ref-compile", str(args.ref_compile),
+                "--moe-fallback", str(args.moe_fallback)]
+        if args.gpus > 1:
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(_free_port())] + tail
+        else:
+            cmd = [sys.executable] + tail
+        t0 = time.time()
+        try:
+            proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                                    start_new_session=True)
+            try:
+                so, se = proc.communicate(timeout=args.extra_timeout)
+            except subprocess.TimeoutExpired:
+                import signal
+                os.killpg(proc.pid, signal.SIGKILL)          # the process group this call started, nothing else
+                proc.communicate()
+                out[key] = {"unavailable": f"config {cfg}: no result within {args.extra_timeout} s"}
+                continue
+            line = next((l for l in reversed(so.splitlines()) if l.startswith("{") and l.rstrip().endswith("}")), None)
+            if proc.returncode != 0 or line is None:
+                err = (se or so).strip().splitlines()
+                out[key] = {"unavailable": f"config {cfg}: exit code {proc.returncode}: " + " | ".join(err[-3:])[:300]}
+                continue
+            r = json.loads(line)
+            out[key] = {k: r[k] for k in _KEEP if k in r}
+            out[key]["wall_s"] = round(time.time() - t0, 1)
+        except Exception as e:                                       # never lose the headline over an extra
+            out[key] = {"unavailable": f"config {cfg}: {type(e).__name__}: {str(e)[:200]}"}
+    return out
 
 
 def main():
@@ -330,6 +407,9 @@ def main():
     ap.add_argument("--moe-fallback", type=int, default=1,
                     help="reference arm, MoE configs: force its padded-bmm expert path (its grouped path only "
                          "type-checks for moe_intermediate_size == hidden_size)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline configuration only: do not measure the MoE and Ulysses configurations afterwards")
+    ap.add_argument("--extra-timeout", type=int, default=900, help="time limit of one extra configuration's job (s)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     _select_config(args.config, args.gpus)
@@ -342,6 +422,8 @@ def main():
     else:
         out = run_ours(args)
     if out is not None:
+        if args.config == "B" and not args.no_extras and "unavailable" not in out:
+            out.update(run_extras(args))
         print(json.dumps(out), flush=True)
 
 

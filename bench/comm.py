@@ -1,6 +1,6 @@
 """Peer-memory communication kernels against their NVLink roofline.
 
-    torchrun --nproc-per-node N -m train_large_model_from_scratch_b200.parallel.bench_comm [--mb 1024]
+    torchrun --nproc-per-node N -m bench.comm [--mb 1024]
 
 Times, with CUDA events and the maximum over ranks, the kernels that move data between GPUs:
 
@@ -53,8 +53,8 @@ def main():
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
-    from ..ops import native
-    from .symm import _Peer, symm_alloc
+    from train_large_model_from_scratch_b200.ops import native
+    from train_large_model_from_scratch_b200.parallel.symm import _Peer, symm_alloc
     dev = torch.device("cuda", torch.cuda.current_device())
     n = (a.mb << 20) // 4
     n -= n % (1024 * world)

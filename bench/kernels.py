@@ -1,11 +1,12 @@
 """Per-kernel timing against the measured roofline.
 
-    python -m train_large_model_from_scratch_b200.ops.bench_kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
+    python -m bench.kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
 
 Times each kernel with CUDA events on the launching stream after warm-up,
 flushing L2 (a 256 MB write) between timed launches, and prints one JSON line
-per case with achieved TFLOP/s or GB/s and, when a peaks file is present
-(`MEASURED_PEAKS.json`), the fraction of the measured cuBLAS / copy peak. The
+per case with achieved TFLOP/s or GB/s and, when a peaks file is named by the
+`TLM_MEASURED_PEAKS` environment variable (JSON with `bf16_tflops`, `hbm_gbs`),
+the fraction of the measured cuBLAS / copy peak. The
 library GEMM (`torch.matmul`, cuBLAS) is timed on the same shapes for context.
 `--once` launches every kernel a single time without timing (the workload for a
 profiler capture).
@@ -18,11 +19,11 @@ import os
 
 import torch
 
-from . import native
+from train_large_model_from_scratch_b200.ops import native
 
 
 def _peaks():
-    for p in (os.environ.get("TLM_MEASURED_PEAKS"), "MEASURED_PEAKS.json"):
+    for p in (os.environ.get("TLM_MEASURED_PEAKS"),):
         if p and os.path.exists(p):
             with open(p) as f:
                 return json.load(f)
@@ -160,7 +161,7 @@ def bench_attn(small: bool):
 def bench_moe(small: bool):
     """Routing, gather / combine and the head-scatter (QKV + RoPE) GEMM epilogue."""
     import ctypes
-    from . import oracle
+    from train_large_model_from_scratch_b200.ops import oracle
     bw = _peaks().get("hbm_gbs")
     M, E, k, D = (4096 if small else 32768), 8, 2, 1024
     logits = torch.randn(M, E, device="cuda").bfloat16()

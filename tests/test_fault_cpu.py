@@ -36,7 +36,7 @@ def test_heartbeat_detects_silent_and_failed_peers():
     now[0] += 4.0
     a.check()                                            # within the limit
     a.beat(1)
-    now[0] += 2.0                                        # rank 1 last beat 6 s ago
+    now[0] += 6.0                                        # rank 1's heartbeat has not changed for 6 s on rank 0's clock
     with pytest.raises(PeerFailure) as e:
         a.check()
     assert e.value.rank == 1 and "no heartbeat" in str(e.value)
@@ -47,6 +47,56 @@ def test_heartbeat_detects_silent_and_failed_peers():
     with pytest.raises(PeerFailure) as e:
         a.check()
     assert e.value.rank == 1 and "boom" in str(e.value)
+
+
+def test_long_pause_between_steps_is_not_a_failure_but_a_missing_peer_is():
+    """Evaluation, a checkpoint or set-up between two steps may outlast the heartbeat limit on every rank:
+    `enter_step` judges liveness by the rendezvous itself (the peer arrives within the limit counted from
+    now), not by the age of the last heartbeat."""
+    from train_large_model_from_scratch_b200.utils.health import Heartbeat, PeerFailure
+    store, now = _FakeStore(), [0.0]
+
+    def clock():
+        now[0] += 0.05
+        return now[0]
+    a = Heartbeat(0, 2, timeout_s=3.0, store=store, clock=clock)
+    b = Heartbeat(1, 2, timeout_s=3.0, store=store, clock=clock)
+    a.beat(0); b.beat(0)
+    a.check(); b.check()
+    now[0] += 500.0                                      # both ranks spend 500 s in evaluation + save
+    store.set("tlm/enter/0", "1")                        # rank 0 arrives at step 1 ...
+    b.enter_step(1, poll_s=0.0)                          # ... and rank 1 joins without complaint
+    a.enter_step(1, poll_s=0.0)
+    a.beat(1)
+    with pytest.raises(PeerFailure) as e:                # rank 1 never arrives at step 2
+        a.enter_step(2, poll_s=0.0)
+    assert e.value.rank == 1 and "did not arrive" in str(e.value)
+
+
+def test_device_timeout_aborts_the_step_before_it_is_logged_or_saved(tmp_path, monkeypatch):
+    """A nonzero device status word after a step (a kernel gave up on a flag wait, so its exchange did not
+    happen) must end the run before the step is committed: no log line, no checkpoint."""
+    import torch
+    from train_large_model_from_scratch_b200.training import Trainer, build_config, parse_args
+    from train_large_model_from_scratch_b200.utils.health import DeviceTimeout
+    flags = TINY + ["--log_dir", str(tmp_path), "--total_batch_size", "512", "--batch_size", "2",
+                    "--do_save", "--save_every_steps", "1", "--sep_size", "1"]
+    trainer = Trainer(build_config(parse_args(flags)))
+    calls = {"n": 0}
+
+    def fake_status():
+        calls["n"] += 1
+        return (41 << 8) | 1 if calls["n"] == 2 else 0       # the second step's reduce-scatter timed out
+
+    monkeypatch.setattr(trainer, "_read_device_status", fake_status)
+    with pytest.raises(DeviceTimeout) as e:
+        trainer.train()
+    assert e.value.status == (41 << 8) | 1 and "site 41" in str(e.value)
+    log = open(trainer.log_file).read().splitlines()
+    assert len(log) == 1 and log[0].startswith("0 train")      # step 1 was never logged
+    import glob
+    assert not glob.glob(str(tmp_path / "*" / "00001_meta.pt"))
+    trainer.close()
 
 
 def test_wait_for_step_times_out_on_a_lagging_peer():

@@ -45,6 +45,22 @@ def test_noalloc_sumsq_matches_regular_entry_point_twice():
         torch.testing.assert_close(got, x.double().pow(2).sum().float(), rtol=1e-5, atol=1e-3)
 
 
+def test_noalloc_sumsq_ragged_lengths_and_empty_input():
+    """Lengths that are not a multiple of the 4-wide vector loads take the scalar tail; n = 0 gives 0."""
+    native, fn, err = _entry()
+    stream = torch.cuda.current_stream().cuda_stream
+    out = torch.full((), -1.0, dtype=torch.float32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(7)
+    base = torch.randn((1 << 16) + 8, device="cuda", generator=g)
+    for n in (1, 2, 3, 5, 1023, (1 << 16) + 1, (1 << 16) + 3, 0):
+        x = base[:n] if n else base[:4]
+        code = fn(x.data_ptr(), n, out.data_ptr(), stream)
+        assert code == 0, err(code)
+        torch.testing.assert_close(out.clone(), base[:n].double().pow(2).sum().float(), rtol=1e-5, atol=1e-4)
+        if n:
+            torch.testing.assert_close(out.clone(), native.sumsq(base[:n].clone()), rtol=1e-5, atol=1e-4)
+
+
 def test_noalloc_sumsq_rejects_oversize_and_bad_arguments():
     native, fn, err = _entry()
     x = torch.zeros(16, device="cuda")

@@ -750,6 +750,21 @@ TLM_API int tlm_adamw(float* p, float* m, float* v, const float* g, void* p_out,
   return launch_status();
 }
 
+// Contract check without a host sync: records status code (site << 8 | 2) when *a and *b differ by more than
+// rel_tol * max(|a|, |b|) (or either is not finite). The host sees it at its next look at the status word.
+__global__ void expect_close_kernel(const float* a, const float* b, float rel_tol, unsigned int site, unsigned int* status) {
+  const float x = *a, y = *b;
+  const float tol = rel_tol * fmaxf(fabsf(x), fabsf(y));
+  if (!(fabsf(x - y) <= tol)) tlm::report_status(status, (site << 8) | 2u);
+}
+
+TLM_API int tlm_expect_close(const float* a, const float* b, float rel_tol, int site, cudaStream_t st) {
+  if (a == nullptr || b == nullptr) return -6;
+  expect_close_kernel<<<1, 1, 0, st>>>(a, b, rel_tol, (unsigned int)site, status_word());
+  count_launch();
+  return launch_status();
+}
+
 // ------------------------------------------------------------------ sum of squares without any allocation
 #include "tlm_noalloc.h"
 

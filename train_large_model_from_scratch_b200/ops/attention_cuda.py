@@ -18,6 +18,20 @@ def _native_ok(hd: int) -> bool:
     return hd in (32, 64, 128)
 
 
+_WARNED: set = set()
+
+
+def _warn_library_path(hd: int, causal: bool) -> None:
+    """Said once per shape class: a configuration must never be measured on the library kernels unnoticed."""
+    key = (hd, causal)
+    if key not in _WARNED:
+        _WARNED.add(key)
+        import warnings
+        warnings.warn(f"attention with head dim {hd}, causal={causal} is outside the tcgen05 kernels "
+                      f"(head dims 32 / 64 / 128, causal): running the library SDPA kernels instead",
+                      RuntimeWarning, stacklevel=3)
+
+
 def fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
     """qkv `[B, T, n_q + 2 n_kv, hd]` bf16 -> (o `[B, T, n_q, hd]` bf16, lse `[B, n_q, T]` fp32)."""
     B, T, _, hd = qkv.shape
@@ -28,6 +42,7 @@ def fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
         native._check(native.lib().tlm_attn_fwd(qkv.data_ptr(), o.data_ptr(), lse.data_ptr(), B, T, n_q, n_kv, hd,
                                                 1.0 / math.sqrt(hd), native._stream()), "attn_fwd")
         return o, lse
+    _warn_library_path(hd, causal)
     q, k, v = _split(qkv, n_q, n_kv)
     out = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, causal, False)
     return out[0].transpose(1, 2).contiguous(), out[1]
@@ -70,6 +85,7 @@ def bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
                                                 dqkv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, T, n_q, n_kv,
                                                 hd, 1.0 / math.sqrt(hd), native._stream()), "attn_bwd")
         return dqkv
+    _warn_library_path(hd, causal)
     rep = n_q // n_kv
     q, k, v = _split(qkv, n_q, n_kv)
     zero = torch.zeros((), dtype=torch.int64, device=qkv.device)

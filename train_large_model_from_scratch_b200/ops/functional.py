@@ -342,6 +342,12 @@ class _LinearCrossEntropy(torch.autograd.Function):
     `grad_scale` (a 0-d fp32 tensor) must be the factor that the caller applies
     to the returned sum to form the final loss (e.g. 1 / (valid tokens * grad
     accumulation steps)); it stays on the device, no host sync is needed.
+    Because the weight gradient has already been accumulated with that factor
+    when `backward()` runs, the contract is CHECKED there: the incoming
+    gradient must equal `grad_scale` (on the CPU path an exception; on CUDA a
+    one-thread kernel that records status site 70 in the device status word,
+    which the trainer turns into an error at the step's synchronize, without a
+    host sync on the hot path).
     """
 
     CHUNK_ROWS = 32768         # rows of logits alive at once on the GPU (3.3 GB of bf16 at V = 50304); measured on the
@@ -381,12 +387,23 @@ class _LinearCrossEntropy(torch.autograd.Function):
                     dh[r0:r1] = dl @ weight
                     mg.add_(dl.float().t() @ hc.float())
         ctx.dh = dh
+        ctx.grad_scale = grad_scale
         return loss_sum
 
     @staticmethod
     def backward(ctx, g):
-        # dh already carries grad_scale; `g` equals grad_scale by contract.
+        # dh and the accumulated weight gradient already carry grad_scale: the upstream gradient must be it
         dh, ctx.dh = ctx.dh, None
+        gs = ctx.grad_scale
+        if dh is not None:
+            if g.is_cuda and native.available():
+                gs_t = gs if torch.is_tensor(gs) else torch.full((), float(gs), dtype=torch.float32, device=g.device)
+                native.expect_close(g.reshape(()).float(), gs_t.reshape(()).float().to(g.device), 1e-3,
+                                    native.SITE_CE_UPSTREAM_GRAD)
+            elif not torch.allclose(g.detach().float().reshape(()).cpu(), torch.as_tensor(gs).float().reshape(()).cpu(),
+                                    rtol=1e-3, atol=0.0):
+                raise RuntimeError("linear_cross_entropy: the upstream gradient differs from grad_scale; multiply "
+                                   "the returned sum by exactly the grad_scale that was passed in")
         return dh, None, None, None, None
 
 

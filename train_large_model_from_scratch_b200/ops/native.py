@@ -90,6 +90,7 @@ _SIGS = {
     "tlm_moe_pair_dot": (_I, [_P, _P, _P, _P, _LL, _I, _I, _P]),
     "tlm_gemm_grouped_rows_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _P, _P, _P, _I, _LL, _P]),
     "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P, _P]),
+    "tlm_expect_close": (_I, [_P, _P, _F, _I, _P]),
 }
 
 
@@ -145,7 +146,26 @@ def raise_on_device_status() -> None:
     torch.cuda.synchronize()
     st = take_device_status()
     if st:
-        raise NativeError(f"a kernel timed out waiting at site {st >> 8} (detail {st & 0xff})")
+        raise NativeError(describe_status(st))
+
+
+def describe_status(st: int) -> str:
+    site, detail = st >> 8, st & 0xff
+    if site == SITE_CE_UPSTREAM_GRAD:
+        return ("linear_cross_entropy: the gradient that reached the fused LM-head loss differs from the "
+                "grad_scale it was given (the loss was rescaled after the op); its gradients are wrong")
+    return f"a kernel timed out waiting at site {site} (detail {detail})"
+
+
+SITE_CE_UPSTREAM_GRAD = 70
+
+
+def expect_close(a: torch.Tensor, b: torch.Tensor, rel_tol: float, site: int) -> None:
+    """Device-side contract check of two 0-d fp32 CUDA tensors (no host sync): if they differ by more than
+    `rel_tol` relatively, the device status word gets `site << 8 | 2`, which `take_device_status()` (and the
+    trainer after each step) reports."""
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_cuda and b.is_cuda
+    _check(lib().tlm_expect_close(a.data_ptr(), b.data_ptr(), float(rel_tol), int(site), _stream()), "expect_close")
 
 
 def wait_flag(flag: torch.Tensor, expect: int, limit_s: float) -> None:

@@ -58,9 +58,13 @@ class PeerMoE:
         native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, 0, native._stream()), "peer_barrier")
 
     def buffer(self, key, rows: int, D: int):
+        """Receive buffer of `key` for this shape; cached per (key, shape) and never freed, because a recorded
+        CUDA graph keeps writing to (and its peers keep addressing) the buffers of the shape it was recorded
+        with, while a call with another shape (ragged last batch, evaluation) needs its own."""
         from ..symm import symm_alloc, _Peer
+        key = (key, int(rows), int(D))
         b = self.buffers.get(key)
-        if b is None or b[0].shape != (rows, D):
+        if b is None:
             t = symm_alloc(rows * D, torch.bfloat16, self.dev).view(rows, D)
             b = (t, _Peer(t, self.group))
             self.buffers[key] = b

@@ -80,8 +80,13 @@ class PeerState:
         return cls._instance
 
     def buffer(self, key, shape, device) -> _Exchange:
+        """The receive buffer of `key` for this shape. Buffers are cached per (key, shape) and never freed: a
+        recorded CUDA graph has the local and peer addresses of the buffers of ITS shape in its kernel arguments
+        and tensor maps, so a call with another shape (a ragged last batch, an evaluation batch) must get a
+        buffer of its own instead of replacing the one the recording still writes to."""
+        key = (key, tuple(int(s) for s in shape))
         ex = self.buffers.get(key)
-        if ex is None or tuple(ex.tensor.shape) != tuple(shape):
+        if ex is None:
             ex = _Exchange(shape, self.group, device)
             self.buffers[key] = ex
         return ex

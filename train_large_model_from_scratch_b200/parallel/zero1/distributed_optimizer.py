@@ -111,7 +111,10 @@ class FusedAdamW:
         dev = self.buffers[0].params.device if self.buffers else torch.device("cpu")
         if dev.type == "cuda":
             self._hyper = torch.zeros(4, dtype=torch.float32, device=dev)
-            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            # a ring of pinned staging slots: the host may run several steps ahead of the device (graph replay
+            # does not wait), and a slot is only rewritten once the copy that read it has run
+            self._hyper_host = [torch.zeros(4, dtype=torch.float32).pin_memory() for _ in range(4)]
+            self._hyper_done = [None] * len(self._hyper_host)
         else:
             self._hyper = self._hyper_host = None
 
@@ -129,8 +132,15 @@ class FusedAdamW:
         if self._hyper is not None:
             b1, b2 = g["betas"]
             vals = native.adam_hyper(self.step_count, g["lr"], b1, b2)
-            self._hyper_host[0], self._hyper_host[1], self._hyper_host[2] = vals
-            self._hyper.copy_(self._hyper_host, non_blocking=True)
+            slot = self.step_count % len(self._hyper_host)
+            if self._hyper_done[slot] is not None:
+                self._hyper_done[slot].synchronize()          # the copy that last read this slot has run
+            host = self._hyper_host[slot]
+            host[0], host[1], host[2] = vals
+            self._hyper.copy_(host, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._hyper_done[slot] = ev
 
     @torch.no_grad()
     def step_device(self, grad_clip_value: float | None = None):

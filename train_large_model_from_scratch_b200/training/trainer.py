@@ -91,6 +91,8 @@ class Trainer:
         self._graph_launches = 0
         self._graph_eager_steps = 0
         self._graph_disabled = False
+        self._prefetched = None            # next step's batches, already on their way to the device
+        self._copy_stream = None
 
     # ------------------------------------------------------------------ init hooks
     def _init_distributed(self, config: Config) -> None:
@@ -273,8 +275,15 @@ class Trainer:
             x = x.pin_memory()
         return x.to(self.device, non_blocking=True)
 
+    def _batch_to_device(self, data_batch: dict):
+        """(input_ids, labels) of this rank's sequence slice on the training device. Batches that `_prefetch`
+        already sliced and copied are passed through."""
+        if data_batch.get("_staged", False):
+            return data_batch["input_ids"], data_batch["labels"]
+        return self._to_device(data_batch["input_ids"]), self._to_device(data_batch["labels"])
+
     def _one_training_micro_step(self, config: Config, micro_step: int, data_batch: dict):
-        x, y = self._to_device(data_batch["input_ids"]), self._to_device(data_batch["labels"])
+        x, y = self._batch_to_device(data_batch)
         ga = self.training_info["grad_accum_steps"]
         with self.profiler_record_fn("forward"):
             _, loss, logging_loss = self.model(x, y, loss_scale=1.0 / ga)
@@ -294,10 +303,49 @@ class Trainer:
             _, batch = next(self.train_loader_iter)
         return batch
 
+    # ------------------------------------------------------------------ input prefetch
+    def _prefetch(self) -> None:
+        """Fetch the NEXT step's micro-batches from the loader, slice this rank's part of the sequence, stage
+        it in pinned memory and start its host->device copy on a side stream. Called right after a step's
+        device work has been queued, so that the loader's host work and the copy run under that step's
+        kernels (the reference copies each batch synchronously in front of its forward pass,
+        `training/trainer.py:227-228`)."""
+        if not self.use_cuda or os.environ.get("TLM_PREFETCH", "1") == "0":
+            return
+        ga = self.training_info["grad_accum_steps"]
+        host = [self._next_batch() for _ in range(ga)]
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        staged = []
+        with torch.cuda.stream(self._copy_stream):
+            for b in host:
+                x, y = self._sp_slice(b["input_ids"]).contiguous(), self._sp_slice(b["labels"]).contiguous()
+                if not x.is_pinned():
+                    x, y = x.pin_memory(), y.pin_memory()
+                staged.append({"input_ids": x.to(self.device, non_blocking=True),
+                               "labels": y.to(self.device, non_blocking=True), "_staged": True, "_pinned": (x, y)})
+            ready = torch.cuda.Event()
+            ready.record(self._copy_stream)
+        self._prefetched = (staged, ready)
+
+    def _take_prefetched(self):
+        """The batches `_prefetch` staged (the current stream is made to wait for their copies), or None."""
+        if self._prefetched is None:
+            return None
+        staged, ready = self._prefetched
+        self._prefetched = None
+        torch.cuda.current_stream().wait_event(ready)
+        for b in staged:                      # the copies ran on the side stream: tie the tensors to this one as well
+            b["input_ids"].record_stream(torch.cuda.current_stream())
+            b["labels"].record_stream(torch.cuda.current_stream())
+        return staged
+
     def _one_training_step(self, config: Config, step: int, batches: list | None = None) -> None:
         self.model.train()
         self.optimizer.zero_grad()
         loss_accum = None
+        if batches is None:
+            batches = self._take_prefetched()
         for micro_step in range(self.training_info["grad_accum_steps"]):
             batch = batches[micro_step] if batches is not None else self._next_batch()
             l = self._one_training_micro_step(config, micro_step, batch)
@@ -356,8 +404,11 @@ class Trainer:
         from ..ops import native
         cfg = self.config
         ga = self.training_info["grad_accum_steps"]
+        if batches is None:
+            batches = self._take_prefetched()
         host = batches if batches is not None else [self._next_batch() for _ in range(ga)]
-        xs = [(self._sp_slice(b["input_ids"]), self._sp_slice(b["labels"])) for b in host]
+        xs = [((b["input_ids"], b["labels"]) if b.get("_staged", False)
+               else (self._sp_slice(b["input_ids"]), self._sp_slice(b["labels"]))) for b in host]
         if self._graph_in is None:
             self._graph_in = [{"input_ids": torch.empty(x.shape, dtype=torch.int64, device=self.device),
                                "labels": torch.empty(y.shape, dtype=torch.int64, device=self.device)} for x, y in xs]
@@ -382,16 +433,23 @@ class Trainer:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 before = native.launch_count()
+                err = None
                 try:
                     with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                         self._graph_out = self._device_step()
                 except Exception as e:                                   # keep training on the ordinary path
+                    import traceback
+                    err = (f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}\n"
+                           + "".join(traceback.format_exc().splitlines(keepends=True)[-14:]))
+                # Every rank must take the same decision: the kernels of a replayed step and of an ordinary step
+                # count the same flag epochs, but a rank that replays while another one re-runs its set-up
+                # collectives would wait for exchanges the other never starts.
+                if not self._all_ranks_ok(err is None):
                     self._graph_disabled = True
-                    if self.master_process:
-                        import traceback
-                        where = "".join(traceback.format_exc().splitlines(keepends=True)[-14:])
-                        print(f"[warn] recording the step as a CUDA graph failed ({type(e).__name__}: "
-                              f"{str(e).splitlines()[0]}); continuing without it\n{where}")
+                    self._graph_out = None
+                    if err is not None:
+                        print(f"[warn] rank {self.rank}: recording the step as a CUDA graph failed ({err}); "
+                              f"all ranks continue without it")
                     torch.cuda.synchronize()
                     loss, norm = self._device_step()
                     self.one_step_results.update(lr=lr, loss=loss, grad_norm=norm)
@@ -400,9 +458,38 @@ class Trainer:
                 self._graph = graph
             self._graph.replay()
             native.add_launch_count(self._graph_launches)
-            loss, norm = self._graph_out
+            # the recording writes its results into the same two tensors every time: hand out copies
+            loss, norm = (t.clone() for t in self._graph_out)
         self.one_step_results.update(lr=lr, loss=loss, grad_norm=norm)
         return True
+
+    def _all_ranks_ok(self, ok: bool) -> bool:
+        """Logical AND of `ok` over all ranks (a host-side collective; call outside of stream capture)."""
+        if self.world_size == 1:
+            return ok
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def _read_device_status(self) -> int:
+        """Status word of the kernels' bounded waits (0 = no wait ran out) since the last call. It lives in
+        mapped host memory, so reading it costs nothing; the caller has synchronised."""
+        if not self.use_cuda:
+            return 0
+        from ..ops import native
+        return native.take_device_status() if native.available() else 0
+
+    def _check_device_status(self) -> None:
+        """After a step's synchronize: a kernel that gave up on a flag or barrier wait skipped its exchange
+        (stale gradient shard, norm 0), so the step must not be committed. Raises `DeviceTimeout` and tells
+        the peers through the heartbeat store."""
+        st = self._read_device_status()
+        if st:
+            from ..utils.health import DeviceTimeout
+            err = DeviceTimeout(st)
+            if self.heartbeat is not None:
+                self.heartbeat.announce_failure(str(err))
+            raise err
 
     def train_step(self, step: int, batches: list | None = None) -> dict:
         """One optimizer step (all micro-steps). Public entry for callers that
@@ -421,6 +508,8 @@ class Trainer:
                 pend = getattr(self, "_pending_batches", None)
                 self._pending_batches = None
                 self._one_training_step(self.config, step, batches if pend is None else pend)
+            if batches is None and step + 1 < self.training_info["max_steps"]:
+                self._prefetch()                   # host work + H2D copy of the next step, under this step's kernels
         except BaseException as e:
             if hb is not None:
                 hb.announce_failure(f"{type(e).__name__}: {e}")
@@ -428,6 +517,7 @@ class Trainer:
         if hb is not None:
             if self.use_cuda:
                 torch.cuda.synchronize()
+                self._check_device_status()
             hb.beat(step)
         return self.one_step_results
 
@@ -529,6 +619,7 @@ class Trainer:
                 ev1.record()
                 torch.cuda.synchronize()
                 self.step_ms_device = ev0.elapsed_time(ev1)
+            self._check_device_status()            # before logging, evaluation and save(): never commit a bad step
             if self.profiler:
                 self.profiler.step()
             if not cfg.train.debug and cfg.train.do_val and (step % cfg.train.val_every_steps == 0 or last_step):
@@ -540,6 +631,8 @@ class Trainer:
             if cfg.ckpt.do_save and not cfg.train.debug and step > 0 and (
                     step % cfg.ckpt.save_every_steps == 0 or last_step):
                 self.save(step)
+            if self.heartbeat is not None:
+                self.heartbeat.beat(step)          # evaluation and saving can outlast the heartbeat limit
             dt = time.time() - t0
             tokens = cfg.train.batch_size * cfg.train.seq_len * ga * self.dp_world_size
             mfu, _, _ = compute_mfu(self.raw_model, cfg.train.batch_size, cfg.train.seq_len, dt, ga, dtype="bf16") \
@@ -556,7 +649,7 @@ class Trainer:
                       f"tok/sec: {tokens / dt:.2f} | MFU: {mfu * 100:.2f}%{extra}")
                 with open(self.log_file, "a") as f:
                     f.write(f"{step} train {loss_v:.6f}\n")
-            self.results[step] = self.one_step_results
+            self.results[step] = dict(self.one_step_results)
         if self.profiler:
             self.profiler.stop()
         self.close()

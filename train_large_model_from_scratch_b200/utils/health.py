@@ -29,8 +29,23 @@ class PeerFailure(RuntimeError):
         self.rank, self.reason = rank, reason
 
 
+class DeviceTimeout(RuntimeError):
+    """A kernel of this rank gave up on a bounded wait (flag, barrier or mbarrier): `status` is the device
+    status word, `site << 8 | detail`. The exchange the kernel was waiting for did not happen, so the data it
+    would have produced (a gradient shard, a received tile) is stale and the step must not be kept."""
+
+    def __init__(self, status: int):
+        super().__init__(f"a kernel timed out waiting at site {status >> 8} (detail {status & 0xff}); "
+                         f"the step's result is not valid")
+        self.status = int(status)
+
+
 class Heartbeat:
-    """`enter_step(step)` before each step, `beat(step)` after it; `check()` at any time.
+    """`enter_step(step)` before each step, `beat(step)` after it (and after anything long that runs between
+    steps: evaluation, a checkpoint); `check()` at any time.
+
+    Ages are measured on the READER's clock: a peer's heartbeat is as old as the time since this rank first
+    saw its current value, so clocks of different hosts are never compared.
 
     `store` is any c10d store shared by the job (default: the store of the
     default process group). Keys: `tlm/hb/<rank>` = "<step>:<unix time>",
@@ -41,6 +56,7 @@ class Heartbeat:
             store = dist.distributed_c10d._get_default_store()
         self.store, self.rank, self.world, self.timeout, self.clock = store, rank, world_size, float(timeout_s), clock
         self.prefix = prefix
+        self._seen: dict = {}               # peer rank -> (raw heartbeat value, local time it was first seen)
         self.beat(-1)
 
     def _key(self, kind: str, rank: int) -> str:
@@ -58,21 +74,29 @@ class Heartbeat:
             pass
 
     def peer_state(self, rank: int):
-        """(step, age in seconds) of `rank`'s last heartbeat, or None before its first one."""
+        """(step, age in seconds) of `rank`'s last heartbeat, or None before its first one. The age counts from
+        the moment THIS rank first read the current value (its own clock), not from the writer's time stamp."""
         key = self._key("hb", rank)
         if not self.store.check([key]):
             return None
-        step, stamp = self.store.get(key).decode().split(":")
-        return int(step), self.clock() - float(stamp)
+        raw = self.store.get(key).decode()
+        now = self.clock()
+        seen = self._seen.get(rank)
+        if seen is None or seen[0] != raw:
+            seen = self._seen[rank] = (raw, now)
+        return int(raw.split(":")[0]), now - seen[1]
 
-    def check(self) -> None:
-        """Raise `PeerFailure` if a peer announced a failure or has been silent for longer than the limit."""
+    def check(self, ages: bool = True) -> None:
+        """Raise `PeerFailure` if a peer announced a failure or (`ages`) has been silent for longer than the
+        limit."""
         for r in range(self.world):
             if r == self.rank:
                 continue
             fkey = self._key("failed", r)
             if self.store.check([fkey]):
                 raise PeerFailure(r, f"reported a failure: {self.store.get(fkey).decode()}")
+            if not ages:
+                continue
             st = self.peer_state(r)
             if st is not None and self.timeout > 0 and st[1] > self.timeout:
                 raise PeerFailure(r, f"sent no heartbeat for {st[1]:.1f} s (limit {self.timeout:.1f} s, last step {st[0]})")
@@ -80,11 +104,15 @@ class Heartbeat:
     def enter_step(self, step: int, poll_s: float = 0.02) -> None:
         """Rendezvous on the host before a step: publish "I am about to run `step`" and wait until every
         peer has published the same (or a later) step. A peer that died or stalled after its last heartbeat
-        never does, so this raises `PeerFailure` after the limit, before anything is launched."""
+        never does, so this raises `PeerFailure` after the limit, before anything is launched.
+        Liveness is judged by this rendezvous alone (and by announced failures), not by heartbeat ages: set-up,
+        evaluation or a checkpoint between two steps may take longer than the limit on every rank, and a
+        healthy peer that is still busy with them simply arrives late, within the limit counted from now."""
+        self.beat(self.last_step)
         self.store.set(self._key("enter", self.rank), str(step))
         t0 = self.clock()
         while True:
-            self.check()
+            self.check(ages=False)
             late = []
             for r in range(self.world):
                 if r == self.rank:

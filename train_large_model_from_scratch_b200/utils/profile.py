@@ -50,9 +50,11 @@ def get_gpu_peak_flops(dtype: str = "bf16", per_device: bool = True, gpu_name: s
 
 
 def get_measured_peak_flops(path: str | None = None, sustained: bool = True) -> float | None:
-    """bf16 GEMM throughput measured on this machine's GPUs, if a peaks file
-    (JSON with `bf16_tflops[_sustained]`) is available; else None."""
-    path = path or os.environ.get("TLM_MEASURED_PEAKS", "MEASURED_PEAKS.json")
+    """bf16 GEMM throughput measured on this machine's GPUs, if a peaks file (JSON with
+    `bf16_tflops[_sustained]`) is named by `path` or by the `TLM_MEASURED_PEAKS` environment variable; else None."""
+    path = path or os.environ.get("TLM_MEASURED_PEAKS")
+    if not path:
+        return None
     try:
         with open(path) as f:
             d = json.load(f)
