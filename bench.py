@@ -96,7 +96,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -168,6 +168,16 @@ def _timed(torch, dist, world, fn, steps):
     return float(ms.item()), wall
 
 
+def _steps_for(torch, dist, world, fn, steps: int, min_timed_s: float) -> int:
+    """Number of timed steps: `steps`, raised (to at most 400) so that the timed region lasts `min_timed_s`
+    seconds: configurations with short steps otherwise finish between two clock samples. All ranks agree."""
+    if min_timed_s <= 0:
+        return steps
+    ms, _ = _timed(torch, dist, world, fn, 2)
+    need = int(min_timed_s * 1e3 / max(ms / 2, 1e-3)) + 1
+    return max(steps, min(need, 400))
+
+
 def _flags(n_gpus: int, steps_total: int, log_dir: str) -> list[str]:
     dp = n_gpus // SEP_SIZE
     tokens = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * dp
@@ -217,7 +227,7 @@ def run_ours(args) -> dict:
     if not torch.cuda.is_available():                  # the CPU path runs, but it is the oracle, not the benchmark
         raise SystemExit("bench.py measures the sm_100a kernels: no CUDA device is visible")
     log_dir = tempfile.mkdtemp(prefix="tlm_bench_")
-    cfg = build_config(parse_args(_flags(n, 2 * (K + W), log_dir)))
+    cfg = build_config(parse_args(_flags(n, 2 * (K + W) + 900, log_dir)))
     trainer = Trainer(cfg)
     dev = trainer.device
     tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * (n // SEP_SIZE)
@@ -240,6 +250,7 @@ def run_ours(args) -> dict:
     for i in range(W):
         step_device(i)
     native.raise_on_device_status()
+    K = _steps_for(torch, dist, world, step_device, K, args.min_timed_s)
     sampler = ClockSampler(_visible_gpu_index(local_rank))
     sampler.start()
     native.reset_launch_count()
@@ -292,32 +303,66 @@ def run_reference(args) -> dict:
 
     n, K, W = args.gpus, args.steps, args.warmup
     log_dir = tempfile.mkdtemp(prefix="ref_bench_")
-    flags = [f for f in _flags(n, 2 * (K + W), log_dir)]
-    if args.ref_compile:
-        flags.append("--use_compile")
-    cfg = build_config(parse_args(flags))
-    trainer = Trainer(cfg)
-    if cfg.model.use_moe and args.moe_fallback:
-        for blk in trainer.raw_model.blocks:
-            blk.mlp.grouped_gemm_supported = False
-    # what Trainer.train() does before and inside its loop (training/trainer.py:308-351)
-    trainer.results = {}
-    trainer.train_loader_iter = enumerate(trainer.train_loader)
-    trainer.start_step = 0
-    trainer._init_profiler(cfg)
+    flags = [f for f in _flags(n, 2 * (K + W) + 500, log_dir)]
+    state = {}
+
+    def build(use_compile: bool):
+        cfg = build_config(parse_args(flags + (["--use_compile"] if use_compile else [])))
+        trainer = Trainer(cfg)
+        if cfg.model.use_moe and args.moe_fallback:
+            for blk in trainer.raw_model.blocks:
+                blk.mlp.grouped_gemm_supported = False
+        # what Trainer.train() does before and inside its loop (training/trainer.py:308-351)
+        trainer.results = {}
+        trainer.train_loader_iter = enumerate(trainer.train_loader)
+        trainer.start_step = 0
+        trainer._init_profiler(cfg)
+        state.update(cfg=cfg, trainer=trainer, compiled=use_compile)
+
     tokens_per_step = SEQ_LEN * MICRO_BATCH * GRAD_ACCUM * (n // SEP_SIZE)
     counter = {"i": 0}
     losses = []
 
     def step(i):
+        trainer = state["trainer"]
         trainer.one_step_results = {}
-        trainer._one_training_step(cfg, counter["i"])
+        trainer._one_training_step(state["cfg"], counter["i"])
         torch.cuda.synchronize()
         losses.append(trainer.one_step_results["loss"].item())
         counter["i"] += 1
 
-    for i in range(W):
+    # The reference's launch scripts run it with its tracing compiler on (USE_COMPILE=1 ->
+    # `--use_compile`, scripts/debug_gpt_0.25b/pretrain.sh:43,79-81), which is also its faster mode on this
+    # hardware, so that is the mode measured; if the compiler cannot run here, its eager mode is measured
+    # and the reason is reported.
+    compile_note = None
+    build(bool(args.ref_compile))
+    try:
+        step(0)
+    except Exception as e:
+        if not args.ref_compile:
+            raise
+        compile_note = f"{type(e).__name__}: {str(e).splitlines()[0][:160] if str(e) else ''}"
+        ok = torch.tensor([0], device="cuda")
+    else:
+        ok = torch.tensor([1], device="cuda")
+    if args.ref_compile:
+        if world > 1:
+            try:
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            except Exception:
+                ok.zero_()
+        if int(ok.item()) == 0:                        # every rank falls back together
+            dist.destroy_process_group()
+            state.clear()
+            counter["i"] = 0
+            losses.clear()
+            build(False)
+            step(0)
+    cfg, trainer = state["cfg"], state["trainer"]
+    for i in range(max(0, W - 1)):
         step(i)
+    K = _steps_for(torch, dist, world, step, K, args.min_timed_s)
     sampler = ClockSampler(_visible_gpu_index(local_rank))
     sampler.start()
     ms, _ = _timed(torch, dist, world, step, K)
@@ -325,7 +370,9 @@ def run_reference(args) -> dict:
     h2d = 2 * GRAD_ACCUM * MICRO_BATCH * (SEQ_LEN // SEP_SIZE) * 8
     extra = {"e2e": {"value": tokens_per_step / (ms / K / 1e3), "unit": "tokens/s", "ms_per_step": ms / K,
                      "h2d_bytes_per_step": h2d * n, "d2h_bytes_per_step": 4 * n},
-             "gpu_launches": None, "final_loss": losses[-1], "use_compile": bool(args.ref_compile)}
+             "gpu_launches": None, "final_loss": losses[-1], "use_compile": bool(state["compiled"])}
+    if compile_note:
+        extra["compile_fallback"] = compile_note
     if cfg.model.use_moe:
         extra["moe_expert_path"] = ("padded bmm (grouped_gemm_supported forced off: its grouped_mm call needs "
                                     "moe_intermediate_size == hidden_size)" if args.moe_fallback else "grouped_mm")
@@ -347,7 +394,7 @@ def _free_port() -> int:
 
 EXTRAS = (("moe", "D"), ("ulysses", "C"))
 _KEEP = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "impl", "config", "clocks", "e2e", "gpu_launches",
-         "final_loss", "use_compile", "unavailable", "moe_expert_path")
+         "final_loss", "use_compile", "compile_fallback", "unavailable", "moe_expert_path")
 
 
 def run_extras(args) -> dict:
@@ -363,7 +410,7 @@ def run_extras(args) -> dict:
     for key, cfg in EXTRAS:
         tail = [os.path.join(ROOT, "bench.py"), "--gpus", str(args.gpus), "--steps", str(steps), "--warmup", str(args.warmup),
                 "--config", cfg, "--impl", args.impl, "--no-extras", "--ref-compile", str(args.ref_compile),
-                "--moe-fallback", str(args.moe_fallback)]
+                "--moe-fallback", str(args.moe_fallback), "--min-timed-s", "3"]
         if args.gpus > 1:
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                    "--master-addr", "127.0.0.1", "--master-port", str(_free_port())] + tail
@@ -400,8 +447,12 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ref-compile", type=int, default=0,
-                    help="reference arm: pass --use_compile to the reference (its CLI default is off)")
+    ap.add_argument("--ref-compile", type=int, default=1,
+                    help="reference arm: pass --use_compile to the reference, as its launch scripts do (1, default; "
+                         "falls back to eager if its compiler cannot run) or run it eagerly (0)")
+    ap.add_argument("--min-timed-s", type=float, default=0.0,
+                    help="raise --steps so that the timed region lasts at least this long (used for the extra "
+                         "configurations, whose steps are short)")
     ap.add_argument("--config", default="B", choices=["B"] + sorted(CONFIGS),
                     help="B (default) is the headline configuration; see CONFIGS for the others")
     ap.add_argument("--moe-fallback", type=int, default=1,

@@ -77,23 +77,29 @@ def main():
     st = lambda: torch.cuda.current_stream().cuda_stream
     vp = lambda x: ctypes.c_void_p(x) if x else None
 
-    def rs(mc, bf16):
+    def rs(mc, bf16, blocks=0):
         epoch[0] += 1
         if bf16:
             native._check(native.lib().tlm_reduce_scatter_bf16(
-                grads.data_ptr(), wire.data_ptr(), n, pw.ptr_array, vp(pw.mc_ptr if mc else 0), pf.ptr_array,
-                out.data_ptr(), partials.data_ptr(), sumsq.data_ptr(), lo, shard, rank, world, epoch[0], st()), "rs_bf16")
+                grads.data_ptr(), wire.data_ptr(), 0, n, pw.ptr_array, vp(pw.mc_ptr if mc else 0), pf.ptr_array,
+                out.data_ptr(), partials.data_ptr(), sumsq.data_ptr(), lo, shard, rank, world, epoch[0], blocks, st()),
+                "rs_bf16")
         else:
             native._check(native.lib().tlm_reduce_scatter(
                 pg.ptr_array, vp(pg.mc_ptr if mc else 0), pf.ptr_array, out.data_ptr(), partials.data_ptr(),
-                sumsq.data_ptr(), lo, shard, rank, world, epoch[0], st()), "rs")
+                sumsq.data_ptr(), lo, shard, rank, world, epoch[0], blocks, st()), "rs")
+
+    ready = symm_alloc(native.lib().tlm_ready_ints(), torch.int32, dev)
+    pr = _Peer(ready, group)
 
     def ag(mc):
+        # the update kernel publishes "parameters ready"; the one-warp wait that follows is what the first reader
+        # of the parameters does (in training: the producer warp of the first GEMM of the next forward pass)
         native._check(native.lib().tlm_adamw_gather(
             master.data_ptr(), m.data_ptr(), v.data_ptr(), out.data_ptr(), pp.ptr_array, vp(pp.mc_ptr if mc else 0),
-            scale.data_ptr(), lo, shard, rank, world, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1.0, 1.0, None, st()), "adamw_gather")
-        epoch[0] += 1
-        native._check(native.lib().tlm_peer_barrier(pf.ptr_array, rank, world, epoch[0], st()), "barrier")
+            scale.data_ptr(), lo, shard, rank, world, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1.0, 1.0, None, pr.ptr_array, 0, st()),
+            "adamw_gather")
+        native._check(native.lib().tlm_wait_params_ready(ready.data_ptr(), 0, world, st()), "wait_params_ready")
 
     has_mc = bool(pg.mc_ptr)
     cases = []
@@ -103,6 +109,8 @@ def main():
             el = 2 if bf16 else 4
             wire_bytes = shard * el * (1 if mc else (world - 1))
             cases.append((f"reduce_scatter {'bf16' if bf16 else 'fp32'} wire, {tag}", lambda mc=mc, bf16=bf16: rs(mc, bf16), wire_bytes))
+        cases.append((f"reduce_scatter fp32 wire, {tag}, 48 blocks (the grid used under the backward pass)",
+                      lambda mc=mc: rs(mc, False, 48), shard * 4 * (1 if mc else (world - 1))))
         cases.append((f"adamw + all-gather (bf16 params), {tag}", lambda mc=mc: ag(mc), shard * 2 * (1 if mc else (world - 1))))
     nccl_out = torch.empty(shard, device=dev)
     cases.append(("nccl reduce_scatter_tensor fp32", lambda: dist.reduce_scatter_tensor(nccl_out, grads), shard * 4 * (world - 1)))

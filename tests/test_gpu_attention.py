@@ -49,3 +49,50 @@ def test_flash_bwd(B, T, Hq, Hkv, hd):
         a, b = dqkv[:, :, sl].float(), x.grad[:, :, sl]
         rel = ((a - b).norm() / b.norm()).item()
         assert rel < 2e-2, (name, rel)
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 64), (1, 384, 2, 1, 128), (2, 320, 8, 2, 32), (1, 200, 4, 4, 64)])
+@pytest.mark.parametrize("variant", ["reference", "standard"])
+def test_flash_bwd_with_transposed_rope_on_the_way_out(B, T, Hq, Hkv, hd, variant):
+    """`rope=(cos, sin)`: dQ and dK come back as gradients of the UN-rotated heads. Oracle: the fp32 autograd
+    gradient of the rotated heads pushed through the transposed rotation in fp32."""
+    from train_large_model_from_scratch_b200.ops import native, oracle
+    torch.manual_seed(3)
+    qkv = torch.randn(B, T, Hq + 2 * Hkv, hd, device="cuda").to(torch.bfloat16)
+    do = torch.randn(B, T, Hq, hd, device="cuda").to(torch.bfloat16)
+    cos, sin = oracle.rope_tables(torch.arange(T, device="cuda"), hd, 10000.0, variant)
+    o, lse = native.flash_attn_fwd(qkv, Hq, Hkv, True)
+    dqkv = native.flash_attn_bwd(do, qkv, o, lse, Hq, Hkv, True, rope=(cos.contiguous(), sin.contiguous()))
+    native.raise_on_device_status()
+    x = qkv.float().requires_grad_()
+    _ref(x, Hq, Hkv).backward(do.float())
+    ref = x.grad.clone()
+    ref[:, :, :Hq + Hkv] = oracle.rope_bwd(x.grad[:, :, :Hq + Hkv], cos, sin)
+    for name, sl in (("dq", slice(0, Hq)), ("dk", slice(Hq, Hq + Hkv)), ("dv", slice(Hq + Hkv, None))):
+        a, b = dqkv[:, :, sl].float(), ref[:, :, sl]
+        rel = ((a - b).norm() / b.norm()).item()
+        assert rel < 2e-2, (name, rel)
+
+
+def test_flash_fwd_bwd_at_the_headline_shape():
+    """B = 8, T = 4096, 16 query / 8 KV heads of 64 (the benchmark's attention shape: 128 (batch, head) pairs,
+    32 KV tiles): the kernels run on the whole batch, the fp32 oracle one batch entry at a time."""
+    from train_large_model_from_scratch_b200.ops import native
+    B, T, Hq, Hkv, hd = 8, 4096, 16, 8, 64
+    torch.manual_seed(4)
+    qkv = (torch.randn(B, T, Hq + 2 * Hkv, hd, device="cuda") * 0.7).to(torch.bfloat16)
+    do = torch.randn(B, T, Hq, hd, device="cuda").to(torch.bfloat16)
+    o, lse = native.flash_attn_fwd(qkv, Hq, Hkv, True)
+    dqkv = native.flash_attn_bwd(do, qkv, o, lse, Hq, Hkv, True)
+    native.raise_on_device_status()
+    for b in (0, 3, 7):
+        x = qkv[b:b + 1].float().requires_grad_()
+        ref = _ref(x, Hq, Hkv)
+        assert (o[b:b + 1].float() - ref).abs().max().item() < 2e-2
+        ref.backward(do[b:b + 1].float())
+        for name, sl in (("dq", slice(0, Hq)), ("dk", slice(Hq, Hq + Hkv)), ("dv", slice(Hq + Hkv, None))):
+            a, g = dqkv[b:b + 1, :, sl].float(), x.grad[:, :, sl]
+            rel = ((a - g).norm() / g.norm()).item()
+            assert rel < 2e-2, (b, name, rel)
+        del x, ref
+        torch.cuda.empty_cache()

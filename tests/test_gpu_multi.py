@@ -91,3 +91,27 @@ def test_expert_parallel_peer_path_matches_nccl_path_and_single_group():
     _close(ref["losses"], peer["losses"], 3e-3)
     _close(ref["losses"], dp["losses"], 5e-3)
     _close(ref["norms"], peer["norms"], 3e-2)
+
+
+WIDE = [f if FLAGS[i - 1] not in ("--num_attention_heads", "--num_key_value_heads") else "8" for i, f in enumerate(FLAGS)]
+
+
+@pytest.mark.parametrize("world,sep,batch", [(4, 4, 4), (4, 2, 2), (8, 8, 8), (8, 2, 2)])
+def test_larger_groups_match_the_nccl_path(world, sep, batch):
+    """The peer-memory paths (optimizer collectives, Ulysses exchanges in the GEMM / attention epilogues) at
+    4 and 8 ranks, pure sequence parallelism and DP x SEP grids, against the library-collective path with the
+    same layout. 8 query / 8 KV heads so that every rank owns whole heads at sep = 8."""
+    flags = [f if FLAGS[i - 1] != "--batch_size" else str(batch) for i, f in enumerate(WIDE)] + ["--sep_size", str(sep)]
+    ref = _run(world, {"TLM_COMM": "nccl"}, flags)
+    peer = _run(world, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags)
+    _close(ref["losses"], peer["losses"], 3e-3)
+    _close(ref["norms"], peer["norms"], 3e-2)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_expert_parallel_at_larger_groups(world):
+    flags = [f if FLAGS[i - 1] != "--batch_size" else str(world) for i, f in enumerate(WIDE)]
+    ref = _run(world, {"TLM_COMM": "nccl"}, flags + MOE + ["--sep_size", str(world)])
+    peer = _run(world, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags + MOE + ["--sep_size", str(world)])
+    _close(ref["losses"], peer["losses"], 3e-3)
+    _close(ref["norms"], peer["norms"], 3e-2)

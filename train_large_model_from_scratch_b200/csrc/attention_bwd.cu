@@ -39,6 +39,11 @@ struct AttnBwdParams {
   float scale, scale_log2;
   unsigned int* status;
   int hd;                   // head dim in memory; 32 runs on the HD = 64 kernel with zero-filled upper columns
+  // Optional transposed RoPE on the way out: with tables cos / sin [T, hd] (fp32, row = position) the kernels
+  // return the gradient of the UN-rotated q and k, i.e. dx[j] = dy[j] c[j] + dy[j+h] s[j+h] and
+  // dx[j+h] = dy[j+h] c[j+h] - dy[j] s[j] (h = hd / 2) applied in fp32 while dQ / dK are still unrounded.
+  const float* cosT;
+  const float* sinT;
 };
 
 template <int HD>
@@ -115,20 +120,48 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   }
 }
 
+// dq_acc (fp32 [B, Hq, T, hd]) * scale -> bf16 q-head slots of dqkv, 8 low columns and their 8 partner columns
+// (j + hd / 2) per thread so that the transposed rotation (see AttnBwdParams) can be applied on the way.
 __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int B, int T,
-                                       int Hq, int heads_total, int hd, float scale) {
-  const int vec = hd / 8;
+                                       int Hq, int heads_total, int hd, float scale, const float* __restrict__ cosT,
+                                       const float* __restrict__ sinT) {
+  const int half = hd / 2, vec = half / 8;
   const long long total = (long long)B * Hq * T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(i % vec);
+    const int j = (int)(i % vec) * 8;
     long long r = i / vec;
     const int t = (int)(r % T); r /= T;
     const int h = (int)(r % Hq); const long long b = r / Hq;
-    const float4 a = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8);
-    const float4 c = *reinterpret_cast<const float4*>(dq_acc + (i - v) * 8 + v * 8 + 4);
-    uint4 out = make_uint4(pack_bf16(a.x * scale, a.y * scale), pack_bf16(a.z * scale, a.w * scale),
-                           pack_bf16(c.x * scale, c.y * scale), pack_bf16(c.z * scale, c.w * scale));
-    *reinterpret_cast<uint4*>(dqkv + ((b * T + t) * heads_total + h) * (long long)hd + v * 8) = out;
+    const float* src = dq_acc + (((long long)b * Hq + h) * T + t) * hd + j;
+    float lo[8], hi[8];
+    *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
+    *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + half);
+    *reinterpret_cast<float4*>(hi + 4) = *reinterpret_cast<const float4*>(src + half + 4);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { lo[k] *= scale; hi[k] *= scale; }
+    if (cosT != nullptr) {
+      const float* c = cosT + (long long)t * hd + j;
+      const float* sn = sinT + (long long)t * hd + j;
+      float cl[8], ch[8], sl[8], sh[8];
+      *reinterpret_cast<float4*>(cl) = *reinterpret_cast<const float4*>(c);
+      *reinterpret_cast<float4*>(cl + 4) = *reinterpret_cast<const float4*>(c + 4);
+      *reinterpret_cast<float4*>(ch) = *reinterpret_cast<const float4*>(c + half);
+      *reinterpret_cast<float4*>(ch + 4) = *reinterpret_cast<const float4*>(c + half + 4);
+      *reinterpret_cast<float4*>(sl) = *reinterpret_cast<const float4*>(sn);
+      *reinterpret_cast<float4*>(sl + 4) = *reinterpret_cast<const float4*>(sn + 4);
+      *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(sn + half);
+      *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(sn + half + 4);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float a = lo[k], bb = hi[k];
+        lo[k] = a * cl[k] + bb * sh[k];
+        hi[k] = bb * ch[k] - a * sl[k];
+      }
+    }
+    __nv_bfloat16* dst = dqkv + ((b * T + t) * heads_total + h) * (long long)hd + j;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
+    *reinterpret_cast<uint4*>(dst + half) = make_uint4(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]), pack_bf16(hi[4], hi[5]), pack_bf16(hi[6], hi[7]));
   }
 }
 
@@ -324,31 +357,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       if (!mbar_wait(bar(5), par, 28, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       uint32_t pp[32], dd[32];                      // 64 columns of P and dS, packed bf16 pairs
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(t_lane + C::S_COL + half * 64 + c, s);
-        tmem_ld32(t_lane + C::DP_COL + half * 64 + c, dp);
+      {
+        // This thread's 64 columns of S and of dP move into registers in one pass and the tensor-memory columns
+        // are handed back BEFORE the arithmetic: the MMA warp issues S / dP of the next step as soon as the loads
+        // have landed, so those MMAs run under this step's exp / dS work instead of after it.
+        uint32_t s[64], dp[64];
+        tmem_ld32(t_lane + C::S_COL + half * 64, s);
+        tmem_ld32(t_lane + C::S_COL + half * 64 + 32, s + 32);
+        tmem_ld32(t_lane + C::DP_COL + half * 64, dp);
+        tmem_ld32(t_lane + C::DP_COL + half * 64 + 32, dp + 32);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(6));         // S / dP columns may be overwritten
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int i = 0; i < 64; i += 2) {
           const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
           float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (diag) {
-            const int col = half * 64 + c + i;
+            const int col = half * 64 + i;
             if (col > row) pr.x = 0.f;
             if (col + 1 > row) pr.y = 0.f;
           }
           // dS = P (dP - delta); the softmax scale is applied once, when dQ and dK leave their accumulators
           const float2 ds = fmul2(pr, fadd2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), nd2));
-          pp[(c + i) >> 1] = pack_bf16(pr.x, pr.y);
-          dd[(c + i) >> 1] = pack_bf16(ds.x, ds.y);
+          pp[i >> 1] = pack_bf16(pr.x, pr.y);
+          dd[i >> 1] = pack_bf16(ds.x, ds.y);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(6));           // S / dP columns may be overwritten
       if (it > 0) {                                 // MMAs of step it-1 done: P / dS free, dQ(it-1) ready
         if (!mbar_wait(bar(8), par ^ 1u, 29, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
@@ -391,6 +428,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             uint32_t r[32];
             tmem_ld32(t_lane + col0 + c, r);
             tmem_ld_wait();
+            // transposed RoPE on dK (fp32): column j pairs with j +- hd / 2. `rot` is warp-uniform (the
+            // tensor-memory load of the partner columns must be executed by the whole warp).
+            const int colg = half * (HD / 2) + c;                      // first of this thread's 32 columns
+            const bool rot = which == 1 && p.cosT != nullptr && colg < p.hd;
+            uint32_t q2[32];
+            if (rot && p.hd == HD) {                                   // partner columns sit in the other half-row
+              tmem_ld32(t_lane + C::DK_COL + (1 - half) * (HD / 2) + c, q2);
+              tmem_ld_wait();
+            }
+            if (rot && t_row < p.T) {
+              const float* cr = p.cosT + (long long)t_row * p.hd;
+              const float* sr = p.sinT + (long long)t_row * p.hd;
+              if (p.hd == HD) {
+                const int pc = (1 - half) * (HD / 2) + c;             // partner's first column
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const float a = __uint_as_float(r[i]), bb = __uint_as_float(q2[i]);
+                  r[i] = __float_as_uint(half == 0 ? a * cr[colg + i] + bb * sr[pc + i] : a * cr[colg + i] - bb * sr[pc + i]);
+                }
+              } else {                                                // hd 32 on the 64-wide kernel: both halves are in r
+                float o[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const float a = __uint_as_float(r[i]), bb = __uint_as_float(r[i + 16]);
+                  o[i] = a * cr[i] + bb * sr[i + 16];
+                  o[i + 16] = bb * cr[i + 16] - a * sr[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(o[i]);
+              }
+            }
             if (t_row < p.T && half * (HD / 2) + c < p.hd) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -435,9 +503,10 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUten
 using namespace tlm;
 
 // dq_acc: fp32 scratch [B,Hq,T,hd]; delta: fp32 scratch [B,Hq,T]. Both are owned by the caller.
+// cosT / sinT (optional, fp32 [T, hd]): the transposed RoPE is applied to dQ and dK on the way out.
 TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
                          float* dq_acc, float* delta, int B, int T, int Hq, int Hkv, int hd, float scale,
-                         cudaStream_t st) {
+                         const float* cosT, const float* sinT, cudaStream_t st) {
   if (hd != 32 && hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
   const long long rows = (long long)B * T * Hq;
@@ -452,7 +521,9 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   if (e) return e;
   e = make_qkv_map(&mdo, dout, B, T, Hq, hd, AB_TILE);
   if (e) return e;
-  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word(), hd};
+  if ((cosT == nullptr) != (sinT == nullptr)) return -6;
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word(), hd,
+                  cosT, sinT};
   CUtensorMap mdq;                                     // fp32 [B*Hq, T, hd] accumulator, box 32 x 32 x 1
   {
     uint64_t dims[3] = {(uint64_t)hd, (uint64_t)T, (uint64_t)B * Hq};
@@ -463,10 +534,10 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   }
   e = hd == 128 ? launch_bwd<128>(mq, mdo, mdq, p, st) : launch_bwd<64>(mq, mdo, mdq, p, st);
   if (e) return e;
-  long long items = rows * (hd / 8);
+  long long items = rows * (hd / 16);
   int cb = (int)((items + 255) / 256);
   if (cb > num_sms() * 16) cb = num_sms() * 16;
-  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale);
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale, cosT, sinT);
   count_launch();
   return launch_status();
 }

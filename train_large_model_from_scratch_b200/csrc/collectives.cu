@@ -26,15 +26,6 @@ struct PeerPtrs {
   void* p[MAX_PEERS];
 };
 
-__device__ __forceinline__ void st_release_sys(int* addr, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
-
 // Threads 0..n-1 of the calling block: (optionally) publish `epoch` to every
 // peer, then wait until every peer has published it here. Returns false on timeout.
 __device__ __forceinline__ bool flag_exchange(const PeerPtrs& flags, int rank, int n, int epoch, bool do_signal,
@@ -249,7 +240,7 @@ __global__ void adamw_gather_kernel(float* __restrict__ p, float* __restrict__ m
                                     const float* __restrict__ g, PeerPtrs params, __nv_bfloat16* mc_params,
                                     const float* __restrict__ scale_ptr, long long lo, long long len, int rank, int n,
                                     float lr, float beta1, float beta2, float eps, float wd, float inv_bc1,
-                                    float inv_sqrt_bc2, const float* __restrict__ hyper) {
+                                    float inv_sqrt_bc2, const float* __restrict__ hyper, PeerPtrs ready, int bucket) {
   if (hyper != nullptr) { lr = hyper[0]; inv_bc1 = hyper[1]; inv_sqrt_bc2 = hyper[2]; }   // per-step values from device memory
   const float scale = *scale_ptr;
   const long long nvec = len / 8;
@@ -289,6 +280,30 @@ __global__ void adamw_gather_kernel(float* __restrict__ p, float* __restrict__ m
       }
     }
   }
+  if (ready.p[0] != nullptr) {
+    // "parameters of this bucket are ready" to every rank, once the LAST block has stored its part: every
+    // thread fences its own (peer / multicast) stores, the block's arrival is counted, and the block that
+    // completes the count publishes the new update count with release stores at system scope.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* mine = reinterpret_cast<int*>(ready.p[rank]);
+      const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int*>(mine + READY_CNT0 + bucket), 1u);
+      if (prev == gridDim.x - 1) {
+        mine[READY_CNT0 + bucket] = 0;
+        __threadfence_system();
+        const int done = reinterpret_cast<volatile int*>(mine)[READY_EPOCH0 + bucket] + 1;
+        for (int r = 0; r < n; ++r) st_release_sys(reinterpret_cast<int*>(ready.p[r]) + bucket * READY_STRIDE + rank, done);
+        reinterpret_cast<volatile int*>(mine)[READY_EPOCH0 + bucket] = done;
+      }
+    }
+  }
+}
+
+// One warp: wait until every rank's update of `bucket` has arrived here (see READY_* in common.cuh). Queued at the
+// top of a step in front of the first kernels that read parameters no GEMM waits for itself (embedding, norms).
+__global__ void wait_params_ready_kernel(const int* ready_local, int bucket, int n, unsigned int* status) {
+  wait_params_ready(ready_local, bucket, n, (int)threadIdx.x, status, 46);
 }
 
 }  // namespace tlm
@@ -319,12 +334,29 @@ TLM_API int tlm_wait_flag(const int* flag, int expect, unsigned long long limit_
 
 TLM_API int tlm_reduce_scatter_blocks() { return 4 * num_sms(); }
 
+// Grid of a reduce-scatter launch: all of it by default; `max_blocks` > 0 caps it (a bucket that is reduced
+// while the backward pass still runs should leave the SMs to the GEMMs: a few dozen blocks keep NVLink busy).
+static int rs_grid(int max_blocks) {
+  const int full = tlm_reduce_scatter_blocks();
+  return (max_blocks > 0 && max_blocks < full) ? max_blocks : full;
+}
+
+TLM_API int tlm_ready_ints() { return READY_INTS; }
+TLM_API int tlm_ready_max_buckets() { return READY_MAX_BUCKETS; }
+
+TLM_API int tlm_wait_params_ready(const int* ready_local, int bucket, int n, cudaStream_t st) {
+  if (ready_local == nullptr || bucket < 0 || bucket >= READY_MAX_BUCKETS || n < 1 || n > READY_STRIDE) return -6;
+  wait_params_ready_kernel<<<1, 32, 0, st>>>(ready_local, bucket, n, status_word());
+  count_launch();
+  return launch_status();
+}
+
 // partials: >= tlm_reduce_scatter_blocks() floats; sumsq_out: 1 float.
 TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, void* const* flag_ptrs, float* out,
                                float* partials, float* sumsq_out, long long lo, long long len, int rank, int n,
-                               int epoch, cudaStream_t st) {
+                               int epoch, int max_blocks, cudaStream_t st) {
   if (n > MAX_PEERS || len % 4 != 0 || lo % 4 != 0) return -6;
-  const int blocks = tlm_reduce_scatter_blocks();
+  const int blocks = rs_grid(max_blocks);
   reduce_scatter_kernel<<<blocks, 512, 0, st>>>(to_ptrs(grad_ptrs, n), mc_grads, to_ptrs(flag_ptrs, n), out, partials, lo,
                                                 len, rank, n, epoch, status_word());
   sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
@@ -332,17 +364,19 @@ TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, vo
   return launch_status();
 }
 
-// bf16 wire: `grads` (this rank's fp32 buffer, n elements) is rounded into `wire_local` (this rank's symmetric
-// bf16 buffer), then the slice [lo, lo+len) is summed over all ranks' wire buffers into `out` (fp32).
-TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long long n_total, void* const* wire_ptrs,
-                                    const void* mc_wire, void* const* flag_ptrs, float* out, float* partials,
-                                    float* sumsq_out, long long lo, long long len, int rank, int n, int epoch,
-                                    cudaStream_t st) {
-  if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0 || n_total % 8 != 0) return -6;
-  long long cb = (n_total / 8 + 255) / 256;
-  if (cb > 8LL * num_sms()) cb = 8LL * num_sms();
-  cast_bf16_kernel<<<(int)(cb < 1 ? 1 : cb), 256, 0, st>>>(grads, (__nv_bfloat16*)wire_local, n_total);
-  const int blocks = tlm_reduce_scatter_blocks();
+// bf16 wire: elements [cast_lo, cast_lo + cast_n) of `grads` (this rank's fp32 buffer) are rounded into the same
+// elements of `wire_local` (this rank's symmetric bf16 buffer; the range is the bucket every rank is about to
+// reduce), then the slice [lo, lo+len) is summed over all ranks' wire buffers into `out` (fp32).
+TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long long cast_lo, long long cast_n,
+                                    void* const* wire_ptrs, const void* mc_wire, void* const* flag_ptrs, float* out,
+                                    float* partials, float* sumsq_out, long long lo, long long len, int rank, int n,
+                                    int epoch, int max_blocks, cudaStream_t st) {
+  if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0 || cast_n % 8 != 0 || cast_lo % 8 != 0) return -6;
+  long long cb = (cast_n / 8 + 255) / 256;
+  const long long cap = max_blocks > 0 ? max_blocks : 8LL * num_sms();
+  if (cb > cap) cb = cap;
+  cast_bf16_kernel<<<(int)(cb < 1 ? 1 : cb), 256, 0, st>>>(grads + cast_lo, (__nv_bfloat16*)wire_local + cast_lo, cast_n);
+  const int blocks = rs_grid(max_blocks);
   reduce_scatter_bf16_kernel<<<blocks, 512, 0, st>>>(to_ptrs(wire_ptrs, n), (const __nv_bfloat16*)mc_wire, to_ptrs(flag_ptrs, n),
                                                      out, partials, lo, len, rank, n, epoch, status_word());
   sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
@@ -351,17 +385,22 @@ TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long l
 }
 
 // `hyper` (optional, device, 3 floats: lr, 1/(1-beta1^t), 1/sqrt(1-beta2^t)) overrides the by-value arguments, so
-// that the launch is identical from step to step.
+// that the launch is identical from step to step. `ready_ptrs` (optional: every rank's READY_INTS-word symmetric
+// flag array): the kernel ends by publishing "bucket `bucket` updated" to all ranks (see READY_* in common.cuh).
 TLM_API int tlm_adamw_gather(float* p, float* m, float* v, const float* g, void* const* param_ptrs, void* mc_params,
                              const float* scale, long long lo, long long len, int rank, int n, float lr, float beta1,
                              float beta2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2, const float* hyper,
-                             cudaStream_t st) {
+                             void* const* ready_ptrs, int bucket, cudaStream_t st) {
   if (n > MAX_PEERS || len % 8 != 0 || lo % 8 != 0) return -6;
+  if (ready_ptrs != nullptr && (bucket < 0 || bucket >= READY_MAX_BUCKETS || n > READY_STRIDE)) return -6;
+  PeerPtrs ready{};
+  if (ready_ptrs != nullptr) ready = to_ptrs(ready_ptrs, n);
   long long blocks = (len / 8 + 255) / 256;
   if (blocks > 8LL * num_sms()) blocks = 8LL * num_sms();
   if (blocks < 1) blocks = 1;
   adamw_gather_kernel<<<(int)blocks, 256, 0, st>>>(p, m, v, g, to_ptrs(param_ptrs, n), (__nv_bfloat16*)mc_params, scale, lo,
-                                                   len, rank, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, hyper);
+                                                   len, rank, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, hyper, ready,
+                                                   bucket);
   count_launch();
   return launch_status();
 }

@@ -45,6 +45,25 @@ __device__ __forceinline__ void report_status(unsigned int* status, unsigned int
   if (status != nullptr) atomicCAS_system(status, 0u, code);
 }
 
+// ---- flags in peer-visible memory ----------------------------------------------------
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// "Parameters ready" flags of the sharded optimizer step (one symmetric int32 array of READY_INTS words per flat
+// buffer). Word [bucket * READY_STRIDE + r] of a rank's array is written by rank r, into every rank's copy, once
+// all of r's parameter stores of that bucket's update have been issued and fenced; it holds the number of updates
+// done so far. Words READY_EPOCH0 + bucket (how many updates this rank itself has done: the value consumers wait
+// for) and READY_CNT0 + bucket (blocks-finished counter of the update kernel) are only used locally.
+constexpr int READY_STRIDE = 16, READY_MAX_BUCKETS = 16;
+constexpr int READY_EPOCH0 = READY_STRIDE * READY_MAX_BUCKETS, READY_CNT0 = READY_EPOCH0 + READY_MAX_BUCKETS;
+constexpr int READY_INTS = 512;
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -101,6 +120,27 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // microsecond, which on a wait that sits on a pipeline's critical path (and
 // almost every wait fails its first poll) is more than the work between waits.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;            // 2 s (flag waits on peers, timed with %globaltimer)
+
+// Lanes 0..n-1 of the calling warp wait (bounded) until every rank's "parameters ready" word of `bucket` has
+// reached this rank's own update count. Returns false on the lanes that gave up (status `site << 8 | rank`).
+__device__ __forceinline__ bool wait_params_ready(const int* ready_local, int bucket, int n, int lane,
+                                                  unsigned int* status, unsigned int site) {
+  bool ok = true;
+  if (lane < n) {
+    const int expect = reinterpret_cast<const volatile int*>(ready_local)[READY_EPOCH0 + bucket];
+    const int* f = ready_local + bucket * READY_STRIDE + lane;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int)(ld_acquire_sys(f) - expect) < 0) {
+      if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        report_status(status, (site << 8) | (unsigned int)lane);
+        ok = false;
+        break;
+      }
+    }
+  }
+  return ok;
+}
 constexpr long long kWaitLimitCycles = 4000000000ll;        // ~2-3 s of SM cycles
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int site,
                                           volatile int* abort_flag, unsigned int* status) {

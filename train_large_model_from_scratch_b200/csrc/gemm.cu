@@ -90,7 +90,27 @@ struct GemmParams {
   const long long* rs_row;
   void* rs_dst[MAX_HEAD_DST];
   long long rs_rows;        // rows of a destination buffer (stores outside are refused)
+  // "Parameters ready" gate (sharded optimizer, several ranks): before its first TMA load the producer warp waits
+  // until every rank's update of the listed buckets has arrived in this rank's parameter replica (flag words in
+  // symmetric memory, see READY_* in common.cuh). This is where the parameter all-gather of the previous
+  // optimizer step is consumed: the first GEMM that reads a bucket's weights waits for them itself, so no barrier
+  // stands between the optimizer step and the next forward pass. wait_flags[i] == nullptr: no gate.
+  const int* wait_flags[2];
+  int wait_bucket[2], wait_n[2];
 };
+
+// Gates armed by tlm_gemm_arm_param_wait; the next GEMM launch of this library takes them all.
+static struct { const int* flags; int bucket, n; } g_pending_wait[2];
+static int g_n_pending_wait = 0;
+
+static void take_pending_waits(GemmParams& p) {
+  for (int i = 0; i < 2; ++i) {
+    p.wait_flags[i] = i < g_n_pending_wait ? g_pending_wait[i].flags : nullptr;
+    p.wait_bucket[i] = i < g_n_pending_wait ? g_pending_wait[i].bucket : 0;
+    p.wait_n[i] = i < g_n_pending_wait ? g_pending_wait[i].n : 0;
+  }
+  g_n_pending_wait = 0;
+}
 
 struct TileCoord {
   int m0, n0;       // output tile origin (row within C / column)
@@ -187,7 +207,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (p.wait_flags[0] != nullptr) {
+      // weights of this GEMM may still be on their way from the ranks that own their optimizer shards
+      bool ready = true;
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+        if (p.wait_flags[w] != nullptr) ready &= wait_params_ready(p.wait_flags[w], p.wait_bucket[w], p.wait_n[w], lane, p.status, 45);
+      if (!ready) *abort_flag = 1;
+      __syncwarp();
+      asm volatile("fence.proxy.async;" ::: "memory");      // the peers' (generic-proxy) stores before this warp's TMA reads
+    }
+    if (lane == 0 && !*abort_flag) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -778,6 +808,7 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   }
   for (int r = n_dst; r < MAX_HEAD_DST; ++r) dst.m[r] = dst.m[0];
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
   p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
@@ -809,6 +840,7 @@ TLM_API int tlm_gemm_swiglu(const void* x, const void* w_gu, void* gate_up, void
   e = store_map_bf16(&md, act, M, I, I);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
   static bool configured = false;
   if (!configured) {
@@ -838,6 +870,7 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   e = store_map_bf16(&mc, d_gate_up, M, 2LL * I, 2LL * I);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
   p.aux = (const __nv_bfloat16*)gate_up;
   static bool configured = false;
@@ -853,6 +886,20 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   return launch_status();
 }
 
+// Arms a "parameters ready" gate for the NEXT GEMM launched through this library (any entry point): its producer
+// warp waits until all `n` ranks' updates of `bucket` have arrived (`ready_local`: this rank's READY_INTS-word flag
+// array in symmetric memory). Up to two gates can be pending; the launch that takes them clears them.
+TLM_API int tlm_gemm_arm_param_wait(const int* ready_local, int bucket, int n) {
+  if (ready_local == nullptr || bucket < 0 || bucket >= READY_MAX_BUCKETS || n < 1 || n > READY_STRIDE) return -6;
+  if (g_n_pending_wait >= 2) return -7;
+  g_pending_wait[g_n_pending_wait].flags = ready_local;
+  g_pending_wait[g_n_pending_wait].bucket = bucket;
+  g_pending_wait[g_n_pending_wait].n = n;
+  ++g_n_pending_wait;
+  return 0;
+}
+TLM_API void tlm_gemm_clear_param_waits() { g_n_pending_wait = 0; }
+
 // C[M,N] = A * B^T with arbitrary operand majors.
 //   a_mn = 0: A is [M,K] (lda); a_mn = 1: A is [K,M] (lda)
 //   b_mn = 0: B is [N,K] (ldb); b_mn = 1: B is [K,N] (ldb)
@@ -867,6 +914,7 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   p.split_k = 1; p.k_chunk = K;
@@ -912,6 +960,7 @@ TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const i
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -938,6 +987,7 @@ TLM_API int tlm_gemm_grouped_pair(const void* A, const void* W, void* C, const i
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = R; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -962,6 +1012,7 @@ TLM_API int tlm_gemm_grouped_rows_scatter(const void* A, const void* B, const in
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -985,6 +1036,7 @@ TLM_API int tlm_gemm_grouped_k(const void* A, const void* B, void* C, const int*
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
+  take_pending_waits(p);
   p.M = M; p.N = N; p.K = R; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 2; p.c_group_stride = c_group_stride;
   int tiles = groups * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);

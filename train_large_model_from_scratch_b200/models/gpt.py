@@ -55,6 +55,22 @@ class Block(nn.Module):
         return x, m
 
 
+class _GroupBoundary(torch.autograd.Function):
+    """Identity on the residual stream at the entry of a layer group. Its backward runs right after the
+    backward of the group's first block, i.e. when every gradient of the group's parameters has been produced,
+    and tells the optimizer so (`hooks.group_backward_done(g)`), which may then start reducing that bucket."""
+
+    @staticmethod
+    def forward(ctx, x, delta, hooks, g):
+        ctx.hooks, ctx.g = hooks, g
+        return x.view_as(x), (delta.view_as(delta) if delta is not None else None)
+
+    @staticmethod
+    def backward(ctx, gx, gd):
+        ctx.hooks.group_backward_done(ctx.g)
+        return gx, gd, None, None
+
+
 class GPT(nn.Module):
     def __init__(self, config: ModelConfig, device=None, compute_dtype: torch.dtype | None = None,
                  flatten: bool = True, shard_world: int = 1, alloc=None):
@@ -81,9 +97,53 @@ class GPT(nn.Module):
                 seeded_normal((config.vocab_size, config.hidden_size), config.init_std, config.seed, dev))
         self.loss_fn = CrossEntropyLoss()
         self.dense_buf = self.expert_buf = None
+        # communication hooks of the sharded optimizer step (set by the trainer on the peer-memory path): an object
+        # with before_forward(), before_group(g) and group_backward_done(g); `_group_of_block[i] = g` for the
+        # blocks that open a layer group (see `plan_buckets`)
+        self.comm_hooks = None
+        self._group_of_block: dict = {}
         if flatten:
             pad = 1024 * max(1, shard_world)
-            self.dense_buf, self.expert_buf = flatten_model(self, compute_dtype, dev, pad, pad, alloc)
+            # every parameter starts at a multiple of 8 * shard count, so that any parameter boundary can be
+            # a bucket boundary of the optimizer step
+            self.dense_buf, self.expert_buf = flatten_model(self, compute_dtype, dev, pad, pad, alloc,
+                                                            align=8 * max(1, shard_world))
+
+    # ------------------------------------------------------------------ optimizer buckets
+    def plan_buckets(self, target_bytes: int = 192 << 20, max_groups: int = 15):
+        """Cut the flat buffers at layer-group boundaries for the bucketed optimizer step.
+
+        Consecutive blocks form a group until the group holds `target_bytes` of fp32 gradients (at most
+        `max_groups` groups). Group g >= 1 starts at block s_g; the dense buffer is cut at the offset of
+        `blocks[s_g].attn.q_proj.weight` (a group's FIRST norm weight stays in the bucket before it: it is read
+        before the group's first GEMM, which is where the group's parameters are waited for), the expert buffer
+        at `blocks[s_g].mlp.experts_gate_weights`. Bucket 0 of the dense buffer (embedding, first norm) belongs
+        to group 0, whose gradients are only final at the end of the backward pass.
+        Returns `(cuts, bucket_groups)`, each a list with one entry per flat buffer (dense, then expert if
+        present), and records which block opens which group."""
+        dl = self.dense_buf.layout
+        offs = [dl[f"blocks.{i}.attn.q_proj.weight"][0] for i in range(len(self.blocks))] + [self.dense_buf.padded]
+        el = self.expert_buf.layout if self.expert_buf is not None else None
+        starts, acc = [0], 0
+        for i in range(len(self.blocks)):
+            layer = offs[i + 1] - offs[i]
+            if el is not None:
+                nxt = el[f"blocks.{i + 1}.mlp.experts_gate_weights"][0] if i + 1 < len(self.blocks) else self.expert_buf.padded
+                layer += nxt - el[f"blocks.{i}.mlp.experts_gate_weights"][0]
+            acc += 4 * layer
+            if acc >= target_bytes and i + 1 < len(self.blocks):
+                starts.append(i + 1)
+                acc = 0
+        if len(starts) > max_groups:                       # merge evenly
+            per = -(-len(self.blocks) // max_groups)
+            starts = list(range(0, len(self.blocks), per))
+        self._group_of_block = {s: g + 1 for g, s in enumerate(starts)}
+        cuts = [[offs[s] for s in starts]]
+        groups = [[0] + [g + 1 for g in range(len(starts))]]
+        if el is not None:
+            cuts.append([el[f"blocks.{s}.mlp.experts_gate_weights"][0] for s in starts if s > 0])
+            groups.append([g + 1 for g in range(len(starts))])
+        return cuts, groups
 
     # ------------------------------------------------------------------ forward
     def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None, loss_scale: float = 1.0,
@@ -98,10 +158,18 @@ class GPT(nn.Module):
         sp = parallel_state.get_sp_world_size()
         assert T * sp <= self.config.block_size * sp and T <= self.config.block_size, \
             f"Cannot forward sequence of length {T}, block size is only {self.config.block_size}"
+        hooks = self.comm_hooks
+        if hooks is not None:
+            hooks.before_forward()                      # embedding and first norm: wait for their bucket
         x = self.wte(idx)
         delta = None
         aux_total = None
-        for block in self.blocks:
+        for i, block in enumerate(self.blocks):
+            g = self._group_of_block.get(i) if hooks is not None else None
+            if g is not None:
+                hooks.before_group(g)                   # the group's first GEMM waits for the group's parameters
+                if torch.is_grad_enabled():
+                    x, delta = _GroupBoundary.apply(x, delta, hooks, g)
             x, delta = block(x, delta, B, T)
             if self.use_moe and block.mlp.aux_loss is not None:
                 aux_total = block.mlp.aux_loss if aux_total is None else aux_total + block.mlp.aux_loss

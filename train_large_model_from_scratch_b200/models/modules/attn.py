@@ -134,9 +134,8 @@ class Attention(nn.Module):
         if F_ops.qkv_project_fused_ok(h, self._qkv_weight, hd, T_local):
             # CUDA: projection + RoPE (+ the seq->head exchange) are one GEMM with a head-scatter epilogue
             if sp == 1:
-                qkv = F_ops.qkv_project(h, self._qkv_weight, cos, sin, self._rope_fp16(T_local, h.device), B, T_local,
+                o = F_ops.qkv_attention(h, self._qkv_weight, cos, sin, self._rope_fp16(T_local, h.device), B, T_local,
                                         Hq, Hkv, hd)
-                o = F_ops.attention_packed(qkv, Hq, Hkv, True)
                 y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
                 return y.view(shape)
             from ...parallel.sequence_parallel import ulysses_peer

@@ -73,18 +73,24 @@ def _split(qkv, n_q, n_kv):
     return q, k, v
 
 
-def bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
-    """-> dqkv `[B, T, n_q + 2 n_kv, hd]` bf16 (gradient of the packed input)."""
+def bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool, rope=None):
+    """-> dqkv `[B, T, n_q + 2 n_kv, hd]` bf16 (gradient of the packed input). With `rope = (cos, sin)` (fp32
+    `[T, hd]`) the q and k parts are the gradient of the UN-rotated heads (transposed RoPE applied in the kernels)."""
     B, T, _, hd = qkv.shape
     if causal and _native_ok(hd):
         do, o = do.contiguous(), o.contiguous()
         dqkv = torch.empty_like(qkv)
         dq_acc = torch.empty(B, n_q, T, hd, dtype=torch.float32, device=qkv.device)
         delta = torch.empty(B, n_q, T, dtype=torch.float32, device=qkv.device)
+        cos, sin = rope if rope is not None else (None, None)
+        if cos is not None:
+            assert cos.dtype == torch.float32 and cos.shape == (T, hd) and cos.is_contiguous() and sin.is_contiguous()
         native._check(native.lib().tlm_attn_bwd(qkv.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                                                 dqkv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, T, n_q, n_kv,
-                                                hd, 1.0 / math.sqrt(hd), native._stream()), "attn_bwd")
+                                                hd, 1.0 / math.sqrt(hd), native._ptr(cos), native._ptr(sin),
+                                                native._stream()), "attn_bwd")
         return dqkv
+    assert rope is None, "the transposed rotation is part of the tcgen05 kernels only"
     _warn_library_path(hd, causal)
     rep = n_q // n_kv
     q, k, v = _split(qkv, n_q, n_kv)

@@ -193,6 +193,41 @@ class _QKVProject(torch.autograd.Function):
         return dh, None, None, None, None, None, None, None, None, None
 
 
+class _QKVAttention(torch.autograd.Function):
+    """`h [B*T, D]` -> causal GQA attention output `[B, T, n_q, hd]`: the QKV projection with RoPE and the packed
+    layout in its epilogue (`_QKVProject`), then flash attention, as ONE autograd node, so that the backward can
+    hand the transposed rotation to the attention-backward kernels (dQ is rotated while it is converted from its
+    fp32 accumulator, dK as it leaves tensor memory) instead of running a separate pass over the packed gradient."""
+
+    @staticmethod
+    def forward(ctx, h, weight, cos, sin, cs, B, T, n_q, n_kv, hd):
+        Ht = n_q + 2 * n_kv
+        qkv = torch.empty(B, T, Ht, hd, dtype=torch.bfloat16, device=h.device)
+        import ctypes
+        dst = (ctypes.c_void_p * 1)(qkv.data_ptr())
+        native.gemm_heads(h, weight, False, dst, 1, B, T, T, Ht, 0, n_q, n_kv, n_q, max(n_kv, 1), hd, n_q + n_kv, cs)
+        o, lse = native.flash_attn_fwd(qkv, n_q, n_kv, True)
+        ctx.save_for_backward(h, qkv, o, lse, cos, sin)
+        ctx.weight, ctx.meta = weight, (n_q, n_kv)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        h, qkv, o, lse, cos, sin = ctx.saved_tensors
+        n_q, n_kv = ctx.meta
+        w = ctx.weight
+        d = native.flash_attn_bwd(do.contiguous(), qkv, o, lse, n_q, n_kv, True, rope=(cos, sin))
+        d2 = d.view(h.shape[0], -1)
+        native.gemm_tn_accum(d2, h, _main_grad(w))
+        dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
+        return dh, None, None, None, None, None, None, None, None, None
+
+
+def qkv_attention(h, weight, cos, sin, cs, B: int, T: int, n_q: int, n_kv: int, hd: int) -> torch.Tensor:
+    """CUDA only (same conditions as `qkv_project`): projection + RoPE + causal attention -> `[B, T, n_q, hd]`."""
+    return _QKVAttention.apply(h, weight, cos.contiguous(), sin.contiguous(), cs, B, T, n_q, n_kv, hd)
+
+
 def qkv_project_fused_ok(h: torch.Tensor, weight: torch.Tensor | None, hd: int, T: int) -> bool:
     return weight is not None and _use_native(h, weight) and native.heads_epilogue_ok(hd, T)
 

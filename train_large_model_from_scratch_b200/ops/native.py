@@ -70,13 +70,18 @@ _SIGS = {
     "tlm_sumsq": (_I, [_P, _LL, _P, _P, _P]),
     "tlm_attn_fwd": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "tlm_attn_fwd_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P]),
-    "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
+    "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
     "tlm_peer_barrier": (_I, [_P, _I, _I, _I, _P]),
     "tlm_wait_flag": (_I, [_P, _I, _c.c_ulonglong, _P]),
     "tlm_reduce_scatter_blocks": (_I, []),
-    "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
-    "tlm_reduce_scatter_bf16": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _P]),
-    "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P, _P]),
+    "tlm_reduce_scatter": (_I, [_P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _I, _P]),
+    "tlm_reduce_scatter_bf16": (_I, [_P, _P, _LL, _LL, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _I, _I, _P]),
+    "tlm_adamw_gather": (_I, [_P, _P, _P, _P, _P, _P, _P, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _F, _F, _P, _P, _I, _P]),
+    "tlm_ready_ints": (_I, []),
+    "tlm_ready_max_buckets": (_I, []),
+    "tlm_wait_params_ready": (_I, [_P, _I, _I, _P]),
+    "tlm_gemm_arm_param_wait": (_I, [_P, _I, _I]),
+    "tlm_gemm_clear_param_waits": (None, []),
     "tlm_peer_allreduce_scalar": (_I, [_P, _P, _P, _P, _F, _I, _I, _I, _P]),
     "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),
@@ -415,9 +420,11 @@ def flash_attn_fwd(qkv: torch.Tensor, n_q: int, n_kv: int, causal: bool):
     return attention_cuda.fwd(qkv, n_q, n_kv, causal)
 
 
-def flash_attn_bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool):
+def flash_attn_bwd(do, qkv, o, lse, n_q: int, n_kv: int, causal: bool, rope=None):
+    """`rope = (cos, sin)` (fp32 `[T, hd]` tables): also apply the transposed rotation to dQ and dK, i.e. return
+    the gradient of the un-rotated q and k (done in fp32 as the gradients leave the kernels)."""
     from . import attention_cuda
-    return attention_cuda.bwd(do, qkv, o, lse, n_q, n_kv, causal)
+    return attention_cuda.bwd(do, qkv, o, lse, n_q, n_kv, causal, rope)
 
 
 # --------------------------------------------------------------------------- grouped GEMMs (MoE experts)

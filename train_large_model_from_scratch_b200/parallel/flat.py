@@ -43,8 +43,13 @@ class FlatBuffer:
     and the name -> (offset, numel, shape) table."""
 
     def __init__(self, named_params: list[tuple[str, torch.nn.Parameter]], compute_dtype: torch.dtype,
-                 device: torch.device, pad_to: int = 1, alloc=None):
+                 device: torch.device, pad_to: int = 1, alloc=None, align: int = _ALIGN):
+        """`align` (elements, a multiple of 8): every parameter starts at a multiple of it. With `align = 8 *
+        shard count` any parameter boundary can be a bucket boundary of the sharded optimizer step (each
+        rank's 1/n part of a bucket then starts 16-byte aligned). The gaps hold zeros and stay zero."""
         self.layout: "OrderedDict[str, tuple[int, int, torch.Size]]" = OrderedDict()
+        assert align % _ALIGN == 0
+        self.align = align
         off = 0
         seen: dict[int, str] = {}
         for name, p in named_params:
@@ -54,6 +59,7 @@ class FlatBuffer:
             n = p.numel()
             if n % _ALIGN:
                 raise ValueError(f"parameter {name} has {n} elements; a multiple of {_ALIGN} is required")
+            off = ((off + align - 1) // align) * align
             self.layout[name] = (off, n, p.shape)
             off += n
         self.numel = off
@@ -115,13 +121,13 @@ def fuse_adjacent(params: list[torch.nn.Parameter]) -> torch.Tensor:
 
 
 def flatten_model(model: torch.nn.Module, compute_dtype: torch.dtype, device: torch.device,
-                  dense_pad: int = 1, expert_pad: int = 1, alloc=None) -> tuple[FlatBuffer, FlatBuffer | None]:
+                  dense_pad: int = 1, expert_pad: int = 1, alloc=None, align: int = _ALIGN) -> tuple[FlatBuffer, FlatBuffer | None]:
     """Move every parameter of `model` into flat storage. Returns (dense, expert)."""
     dense, expert = [], []
     for name, p in model.named_parameters():
         (expert if is_expert_param(name) else dense).append((name, p))
-    dense_buf = FlatBuffer(dense, compute_dtype, device, dense_pad, alloc)
-    expert_buf = FlatBuffer(expert, compute_dtype, device, expert_pad, alloc) if expert else None
+    dense_buf = FlatBuffer(dense, compute_dtype, device, dense_pad, alloc, align)
+    expert_buf = FlatBuffer(expert, compute_dtype, device, expert_pad, alloc, align) if expert else None
     for m in model.modules():
         hook = getattr(m, "_post_flatten", None)
         if hook is not None:

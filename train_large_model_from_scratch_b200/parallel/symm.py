@@ -12,8 +12,14 @@ communication themselves:
                    `--grad_wire_dtype bf16` the peers read a bf16 rounding of the
                    gradients instead (half the NVLink bytes, fp32 accumulation);
   AdamW + gather   the optimizer kernel stores the updated bf16 parameters into
-                   every rank's replica (`multimem.st` or P2P stores);
-  barriers         symmetric flag arrays with bounded waits.
+                   every rank's replica (`multimem.st` or P2P stores) and ends by
+                   publishing per-bucket "parameters ready" words, which the first
+                   GEMM of the next forward pass that reads the bucket waits for
+                   in its producer warp (no barrier after the optimizer step);
+  buckets          the buffer is cut at layer-group boundaries; every rank owns 1/n
+                   of each bucket, and a bucket's reduce-scatter starts on a side
+                   stream as soon as the last backward pass has left its layers;
+  flags            symmetric flag arrays with bounded waits.
 
 `torch.distributed` (NCCL) stays for the control plane: rendezvous, the scalar
 norm / loss reductions, checkpoint traffic. Set `TLM_COMM=nccl` to run the
@@ -64,26 +70,44 @@ class _Peer:
 
 
 class PeerCollectives:
+    """Bucket-wise gradient reduce-scatter and AdamW + parameter all-gather over peer memory.
+
+    Per flat buffer: one symmetric flag array for the reduce-scatter's "my gradients of this bucket are final"
+    exchange (epochs counted by the kernels, one per launch, same launch order on every rank) and one for the
+    "parameters ready" words that the update kernels publish and the consumers of the parameters wait for
+    (`csrc/common.cuh`, READY_*). Reductions that start during the backward pass run on `comm_stream`
+    with a small grid; `join()` brings the main stream behind them."""
+
     def __init__(self):
         self.state = {}          # id(shard) -> dict
         self.wire_dtype = "fp32"
+        self.comm_stream = None
+        self._forked = False
+        self.overlap_blocks = int(os.environ.get("TLM_RS_OVERLAP_BLOCKS", "48"))
 
     @classmethod
     def create(cls, fused, wire_dtype: str = "fp32") -> "PeerCollectives":
         self = cls()
         self.wire_dtype = wire_dtype
+        L = native.lib()
         for s in fused.shards:
             if s.n == 1 or not s.sharded:
                 continue
+            assert len(s.buckets) <= L.tlm_ready_max_buckets() and s.n <= 16
             dev = s.buf.params.device
+            if self.comm_stream is None:
+                self.comm_stream = torch.cuda.Stream(device=dev, priority=-1)
             flags = symm_alloc(64, torch.int32, dev)
+            ready = symm_alloc(L.tlm_ready_ints(), torch.int32, dev)
             st = {
                 "grad": _Peer(s.buf.main_grad, s.group),
                 "param": _Peer(s.buf.params, s.group),
                 "flags": _Peer(flags, s.group),
                 "flags_t": flags,
-                "partials": torch.zeros(native.lib().tlm_reduce_scatter_blocks(), dtype=torch.float32, device=dev),
-                "sumsq": torch.zeros((), dtype=torch.float32, device=dev),
+                "ready": _Peer(ready, s.group),
+                "ready_t": ready,
+                "partials": torch.zeros(L.tlm_reduce_scatter_blocks(), dtype=torch.float32, device=dev),
+                "sumsq": torch.zeros(len(s.buckets), dtype=torch.float32, device=dev),
             }
             if wire_dtype == "bf16":
                 wire = symm_alloc(s.buf.padded, torch.bfloat16, dev)
@@ -100,44 +124,93 @@ class PeerCollectives:
         f = self.state[id(s)]["flags"]
         native._check(native.lib().tlm_peer_barrier(f.ptr_array, f.rank, f.n, 0, native._stream()), "peer_barrier")
 
-    def reduce_grads(self, s) -> torch.Tensor:
-        """Sum of every rank's gradient slice -> `s.grad_shard`; also leaves the
-        slice's sum of squares in `self.last_sumsq(s)`. (Epoch argument 0: the kernels count their own
-        flag epochs, so the launch is the same every step.)"""
+    # -- gradients -----------------------------------------------------------------------
+    def reduce_bucket(self, s, bi: int, overlapped: bool) -> None:
+        """Sum of every rank's gradients over this rank's piece of bucket `bi` -> `s.grad_shard`, and the piece's
+        sum of squares -> entry `bi` of the shard's sumsq vector. The kernel's prologue is the flag exchange
+        that tells the peers "my gradients of this bucket are final" and waits for theirs. `overlapped`: the
+        backward pass is still running; launch on the communication stream behind everything queued so far,
+        with a grid that leaves the SMs to the GEMMs."""
         st = self.state[id(s)]
+        b = s.buckets[bi]
         g, f = st["grad"], st["flags"]
-        if "wire" in st:
-            w = st["wire"]
-            native._check(native.lib().tlm_reduce_scatter_bf16(
-                s.buf.main_grad.data_ptr(), st["wire_t"].data_ptr(), s.buf.padded, w.ptr_array,
-                ctypes.c_void_p(w.mc_ptr) if w.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
-                st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, 0,
-                native._stream()), "reduce_scatter_bf16")
-            return s.grad_shard
-        native._check(native.lib().tlm_reduce_scatter(
-            g.ptr_array, ctypes.c_void_p(g.mc_ptr) if g.mc_ptr else None, f.ptr_array, s.grad_shard.data_ptr(),
-            st["partials"].data_ptr(), st["sumsq"].data_ptr(), s.lo, s.len, g.rank, g.n, 0,
-            native._stream()), "reduce_scatter")
-        return s.grad_shard
+        out = s.grad_shard[b.off:b.off + b.seg]
+        sumsq = st["sumsq"][bi:bi + 1]
+        blocks = self.overlap_blocks if overlapped else 0
+        if overlapped:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            self._forked = True
+            ctx = torch.cuda.stream(self.comm_stream)
+        else:
+            import contextlib
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if "wire" in st:
+                w = st["wire"]
+                native._check(native.lib().tlm_reduce_scatter_bf16(
+                    s.buf.main_grad.data_ptr(), st["wire_t"].data_ptr(), b.lo, b.hi - b.lo, w.ptr_array,
+                    ctypes.c_void_p(w.mc_ptr) if w.mc_ptr else None, f.ptr_array, out.data_ptr(),
+                    st["partials"].data_ptr(), sumsq.data_ptr(), b.seg_lo, b.seg, g.rank, g.n, 0, blocks,
+                    native._stream()), "reduce_scatter_bf16")
+            else:
+                native._check(native.lib().tlm_reduce_scatter(
+                    g.ptr_array, ctypes.c_void_p(g.mc_ptr) if g.mc_ptr else None, f.ptr_array, out.data_ptr(),
+                    st["partials"].data_ptr(), sumsq.data_ptr(), b.seg_lo, b.seg, g.rank, g.n, 0, blocks,
+                    native._stream()), "reduce_scatter")
+
+    def join(self) -> None:
+        """The main stream waits for the reductions queued on the communication stream."""
+        if self._forked:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            self._forked = False
 
     def last_sumsq(self, s) -> torch.Tensor:
-        return self.state[id(s)]["sumsq"]
+        return self.state[id(s)]["sumsq"].sum()
 
-    def update_and_gather(self, s, grad, scale, step: int, g: dict, hyper=None) -> None:
+    # -- parameters ----------------------------------------------------------------------
+    def update_and_gather(self, s, bi: int, grad, scale, step: int, g: dict, hyper=None) -> None:
+        """Clipped AdamW on this rank's piece of bucket `bi`; the bf16 result goes into every rank's replica and
+        the kernel ends by publishing the bucket's "parameters ready" word to all ranks."""
         st = self.state[id(s)]
+        b = s.buckets[bi]
         b1, b2 = g["betas"]
-        pr = st["param"]
+        pr, rd = st["param"], st["ready"]
+        sl = slice(b.off, b.off + b.seg)
         lr, inv_bc1, inv_sqrt_bc2 = native.adam_hyper(max(step, 1), g["lr"], b1, b2)
         native._check(native.lib().tlm_adamw_gather(
-            s.master.data_ptr(), s.exp_avg.data_ptr(), s.exp_avg_sq.data_ptr(), grad.data_ptr(), pr.ptr_array,
-            ctypes.c_void_p(pr.mc_ptr) if pr.mc_ptr else None, scale.data_ptr(), s.lo, s.len, pr.rank, pr.n,
-            lr, b1, b2, g["eps"], g["weight_decay"], inv_bc1, inv_sqrt_bc2, native._ptr(hyper), native._stream()),
-            "adamw_gather")
-        self.barrier(s)          # every replica complete before anyone's next forward reads it
+            s.master[sl].data_ptr(), s.exp_avg[sl].data_ptr(), s.exp_avg_sq[sl].data_ptr(), grad[sl].data_ptr(),
+            pr.ptr_array, ctypes.c_void_p(pr.mc_ptr) if pr.mc_ptr else None, scale.data_ptr(), b.seg_lo, b.seg, pr.rank,
+            pr.n, lr, b1, b2, g["eps"], g["weight_decay"], inv_bc1, inv_sqrt_bc2, native._ptr(hyper), rd.ptr_array, bi,
+            native._stream()), "adamw_gather")
 
     def gather_params(self, s) -> None:
         """Parameters were already distributed by `update_and_gather`."""
         return None
+
+    def wait_first_buckets(self, shards) -> None:
+        """Stream-ordered bounded wait for the buckets of layer group 0 (embedding, first norm; every bucket of
+        a buffer whose buckets are not tied to layer groups): no GEMM is their first reader."""
+        native.lib().tlm_gemm_clear_param_waits()
+        for s in shards:
+            st = self.state.get(id(s))
+            if st is None:
+                continue
+            for bi, b in enumerate(s.buckets):
+                if b.group == 0:
+                    native._check(native.lib().tlm_wait_params_ready(st["ready_t"].data_ptr(), bi, s.n, native._stream()),
+                                  "wait_params_ready")
+
+    def arm_group(self, shards, g: int) -> None:
+        """The next GEMM launched waits, in its producer warp, for every rank's update of group `g`'s buckets."""
+        if g == 0:
+            return
+        for s in shards:
+            st = self.state.get(id(s))
+            if st is None:
+                continue
+            for bi, b in enumerate(s.buckets):
+                if b.group == g:
+                    native._check(native.lib().tlm_gemm_arm_param_wait(st["ready_t"].data_ptr(), bi, s.n), "arm_param_wait")
 
 
 class PeerScalar:

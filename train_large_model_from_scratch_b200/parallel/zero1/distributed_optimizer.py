@@ -66,28 +66,87 @@ def partition_tensors(tensor_dict: "OrderedDict[tuple[int, int], torch.Tensor]",
     return assignment, tensor_dict
 
 
-class _Shard:
-    """Optimizer state of one flat buffer on this rank."""
+class _Bucket:
+    """One contiguous range `[lo, hi)` of a flat buffer and this rank's 1/parts piece of it."""
 
-    def __init__(self, buf: FlatBuffer, group, sharded: bool):
+    __slots__ = ("lo", "hi", "off", "seg", "seg_lo", "group")
+
+    def __init__(self, lo: int, hi: int, off: int, seg: int, seg_lo: int, group: int):
+        self.lo, self.hi = lo, hi            # range of the bucket in the flat buffer (elements)
+        self.off, self.seg = off, seg        # this rank's piece: `seg` elements at `off` of its local state arrays
+        self.seg_lo = seg_lo                 # ... which are elements [seg_lo, seg_lo + seg) of the flat buffer
+        self.group = group                   # layer group whose backward completes the bucket's gradients (0: the last)
+
+
+class _Shard:
+    """Optimizer state of one flat buffer on this rank.
+
+    The buffer is cut into buckets (`cuts`: ascending element offsets) and every rank owns the r-th 1/n piece of
+    EVERY bucket, not one contiguous 1/n slice of the whole buffer: a bucket's gradients are final as soon as the
+    backward pass has left its layers, so its reduce-scatter can run under the rest of the backward pass, and
+    after the update its parameters can be handed to the next forward pass bucket by bucket. The local state
+    arrays (`master`, `exp_avg`, `exp_avg_sq`, `grad_shard`) are the concatenation of the rank's pieces."""
+
+    def __init__(self, buf: FlatBuffer, group, sharded: bool, cuts: list[int] | None = None,
+                 bucket_groups: list[int] | None = None):
         self.buf, self.group = buf, group
         self.n = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.sharded = sharded and self.n > 1
         parts = self.n if self.sharded else 1
         assert buf.padded % parts == 0, "flat buffer must be padded to a multiple of the shard count"
-        self.len = buf.padded // parts
-        self.lo = (self.rank if self.sharded else 0) * self.len
-        self.hi = self.lo + self.len
-        self.master = buf.init_fp32[self.lo:self.hi].clone()
+        if parts == 1:
+            cuts, bucket_groups = None, None                 # nothing to overlap: one bucket, one kernel
+        pts = sorted(set([0, buf.padded] + [int(c) for c in (cuts or []) if 0 < c < buf.padded]))
+        if bucket_groups is None or len(bucket_groups) != len(pts) - 1:
+            bucket_groups = [0] * (len(pts) - 1)
+        unit = parts * 8
+        self.buckets: list[_Bucket] = []
+        off = 0
+        for (lo, hi), g in zip(zip(pts[:-1], pts[1:]), bucket_groups):
+            assert parts == 1 or (lo % unit == 0 and hi % unit == 0), \
+                f"bucket boundaries must be multiples of 8 * shard count ({unit}): {lo}, {hi}"
+            seg = (hi - lo) // parts
+            self.buckets.append(_Bucket(lo, hi, off, seg, lo + (self.rank if self.sharded else 0) * seg, g))
+            off += seg
+        self.len = off
+        self.master = self.take_local(buf.init_fp32)
         buf.init_fp32 = None                                    # full fp32 copy no longer needed
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_shard = None if not self.sharded else torch.zeros_like(self.master)
-        # slice of the buffer whose |g|^2 this rank contributes to the global norm
+        self.reduced: set = set()                               # buckets already reduced in the current step
+        # slice of the buffer whose |g|^2 this rank contributes to the global norm when nothing is sharded
         vlen = buf.padded // self.n
-        self.norm_lo, self.norm_hi = ((self.lo, self.hi) if self.sharded
-                                      else (self.rank * vlen, (self.rank + 1) * vlen))
+        self.norm_lo, self.norm_hi = self.rank * vlen, (self.rank + 1) * vlen
+
+    # -- local <-> flat ------------------------------------------------------------------
+    def take_local(self, full: torch.Tensor) -> torch.Tensor:
+        """This rank's pieces of a full-length tensor, concatenated (a new tensor)."""
+        if len(self.buckets) == 1:
+            b = self.buckets[0]
+            return full[b.seg_lo:b.seg_lo + b.seg].clone()
+        return torch.cat([full[b.seg_lo:b.seg_lo + b.seg] for b in self.buckets])
+
+    def put_local(self, full: torch.Tensor, local: torch.Tensor) -> None:
+        """Inverse of `take_local`: writes the pieces into their places of `full` (dtype of `full`)."""
+        for b in self.buckets:
+            full[b.seg_lo:b.seg_lo + b.seg].copy_(local[b.off:b.off + b.seg])
+
+    def copy_range_from(self, local: torch.Tensor, off: int, n: int, src: torch.Tensor) -> None:
+        """`local` (one of the state arrays) takes the part of flat elements `[off, off + n)` that this rank
+        owns from `src` (`n` values: the whole range)."""
+        for b in self.buckets:
+            lo, hi = max(off, b.seg_lo), min(off + n, b.seg_lo + b.seg)
+            if lo < hi:
+                local[b.off + lo - b.seg_lo:b.off + hi - b.seg_lo].copy_(src[lo - off:hi - off])
+
+    def assemble_full(self, stack: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """`stack [n, len]` (row r = rank r's local array) -> the full buffer."""
+        full = out if out is not None else torch.empty(self.buf.padded, dtype=stack.dtype, device=stack.device)
+        for b in self.buckets:
+            full[b.lo:b.hi].view(stack.shape[0], b.seg).copy_(stack[:, b.off:b.off + b.seg])
+        return full
 
 
 class FusedAdamW:
@@ -96,17 +155,22 @@ class FusedAdamW:
 
     def __init__(self, buffers: list[FlatBuffer], lr: float = 1e-3, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, groups: list | None = None, grad_divisor: float = 1.0,
-                 sharded: bool = False, norm_group=None):
+                 sharded: bool = False, norm_group=None, cuts: list | None = None, bucket_groups: list | None = None):
+        """`cuts[i]` / `bucket_groups[i]` (optional, per buffer): bucket boundaries in elements and, per bucket,
+        the layer group whose backward pass completes its gradients (see `_Shard`, `group_backward_done`)."""
         self.buffers = [b for b in buffers if b is not None]
         groups = groups if groups is not None else [None] * len(self.buffers)
+        cuts = cuts if cuts is not None else [None] * len(self.buffers)
+        bucket_groups = bucket_groups if bucket_groups is not None else [None] * len(self.buffers)
         self.param_groups = [dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
                                   amsgrad=False, maximize=False, params=[])]
         self.grad_divisor = float(grad_divisor)
         self.norm_group = norm_group
-        self.shards = [_Shard(b, g, sharded) for b, g in zip(self.buffers, groups)]
+        self.shards = [_Shard(b, g, sharded, c, bg) for b, g, c, bg in zip(self.buffers, groups, cuts, bucket_groups)]
         self.step_count = 0
         self.grad_norm = None
         self._comm = None              # optional peer-memory collective engine (CUDA)
+        self.last_micro_step = True    # set by the trainer: bucket reductions only start in the step's last backward
         # per-step scalars of the AdamW kernels (lr, bias corrections) in device memory, fed from pinned memory
         dev = self.buffers[0].params.device if self.buffers else torch.device("cpu")
         if dev.type == "cuda":
@@ -120,8 +184,41 @@ class FusedAdamW:
 
     # -- the reference-style surface ------------------------------------------------
     def zero_grad(self, set_to_none: bool = True) -> None:
+        # the peers read this rank's gradient buffer in their reduce-scatter: their "parameters ready" flags
+        # (which they send after it) must be here before the buffer is cleared for the next step
+        self.wait_params_ready()
         for b in self.buffers:
             b.zero_grad()
+        for s in self.shards:
+            s.reduced.clear()
+
+    # -- hooks of the model's forward / backward pass (peer-memory path only) ---------
+    def wait_params_ready(self) -> None:
+        """Queue the wait for the buckets no GEMM waits for itself (group 0: embedding, first norm)."""
+        if self._comm is not None:
+            self._comm.wait_first_buckets(self.shards)
+
+    def before_forward(self) -> None:
+        self.wait_params_ready()
+
+    def before_group(self, g: int) -> None:
+        """Forward pass is about to enter layer group `g`: its first GEMM waits for the group's parameters."""
+        if self._comm is not None:
+            self._comm.arm_group(self.shards, g)
+
+    def group_backward_done(self, g: int) -> None:
+        """Backward pass has left layer group `g`: on the step's last micro-step the gradients of the group's
+        buckets are final, so their reduce-scatter starts now, on the communication stream, under the rest
+        of the backward pass (what DDP's bucketed all-reduce gives the reference, `training/trainer.py:133,247`)."""
+        if self._comm is None or not self.last_micro_step:
+            return
+        for s in self.shards:
+            if not self._comm.handles(s):
+                continue
+            for bi, b in enumerate(s.buckets):
+                if b.group == g and bi not in s.reduced:
+                    self._comm.reduce_bucket(s, bi, overlapped=True)
+                    s.reduced.add(bi)
 
     def prepare_step(self) -> None:
         """Host part of a step: advance the step counter and publish this step's scalars (learning rate, bias
@@ -149,10 +246,12 @@ class FusedAdamW:
         g = self.param_groups[0]
         inv = 1.0 / self.grad_divisor
         norm_sq = None
+        if self._comm is not None:
+            self._comm.join()                    # bucket reductions started during backward
         for s in self.shards:
             grad = self._reduce(s)
             if self._comm is not None and self._comm.handles(s):
-                part = self._comm.last_sumsq(s)          # produced by the reduce-scatter kernel
+                part = self._comm.last_sumsq(s)          # produced by the reduce-scatter kernels
             else:
                 part = self._sumsq(grad if s.sharded else s.buf.main_grad[s.norm_lo:s.norm_hi])
             norm_sq = part if norm_sq is None else norm_sq + part
@@ -185,13 +284,20 @@ class FusedAdamW:
         if s.n == 1:
             return mg
         if self._comm is not None and self._comm.handles(s):
-            return self._comm.reduce_grads(s)
+            for bi in range(len(s.buckets)):
+                if bi not in s.reduced:
+                    self._comm.reduce_bucket(s, bi, overlapped=False)
+                    s.reduced.add(bi)
+            return s.grad_shard
         if s.sharded:
             if mg.is_cuda:
-                dist.reduce_scatter_tensor(s.grad_shard, mg, op=dist.ReduceOp.SUM, group=s.group)
+                for b in s.buckets:             # rank r receives the r-th 1/n piece of every bucket
+                    dist.reduce_scatter_tensor(s.grad_shard[b.off:b.off + b.seg], mg[b.lo:b.hi], op=dist.ReduceOp.SUM,
+                                               group=s.group)
             else:                                   # Gloo has no reduce-scatter
                 dist.all_reduce(mg, op=dist.ReduceOp.SUM, group=s.group)
-                s.grad_shard.copy_(mg[s.lo:s.hi])
+                for b in s.buckets:
+                    s.grad_shard[b.off:b.off + b.seg].copy_(mg[b.seg_lo:b.seg_lo + b.seg])
             return s.grad_shard
         dist.all_reduce(mg, op=dist.ReduceOp.SUM, group=s.group)
         return mg
@@ -204,16 +310,21 @@ class FusedAdamW:
 
     def _update(self, s: _Shard, grad: torch.Tensor, scale: torch.Tensor, g: dict) -> None:
         b1, b2 = g["betas"]
-        out = s.buf.params[s.lo:s.hi]
         if self._comm is not None and self._comm.handles(s):
-            self._comm.update_and_gather(s, grad, scale, self.step_count, g, hyper=self._hyper)
-        elif grad.is_cuda:
-            native.adamw_step(s.master, s.exp_avg, s.exp_avg_sq, grad, out, scale, self.step_count,
-                              g["lr"], b1, b2, g["eps"], g["weight_decay"], hyper=self._hyper)
-        else:
-            oracle.adamw_step(s.master, grad, s.exp_avg, s.exp_avg_sq, self.step_count, g["lr"], b1, b2,
-                              g["eps"], g["weight_decay"], grad_scale=float(scale))
-            out.copy_(s.master.to(out.dtype))
+            for bi in range(len(s.buckets)):                 # bucket 0 first: the next forward pass needs it first
+                self._comm.update_and_gather(s, bi, grad, scale, self.step_count, g, hyper=self._hyper)
+            return
+        for b in s.buckets:
+            sl = slice(b.off, b.off + b.seg)
+            out = s.buf.params[b.seg_lo:b.seg_lo + b.seg]
+            if grad.is_cuda:
+                native.adamw_step(s.master[sl], s.exp_avg[sl], s.exp_avg_sq[sl], grad[sl], out, scale, self.step_count,
+                                  g["lr"], b1, b2, g["eps"], g["weight_decay"], hyper=self._hyper)
+            else:
+                m = s.master[sl]
+                oracle.adamw_step(m, grad[sl], s.exp_avg[sl], s.exp_avg_sq[sl], self.step_count, g["lr"], b1, b2,
+                                  g["eps"], g["weight_decay"], grad_scale=float(scale))
+                out.copy_(m.to(out.dtype))
 
     def _gather(self, s: _Shard, via_library: bool = False) -> None:
         if not s.sharded:
@@ -221,11 +332,13 @@ class FusedAdamW:
         if not via_library and self._comm is not None and self._comm.handles(s):
             return self._comm.gather_params(s)
         p = s.buf.params
-        if p.is_cuda:
-            dist.all_gather_into_tensor(p, p[s.lo:s.hi].clone(), group=s.group)
-        else:
-            chunks = list(p.view(s.n, s.len).unbind(0))
-            dist.all_gather(chunks, p[s.lo:s.hi].clone(), group=s.group)
+        for b in s.buckets:
+            mine = p[b.seg_lo:b.seg_lo + b.seg].clone()
+            if p.is_cuda:
+                dist.all_gather_into_tensor(p[b.lo:b.hi], mine, group=s.group)
+            else:
+                chunks = list(p[b.lo:b.hi].view(s.n, b.seg).unbind(0))
+                dist.all_gather(chunks, mine, group=s.group)
 
     # -- full-buffer views of sharded state (checkpointing) -----------------------------
     def gather_full(self, s: _Shard, which: str) -> torch.Tensor:
@@ -233,18 +346,17 @@ class FusedAdamW:
         local = getattr(s, which)
         if not s.sharded:
             return local.clone()
-        full = torch.empty(s.buf.padded, dtype=torch.float32, device=local.device)
-        chunks = list(full.view(s.n, s.len).unbind(0))
-        dist.all_gather(chunks, local.contiguous(), group=s.group)
-        return full
+        stack = torch.empty(s.n, s.len, dtype=torch.float32, device=local.device)
+        dist.all_gather(list(stack.unbind(0)), local.contiguous(), group=s.group)
+        return s.assemble_full(stack)
 
     def scatter_full(self, s: _Shard, which: str, full: torch.Tensor) -> None:
-        getattr(s, which).copy_(full[s.lo:s.hi])
+        getattr(s, which).copy_(s.take_local(full))
 
     def sync_params_from_master(self) -> None:
         """Rewrite the compute-dtype parameters from the fp32 master shards."""
         for s in self.shards:
-            s.buf.params[s.lo:s.hi].copy_(s.master.to(s.buf.params.dtype))
+            s.put_local(s.buf.params, s.master)
             self._gather(s, via_library=True)
 
 

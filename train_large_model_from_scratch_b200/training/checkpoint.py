@@ -90,9 +90,7 @@ def load_model_state_dict(model, optimizer, state: dict) -> None:
             t = t[ep_rank * el:(ep_rank + 1) * el]
         i, off, n, shape = _locate(model, name)
         s = opt.shards[i]
-        lo, hi = max(off, s.lo), min(off + n, s.hi)
-        if lo < hi:
-            s.master[lo - s.lo:hi - s.lo].copy_(t.reshape(-1)[lo - off:hi - off])
+        s.copy_range_from(s.master, off, n, t.reshape(-1))
     opt.sync_params_from_master()
 
 

@@ -189,12 +189,18 @@ class Trainer:
         # summed over SP and averaged over DP); expert parameters only over DP.
         buffers = [m.dense_buf] + ([m.expert_buf] if m.expert_buf is not None else [])
         groups = [self.dp_sp_group] + ([self.dp_group] if m.expert_buf is not None else [])
+        cuts = bucket_groups = None
+        if zero1 and self.world_size > 1:
+            # buckets of the sharded step: cut at layer groups of ~TLM_ZERO1_BUCKET_MB of fp32 gradients
+            cuts, bucket_groups = m.plan_buckets(int(float(os.environ.get("TLM_ZERO1_BUCKET_MB", "192")) * (1 << 20)))
         fused = FusedAdamW(buffers, lr=o.max_lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
                            weight_decay=o.weight_decay, groups=groups, grad_divisor=self.dp_world_size,
-                           sharded=zero1, norm_group=self.dp_sp_group)
+                           sharded=zero1, norm_group=self.dp_sp_group, cuts=cuts, bucket_groups=bucket_groups)
         if getattr(self, "_symm", False):
             from ..parallel.symm import PeerCollectives
             fused._comm = PeerCollectives.create(fused, wire_dtype=config.parallel.grad_wire_dtype)
+            if fused._comm.state:
+                m.comm_hooks = fused          # forward: gate GEMMs on "parameters ready"; backward: start bucket reductions
         if zero1:
             named = OrderedDict((n, p) for n, p in m.named_parameters())
             self.optimizer = DistributedOptimizer(optimizer=fused, process_group=self.dp_group, named_tensors=named)
@@ -348,6 +354,7 @@ class Trainer:
             batches = self._take_prefetched()
         for micro_step in range(self.training_info["grad_accum_steps"]):
             batch = batches[micro_step] if batches is not None else self._next_batch()
+            self.raw_optimizer.last_micro_step = micro_step == self.training_info["grad_accum_steps"] - 1
             l = self._one_training_micro_step(config, micro_step, batch)
             loss_accum = l if loss_accum is None else loss_accum + l
         lr = self._lr_scheduler(step, self.training_info["max_steps"], config.optim.warmup_steps,
@@ -387,6 +394,7 @@ class Trainer:
         loss_accum = None
         for ms in range(ga):
             b = self._graph_in[ms]
+            self.raw_optimizer.last_micro_step = ms == ga - 1
             _, loss, logging_loss = self.model(b["input_ids"], b["labels"], loss_scale=1.0 / ga)
             loss.backward()
             l = logging_loss.detach()
