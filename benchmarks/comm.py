@@ -1,6 +1,6 @@
 """Peer-memory communication kernels against their NVLink roofline.
 
-    torchrun --nproc-per-node N -m bench.comm [--mb 1024]
+    torchrun --nproc-per-node N -m benchmarks.comm [--mb 1024]
 
 Times, with CUDA events and the maximum over ranks, the kernels that move data between GPUs:
 
@@ -109,8 +109,8 @@ def main():
             el = 2 if bf16 else 4
             wire_bytes = shard * el * (1 if mc else (world - 1))
             cases.append((f"reduce_scatter {'bf16' if bf16 else 'fp32'} wire, {tag}", lambda mc=mc, bf16=bf16: rs(mc, bf16), wire_bytes))
-        cases.append((f"reduce_scatter fp32 wire, {tag}, 48 blocks (the grid used under the backward pass)",
-                      lambda mc=mc: rs(mc, False, 48), shard * 4 * (1 if mc else (world - 1))))
+        cases.append((f"reduce_scatter fp32 wire, {tag}, 296 blocks of 128 threads (the grid used under the backward pass)",
+                      lambda mc=mc: rs(mc, False, 296), shard * 4 * (1 if mc else (world - 1))))
         cases.append((f"adamw + all-gather (bf16 params), {tag}", lambda mc=mc: ag(mc), shard * 2 * (1 if mc else (world - 1))))
     nccl_out = torch.empty(shard, device=dev)
     cases.append(("nccl reduce_scatter_tensor fp32", lambda: dist.reduce_scatter_tensor(nccl_out, grads), shard * 4 * (world - 1)))

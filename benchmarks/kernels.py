@@ -1,6 +1,6 @@
 """Per-kernel timing against the measured roofline.
 
-    python -m bench.kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
+    python -m benchmarks.kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
 
 Times each kernel with CUDA events on the launching stream after warm-up,
 flushing L2 (a 256 MB write) between timed launches, and prints one JSON line

@@ -49,10 +49,23 @@ def main():
         except RuntimeError:
             pass
     wsum = float(t.raw_model.dense_buf.params.double().sum())
+    guards = []
+    if torch.cuda.is_available():
+        from train_large_model_from_scratch_b200.ops import native
+        from train_large_model_from_scratch_b200.parallel import symm
+        torch.cuda.synchronize()
+        guards = symm.check_guards()                     # empty unless TLM_SYMM_CANARY=1 found damage
+        if native.available():
+            native.raise_on_device_status()
+        if t.world_size > 1:
+            import torch.distributed as dist
+            all_guards = [None] * t.world_size
+            dist.all_gather_object(all_guards, guards)
+            guards = [f"rank {r}: {g}" for r, gs in enumerate(all_guards) for g in gs]
     if rank == 0:
         with open(os.environ["TLM_TEST_OUT"], "w") as f:
             json.dump({"losses": losses, "norms": norms, "start_step": t.start_step, "wsum": wsum,
-                       "log_dir": t.log_dir}, f)
+                       "log_dir": t.log_dir, "guards": guards}, f)
     t.close()
 
 

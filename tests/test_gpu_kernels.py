@@ -57,6 +57,19 @@ def test_gemm_tn_accum(nat, M, N, K):
     assert _rel_err(acc, 2 * ref - 1.0) < 1e-4
 
 
+@pytest.mark.parametrize("M,N,K", [(32768, 1024, 1024), (16384, 4096, 1024), (20000, 520, 264)])
+def test_gemm_tn_accum_long_reductions(nat, M, N, K):
+    """Weight-gradient shapes: long reductions with few output tiles (split-K with atomic adds)."""
+    dy, x = _rand(M, N, seed=25, scale=0.5), _rand(M, K, seed=26, scale=0.5)
+    ref = 1.0 + dy.float().t() @ x.float()
+    acc = torch.ones(N, K, device="cuda")
+    nat.gemm_tn_accum(dy, x, acc)
+    nat.raise_on_device_status()
+    assert _rel_err(acc, ref) < 1e-4
+    nat.gemm_tn_accum(dy, x, acc)                       # accumulates on top
+    assert _rel_err(acc, 2 * ref - 1.0) < 1e-4
+
+
 def test_gemm_strided_output_and_guard_rows(nat):
     """Output written into a slice of a larger buffer must not touch its neighbours."""
     M, N, K = 200, 264, 72

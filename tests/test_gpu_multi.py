@@ -115,3 +115,23 @@ def test_expert_parallel_at_larger_groups(world):
     peer = _run(world, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags + MOE + ["--sep_size", str(world)])
     _close(ref["losses"], peer["losses"], 3e-3)
     _close(ref["norms"], peer["norms"], 3e-2)
+
+
+@pytest.mark.parametrize("kind", ["dense_dp", "ulysses", "moe"])
+def test_guard_bands_stay_intact_and_results_do_not_depend_on_epoch_parity(kind):
+    """Stand-ins for a device-side memory / race checker on the peer-memory paths: (1) every symmetric buffer
+    between guard bands that no peer store may touch; (2) the same job with all flag epochs started at an odd value
+    (every double-buffered slot swaps parity) and just below 2^31 (the counters wrap within the run): losses and
+    norms must not move."""
+    flags4 = [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)]
+    flags = {"dense_dp": FLAGS + ["--sep_size", "1"], "ulysses": flags4 + ["--sep_size", "2"],
+             "moe": flags4 + MOE + ["--sep_size", "2"]}[kind]
+    env = {"TLM_COMM": "symm", "TLM_NVLS": "0"}
+    base = _run(2, env, flags)
+    guarded = _run(2, dict(env, TLM_SYMM_CANARY="1"), flags)
+    assert guarded["guards"] == [], guarded["guards"]
+    _close(base["losses"], guarded["losses"], 2e-3)
+    for e0 in ("1", "2147483600"):
+        other = _run(2, dict(env, TLM_EPOCH0=e0), flags)
+        _close(base["losses"], other["losses"], 2e-3)
+        _close(base["norms"], other["norms"], 2e-2)

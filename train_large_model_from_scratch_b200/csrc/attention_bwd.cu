@@ -28,7 +28,19 @@
 
 namespace tlm {
 
-constexpr int AB_TILE = 128, AB_THREADS = 320;
+constexpr int AB_TILE = 128, AB_MAX_DST = 8;
+// Four warpgroups: 0 = TMA producer (warp 0) + MMA issuer (warp 1), 1 and 2 = softmax (the two column halves),
+// 3 = dQ flush. Registers are moved from the light warpgroups to the softmax ones with setmaxnreg.
+constexpr int AB_THREADS = 512;
+constexpr int AB_REGS_CTRL = 104, AB_REGS_FLUSH = 88, AB_REGS_SOFTMAX = 160;   // 128 * (104 + 88) + 256 * 160 = 65536
+
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
+struct AttnBwdDst {
+  __nv_bfloat16* p[AB_MAX_DST];
+  int n, rows, heads;
+};
 
 struct AttnBwdParams {
   __nv_bfloat16* dqkv;
@@ -44,6 +56,14 @@ struct AttnBwdParams {
   // dx[j+h] = dy[j+h] c[j+h] - dy[j] s[j] (h = hd / 2) applied in fp32 while dQ / dK are still unrounded.
   const float* cosT;
   const float* sinT;
+  // Optional head -> sequence return of the packed gradient (Ulysses backward): instead of dqkv, row t of local
+  // head slot s is stored into
+  //   dst[t / dst_rows][b, t % dst_rows, head(s), :]     (bf16 [B, dst_rows, dst_heads, hd] per rank)
+  // with head(s) = dst_q0 + s for q slots, dst_k0 + s for k, dst_v0 + s for v: the rows go straight from the
+  // kernels to the ranks that own those sequence chunks (peer-mapped addresses, plain 16-byte stores).
+  // n_dst == 0: off.
+  __nv_bfloat16* dst[AB_MAX_DST];
+  int n_dst, dst_rows, dst_heads, dst_q0, dst_k0, dst_v0;
 };
 
 template <int HD>
@@ -124,7 +144,7 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 // (j + hd / 2) per thread so that the transposed rotation (see AttnBwdParams) can be applied on the way.
 __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int B, int T,
                                        int Hq, int heads_total, int hd, float scale, const float* __restrict__ cosT,
-                                       const float* __restrict__ sinT) {
+                                       const float* __restrict__ sinT, const AttnBwdDst d, int dst_q0) {
   const int half = hd / 2, vec = half / 8;
   const long long total = (long long)B * Hq * T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -159,7 +179,14 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bf
         hi[k] = bb * ch[k] - a * sl[k];
       }
     }
-    __nv_bfloat16* dst = dqkv + ((b * T + t) * heads_total + h) * (long long)hd + j;
+    __nv_bfloat16* dst;
+    if (d.n > 0) {
+      const int owner = t / d.rows, tl = t - owner * d.rows;
+      if (owner >= d.n) continue;
+      dst = d.p[owner] + ((b * d.rows + tl) * d.heads + dst_q0 + h) * (long long)hd + j;
+    } else {
+      dst = dqkv + ((b * T + t) * heads_total + h) * (long long)hd + j;
+    }
     *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
     *reinterpret_cast<uint4*>(dst + half) = make_uint4(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]), pack_bf16(hi[4], hi[5]), pack_bf16(hi[6], hi[7]));
   }
@@ -192,7 +219,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const int heads_total = p.Hq + 2 * p.Hkv;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == 0 || i == 1 || i == 6 || i == 7 || i == 9) ? 8 : 1);
+    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == 0 || i == 1) ? 4 : (i == 6 || i == 7 || i == 9) ? 8 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -205,6 +232,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  if (warp < 4) {
+  reg_dec<AB_REGS_CTRL>();
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -304,9 +333,58 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         umma_commit(bar(13 + st));
       }
     }
+  }                                                 // warps 2, 3: no role (they complete warpgroup 0)
+  } else if (warp >= 12) {
+    reg_dec<AB_REGS_FLUSH>();
+    // ---------------------------------------------------------------- dQ flush warps (warps 12..15, hd 64)
+    // dQ of step `it` leaves its tensor-memory buffer here, so that the softmax warps go straight from publishing
+    // P / dS to the next step's S / dP. Each warp owns the 32 query rows of its lane quarter: [32 rows][64 columns]
+    // fp32 -> two swizzled [32][32] boxes in shared memory -> TMA reduce-add tile stores into the fp32 dQ buffer
+    // (several KV tiles add into the same query rows), one bulk operation per 4 KB instead of 256 vector atomics.
+    if (C::PIPELINED) {
+      const int q4 = warp & 3;
+      const uint32_t t_lane = tmem + ((uint32_t)(q4 * 32) << 16);
+      uint8_t* stg = sal + C::OFF_DQS + (warp - 12) * 8192;
+      const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 12) * 8192;
+      for (int it = 0; it < n_it; ++it) {
+        if (!mbar_wait(bar(8), (uint32_t)it & 1u, 32, abort_flag, p.status)) break;     // dQ(it) complete
+        tc_fence_after();
+        const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
+        const int y0 = qi * AB_TILE + q4 * 32;               // first of this warp's 32 query rows
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_lane + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS, r0);
+        tmem_ld32(t_lane + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS + 32, r1);
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // both staging boxes free again
+        __syncwarp();
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(it & 1));             // the tensor-memory buffer may take dQ of step it + 2
+        uint8_t* rowp = stg + lane * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_uint4(r0[4 * ch], r0[4 * ch + 1], r0[4 * ch + 2], r0[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(rowp + 4096 + ((ch ^ (lane & 7)) << 4)) = make_uint4(r1[4 * ch], r1[4 * ch + 1], r1[4 * ch + 2], r1[4 * ch + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (y0 < p.T) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              if (c * 32 < p.hd)
+                asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                             ::"l"((uint64_t)&tm_dq), "r"(stg_s + c * 4096), "r"(c * 32), "r"(y0), "r"(b * p.Hq + hq) : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // dQ reductions have landed
+    }
   } else {
-    // ---------------------------------------------------------------- softmax warpgroups (warps 2..9)
-    const int q4 = warp & 3, half = (warp - 2) >> 2;
+    // ---------------------------------------------------------------- softmax warpgroups (warps 4..11)
+    reg_inc<AB_REGS_SOFTMAX>();
+    const int q4 = warp & 3, half = (warp - 4) >> 2;
     const int row = q4 * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(q4 * 32) << 16);
     constexpr float LOG2E = 1.4426950408889634f;
@@ -316,8 +394,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     // part into swizzled [32][32 fp32] boxes in shared memory and one lane hands them to the TMA unit as
     // reduce-add tile stores (several KV tiles add into the same query rows), so the SM issues one bulk
     // operation per 4 KB instead of 256 vector atomics.
-    uint8_t* stg = sal + C::OFF_DQS + (warp - 2) * 4096;
-    const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 2) * 4096;
+    uint8_t* stg = sal + C::OFF_DQS + (warp - 4) * 4096;
+    const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 4) * 4096;
     auto flush_dq = [&](int it) {
       const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
       const int y0 = qi * AB_TILE + q4 * 32;                 // first of this warp's 32 query rows
@@ -357,33 +435,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       if (!mbar_wait(bar(5), par, 28, abort_flag, p.status)) { ok = false; break; }
       tc_fence_after();
       uint32_t pp[32], dd[32];                      // 64 columns of P and dS, packed bf16 pairs
-      {
-        // This thread's 64 columns of S and of dP move into registers in one pass and the tensor-memory columns
-        // are handed back BEFORE the arithmetic: the MMA warp issues S / dP of the next step as soon as the loads
-        // have landed, so those MMAs run under this step's exp / dS work instead of after it.
-        uint32_t s[64], dp[64];
-        tmem_ld32(t_lane + C::S_COL + half * 64, s);
-        tmem_ld32(t_lane + C::S_COL + half * 64 + 32, s + 32);
-        tmem_ld32(t_lane + C::DP_COL + half * 64, dp);
-        tmem_ld32(t_lane + C::DP_COL + half * 64 + 32, dp + 32);
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(t_lane + C::S_COL + half * 64 + c, s);
+        tmem_ld32(t_lane + C::DP_COL + half * 64 + c, dp);
         tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(6));         // S / dP columns may be overwritten
+        if (c == 32) {
+          // all of this thread's S / dP columns are in registers: hand the tensor-memory columns back before the
+          // second half of the arithmetic, so that the next step's S / dP MMAs can be issued under it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(6));
+        }
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
+        for (int i = 0; i < 32; i += 2) {
           const float2 x = ffma2(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, nl2);
           float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (diag) {
-            const int col = half * 64 + i;
+            const int col = half * 64 + c + i;
             if (col > row) pr.x = 0.f;
             if (col + 1 > row) pr.y = 0.f;
           }
           // dS = P (dP - delta); the softmax scale is applied once, when dQ and dK leave their accumulators
           const float2 ds = fmul2(pr, fadd2(make_float2(__uint_as_float(dp[i]), __uint_as_float(dp[i + 1])), nd2));
-          pp[i >> 1] = pack_bf16(pr.x, pr.y);
-          dd[i >> 1] = pack_bf16(ds.x, ds.y);
+          pp[(c + i) >> 1] = pack_bf16(pr.x, pr.y);
+          dd[(c + i) >> 1] = pack_bf16(ds.x, ds.y);
         }
       }
       if (it > 0) {                                 // MMAs of step it-1 done: P / dS free, dQ(it-1) ready
@@ -401,17 +479,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(7));
-      if (C::PIPELINED) {
-        if (it > 0) flush_dq(it - 1);
-      } else {
+      if (!C::PIPELINED) {                          // hd 128: dQ shares the S columns, this warp drains it itself
         if (!mbar_wait(bar(8), par, 30, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         flush_dq(it);
       }
     }
     if (ok && n_it > 0) {
-      if (C::PIPELINED) {
-        if (mbar_wait(bar(8), (uint32_t)(n_it - 1) & 1u, 31, abort_flag, p.status)) { tc_fence_after(); flush_dq(n_it - 1); } else ok = false;
+      if (C::PIPELINED) {                           // the last step's MMAs: dV, dK complete
+        if (!mbar_wait(bar(8), (uint32_t)(n_it - 1) & 1u, 31, abort_flag, p.status)) ok = false;
       }
       if (ok) {
         // dV, dK accumulators -> bf16 rows of the packed gradient tensor
@@ -423,6 +499,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           const float osc = which == 0 ? 1.f : p.scale;
           const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
           __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * p.hd + half * (HD / 2);
+          bool dst_ok = true;
+          if (p.n_dst > 0) {
+            const int owner = t_row / p.dst_rows, tl = t_row - owner * p.dst_rows;
+            dst_ok = owner < p.n_dst;
+            if (dst_ok)
+              dst = p.dst[owner] + (((long long)b * p.dst_rows + tl) * p.dst_heads + (which == 0 ? p.dst_v0 : p.dst_k0) + kvh) * p.hd
+                    + half * (HD / 2);
+          }
 #pragma unroll
           for (int c = 0; c < HD / 2; c += 32) {
             uint32_t r[32];
@@ -459,7 +543,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
                 for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(o[i]);
               }
             }
-            if (t_row < p.T && half * (HD / 2) + c < p.hd) {
+            if (t_row < p.T && dst_ok && half * (HD / 2) + c < p.hd) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint4 v;
@@ -504,9 +588,11 @@ using namespace tlm;
 
 // dq_acc: fp32 scratch [B,Hq,T,hd]; delta: fp32 scratch [B,Hq,T]. Both are owned by the caller.
 // cosT / sinT (optional, fp32 [T, hd]): the transposed RoPE is applied to dQ and dK on the way out.
-TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
+// dst_ptrs (optional, n_dst > 0): head -> sequence return, see AttnBwdParams; dqkv may then be null.
+static int attn_bwd_impl(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
                          float* dq_acc, float* delta, int B, int T, int Hq, int Hkv, int hd, float scale,
-                         const float* cosT, const float* sinT, cudaStream_t st) {
+                         const float* cosT, const float* sinT, void* const* dst_ptrs, int n_dst, int dst_rows,
+                         int dst_heads, int dst_q0, int dst_k0, int dst_v0, cudaStream_t st) {
   if (hd != 32 && hd != 64 && hd != 128) return -4;
   if (Hq % Hkv != 0) return -5;
   const long long rows = (long long)B * T * Hq;
@@ -522,8 +608,16 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   e = make_qkv_map(&mdo, dout, B, T, Hq, hd, AB_TILE);
   if (e) return e;
   if ((cosT == nullptr) != (sinT == nullptr)) return -6;
-  AttnBwdParams p{(__nv_bfloat16*)dqkv, dq_acc, lse, delta, B, T, Hq, Hkv, scale, scale * 1.4426950408889634f, status_word(), hd,
-                  cosT, sinT};
+  if (n_dst < 0 || n_dst > AB_MAX_DST || (n_dst > 0 && (dst_ptrs == nullptr || dst_rows <= 0 || (long long)dst_rows * n_dst < T)))
+    return -6;
+  if (n_dst == 0 && dqkv == nullptr) return -6;
+  AttnBwdParams p{};
+  p.dqkv = (__nv_bfloat16*)dqkv; p.dq_acc = dq_acc; p.lse = lse; p.delta = delta; p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status_word(); p.hd = hd; p.cosT = cosT; p.sinT = sinT;
+  p.n_dst = n_dst; p.dst_rows = dst_rows; p.dst_heads = dst_heads; p.dst_q0 = dst_q0; p.dst_k0 = dst_k0; p.dst_v0 = dst_v0;
+  AttnBwdDst dd{};
+  dd.n = n_dst; dd.rows = dst_rows; dd.heads = dst_heads;
+  for (int i = 0; i < n_dst; ++i) { p.dst[i] = (__nv_bfloat16*)dst_ptrs[i]; dd.p[i] = p.dst[i]; }
   CUtensorMap mdq;                                     // fp32 [B*Hq, T, hd] accumulator, box 32 x 32 x 1
   {
     uint64_t dims[3] = {(uint64_t)hd, (uint64_t)T, (uint64_t)B * Hq};
@@ -537,7 +631,24 @@ TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const
   long long items = rows * (hd / 16);
   int cb = (int)((items + 255) / 256);
   if (cb > num_sms() * 16) cb = num_sms() * 16;
-  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale, cosT, sinT);
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale, cosT, sinT, dd, dst_q0);
   count_launch();
   return launch_status();
+}
+
+TLM_API int tlm_attn_bwd(const void* qkv, const void* o, const void* dout, const float* lse, void* dqkv,
+                         float* dq_acc, float* delta, int B, int T, int Hq, int Hkv, int hd, float scale,
+                         const float* cosT, const float* sinT, cudaStream_t st) {
+  return attn_bwd_impl(qkv, o, dout, lse, dqkv, dq_acc, delta, B, T, Hq, Hkv, hd, scale, cosT, sinT, nullptr, 0, 0, 0, 0, 0, 0, st);
+}
+
+// Attention backward whose gradient rows leave for the sequence owners' packed buffers (see AttnBwdParams):
+// dst_ptrs[r]: bf16 [B, dst_rows, dst_heads, hd] on rank r; q slot s -> head dst_q0 + s, k -> dst_k0 + s, v -> dst_v0 + s.
+TLM_API int tlm_attn_bwd_scatter(const void* qkv, const void* o, const void* dout, const float* lse, float* dq_acc,
+                                 float* delta, int B, int T, int Hq, int Hkv, int hd, float scale, const float* cosT,
+                                 const float* sinT, void* const* dst_ptrs, int n_dst, int dst_rows, int dst_heads,
+                                 int dst_q0, int dst_k0, int dst_v0, cudaStream_t st) {
+  if (n_dst < 1) return -6;
+  return attn_bwd_impl(qkv, o, dout, lse, nullptr, dq_acc, delta, B, T, Hq, Hkv, hd, scale, cosT, sinT, dst_ptrs, n_dst,
+                       dst_rows, dst_heads, dst_q0, dst_k0, dst_v0, st);
 }

@@ -37,12 +37,12 @@ __device__ __forceinline__ bool flag_exchange(const PeerPtrs& flags, int rank, i
     const int r = threadIdx.x;
     if (do_signal) {
       __threadfence_system();
-      st_release_sys(reinterpret_cast<int*>(flags.p[r]) + rank, epoch);
+      proto::announce<DeviceMem>(reinterpret_cast<int*>(flags.p[r]), rank, epoch);
     }
     const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + r;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+    while (!proto::reached<DeviceMem>(mine, epoch)) {
       if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
         report_status(status, (site << 8) | (unsigned int)r);
         s_ok = 0;
@@ -61,7 +61,7 @@ __device__ __forceinline__ bool flag_exchange(const PeerPtrs& flags, int rank, i
 // the launches can be recorded in a CUDA graph and replayed.
 constexpr int EPOCH_SLOT = 32;
 __device__ __forceinline__ int resolve_epoch(const PeerPtrs& flags, int rank, int epoch) {
-  return epoch > 0 ? epoch : reinterpret_cast<volatile int*>(flags.p[rank])[EPOCH_SLOT] + 1;
+  return epoch > 0 ? epoch : (int)((unsigned int)reinterpret_cast<volatile int*>(flags.p[rank])[EPOCH_SLOT] + 1u);
 }
 __device__ __forceinline__ void commit_epoch(const PeerPtrs& flags, int rank, int epoch_arg, int epoch_used) {
   if (epoch_arg <= 0) reinterpret_cast<volatile int*>(flags.p[rank])[EPOCH_SLOT] = epoch_used;
@@ -80,7 +80,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int n, int epoch_a
 __global__ void peer_allreduce_scalar_kernel(PeerPtrs slots, PeerPtrs flags, const float* __restrict__ in, float* __restrict__ out,
                                              float scale, int rank, int n, int epoch_arg, unsigned int* status) {
   const int epoch = resolve_epoch(flags, rank, epoch_arg);
-  const int par = (epoch & 1) * MAX_PEERS;
+  const int par = proto::parity_slot(epoch, MAX_PEERS, 0);
   if ((int)threadIdx.x < n) reinterpret_cast<volatile float*>(slots.p[threadIdx.x])[par + rank] = *in;
   const bool ok = flag_exchange(flags, rank, n, epoch, true, status, 44);
   if (threadIdx.x == 0) {
@@ -99,7 +99,7 @@ __global__ void peer_allreduce_scalar_kernel(PeerPtrs slots, PeerPtrs flags, con
 __global__ void wait_flag_kernel(const int* flag, int expect, unsigned long long limit_ns, unsigned int* status) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
-  while ((int)(ld_acquire_sys(flag) - expect) < 0) {
+  while (!proto::reached<DeviceMem>(flag, expect)) {
     if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) {
       report_status(status, (42u << 8) | 1u);
       break;
@@ -289,13 +289,9 @@ __global__ void adamw_gather_kernel(float* __restrict__ p, float* __restrict__ m
     if (threadIdx.x == 0) {
       int* mine = reinterpret_cast<int*>(ready.p[rank]);
       const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int*>(mine + READY_CNT0 + bucket), 1u);
-      if (prev == gridDim.x - 1) {
-        mine[READY_CNT0 + bucket] = 0;
-        __threadfence_system();
-        const int done = reinterpret_cast<volatile int*>(mine)[READY_EPOCH0 + bucket] + 1;
-        for (int r = 0; r < n; ++r) st_release_sys(reinterpret_cast<int*>(ready.p[r]) + bucket * READY_STRIDE + rank, done);
-        reinterpret_cast<volatile int*>(mine)[READY_EPOCH0 + bucket] = done;
-      }
+      if (prev == gridDim.x - 1) __threadfence_system();           // acquire side of the count: see every block's stores
+      const proto::ReadyLayout layout{READY_STRIDE, READY_EPOCH0, READY_CNT0};
+      proto::publish_if_last<DeviceMem>(reinterpret_cast<int* const*>(ready.p), n, rank, bucket, layout, prev, gridDim.x);
     }
   }
 }
@@ -357,8 +353,10 @@ TLM_API int tlm_reduce_scatter(void* const* grad_ptrs, const float* mc_grads, vo
                                int epoch, int max_blocks, cudaStream_t st) {
   if (n > MAX_PEERS || len % 4 != 0 || lo % 4 != 0) return -6;
   const int blocks = rs_grid(max_blocks);
-  reduce_scatter_kernel<<<blocks, 512, 0, st>>>(to_ptrs(grad_ptrs, n), mc_grads, to_ptrs(flag_ptrs, n), out, partials, lo,
-                                                len, rank, n, epoch, status_word());
+  // Under the backward pass (max_blocks > 0) the blocks are small (128 threads, a few thousand registers), so that
+  // they fit on an SM next to a resident GEMM block instead of waiting for it or keeping the next one out.
+  reduce_scatter_kernel<<<blocks, max_blocks > 0 ? 128 : 512, 0, st>>>(to_ptrs(grad_ptrs, n), mc_grads, to_ptrs(flag_ptrs, n),
+                                                                      out, partials, lo, len, rank, n, epoch, status_word());
   sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
   count_launch(2);
   return launch_status();
@@ -377,7 +375,7 @@ TLM_API int tlm_reduce_scatter_bf16(const float* grads, void* wire_local, long l
   if (cb > cap) cb = cap;
   cast_bf16_kernel<<<(int)(cb < 1 ? 1 : cb), 256, 0, st>>>(grads + cast_lo, (__nv_bfloat16*)wire_local + cast_lo, cast_n);
   const int blocks = rs_grid(max_blocks);
-  reduce_scatter_bf16_kernel<<<blocks, 512, 0, st>>>(to_ptrs(wire_ptrs, n), (const __nv_bfloat16*)mc_wire, to_ptrs(flag_ptrs, n),
+  reduce_scatter_bf16_kernel<<<blocks, max_blocks > 0 ? 128 : 512, 0, st>>>(to_ptrs(wire_ptrs, n), (const __nv_bfloat16*)mc_wire, to_ptrs(flag_ptrs, n),
                                                      out, partials, lo, len, rank, n, epoch, status_word());
   sum_partials_kernel<<<1, 256, 0, st>>>(partials, blocks, sumsq_out, to_ptrs(flag_ptrs, n), rank, epoch);
   count_launch(3);

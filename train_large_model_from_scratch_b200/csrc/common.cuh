@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flag_protocol.h"
+
 #define TLM_API extern "C" __attribute__((visibility("default")))
 
 namespace tlm {
@@ -60,6 +62,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
 // all of r's parameter stores of that bucket's update have been issued and fenced; it holds the number of updates
 // done so far. Words READY_EPOCH0 + bucket (how many updates this rank itself has done: the value consumers wait
 // for) and READY_CNT0 + bucket (blocks-finished counter of the update kernel) are only used locally.
+// Memory policy of the flag protocols (flag_protocol.h) on the device: system-scope acquire loads / release stores.
+struct DeviceMem {
+  static __device__ __forceinline__ int load_acquire(const int* p) { return ld_acquire_sys(p); }
+  static __device__ __forceinline__ void store_release(int* p, int v) { st_release_sys(p, v); }
+};
+
 constexpr int READY_STRIDE = 16, READY_MAX_BUCKETS = 16;
 constexpr int READY_EPOCH0 = READY_STRIDE * READY_MAX_BUCKETS, READY_CNT0 = READY_EPOCH0 + READY_MAX_BUCKETS;
 constexpr int READY_INTS = 512;
@@ -128,10 +136,10 @@ __device__ __forceinline__ bool wait_params_ready(const int* ready_local, int bu
   bool ok = true;
   if (lane < n) {
     const int expect = reinterpret_cast<const volatile int*>(ready_local)[READY_EPOCH0 + bucket];
-    const int* f = ready_local + bucket * READY_STRIDE + lane;
+    const proto::ReadyLayout layout{READY_STRIDE, READY_EPOCH0, READY_CNT0};
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while ((int)(ld_acquire_sys(f) - expect) < 0) {
+    while (!proto::ready_from<DeviceMem>(ready_local, bucket, layout, lane, expect)) {
       if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
         report_status(status, (site << 8) | (unsigned int)lane);
         ok = false;

@@ -141,9 +141,8 @@ class Attention(nn.Module):
             from ...parallel.sequence_parallel import ulysses_peer
             if self._peer_path(h, sp) and ulysses_peer.fused_ok(Hq, Hkv, sp, hd, T_local):
                 cos_f, sin_f = self._rope_full(T_local * sp, h.device)
-                qkv_l = ulysses_peer.qkv_project_scatter(h, self._qkv_weight, Hq, Hkv, hd, B, T_local,
-                                                         self._rope_fp16(T_local, h.device), cos_f, sin_f, id(self), group)
-                y = ulysses_peer.attention_out_project(qkv_l, self.c_proj.weight, Hq, Hkv, id(self), group)
+                y = ulysses_peer.attention_block(h, self._qkv_weight, self.c_proj.weight, Hq, Hkv, hd, B, T_local,
+                                                 self._rope_fp16(T_local, h.device), cos_f, sin_f, id(self), group)
                 return y.view(shape)
         if self._qkv_weight is not None:
             qkv = F_ops.linear(h, self._qkv_weight)

@@ -63,6 +63,25 @@ def fwd_scatter(qkv: torch.Tensor, n_q: int, n_kv: int, dst_ptrs, n_dst: int, ds
     return o, lse
 
 
+def bwd_scatter(do, qkv, o, lse, n_q: int, n_kv: int, rope, dst_ptrs, n_dst: int, dst_rows: int, dst_heads: int,
+                dst_q0: int, dst_k0: int, dst_v0: int) -> None:
+    """Causal attention backward (head dims 32 / 64 / 128) whose gradient rows are stored straight into the sequence
+    owners' packed gradient tensors: row t of local q head s -> `dst[t // dst_rows][b, t % dst_rows, dst_q0 + s]`,
+    k -> `dst_k0 + s`, v -> `dst_v0 + s` (`dst_ptrs`: ctypes array of device addresses of bf16
+    `[B, dst_rows, dst_heads, hd]` tensors, typically peers' symmetric buffers). `rope = (cos, sin)` fp32 `[T, hd]`
+    or None: transposed rotation of dQ / dK on the way."""
+    B, T, _, hd = qkv.shape
+    assert _native_ok(hd) and qkv.is_contiguous()
+    do, o = do.contiguous(), o.contiguous()
+    dq_acc = torch.empty(B, n_q, T, hd, dtype=torch.float32, device=qkv.device)
+    delta = torch.empty(B, n_q, T, dtype=torch.float32, device=qkv.device)
+    cos, sin = rope if rope is not None else (None, None)
+    native._check(native.lib().tlm_attn_bwd_scatter(
+        qkv.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, T, n_q, n_kv,
+        hd, 1.0 / math.sqrt(hd), native._ptr(cos), native._ptr(sin), dst_ptrs, n_dst, dst_rows, dst_heads, dst_q0, dst_k0,
+        dst_v0, native._stream()), "attn_bwd_scatter")
+
+
 def _split(qkv, n_q, n_kv):
     q = qkv[:, :, :n_q].transpose(1, 2)
     k = qkv[:, :, n_q:n_q + n_kv].transpose(1, 2)

@@ -71,6 +71,7 @@ _SIGS = {
     "tlm_attn_fwd": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P]),
     "tlm_attn_fwd_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _I, _I, _P]),
     "tlm_attn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
+    "tlm_attn_bwd_scatter": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_barrier": (_I, [_P, _I, _I, _I, _P]),
     "tlm_wait_flag": (_I, [_P, _I, _c.c_ulonglong, _P]),
     "tlm_reduce_scatter_blocks": (_I, []),

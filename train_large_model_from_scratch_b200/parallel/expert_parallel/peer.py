@@ -35,13 +35,13 @@ class PeerMoE:
     _instance = None
 
     def __init__(self, group, num_experts: int):
-        from ..symm import symm_alloc, _Peer
+        from ..symm import alloc_flags, symm_alloc, _Peer
         self.group, self.ep, self.me = group, dist.get_world_size(group), dist.get_rank(group)
         self.E = num_experts
         self.E_l = num_experts // self.ep
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
-        self.flags = _Peer(symm_alloc(64, torch.int32, dev), group)
+        self.flags = _Peer(alloc_flags(dev), group)
         self.counts_t = symm_alloc(self.ep * num_experts, torch.int32, dev)
         self.counts = _Peer(self.counts_t, group)
         self.buffers: dict = {}

@@ -1,13 +1,16 @@
 """Ulysses seq<->head exchanges as direct stores into peer memory (CUDA).
 
 Replaces, on the GPU, the pack -> `all_to_all_single` -> unpack sequence of
-`ulysses.py` (and the reference's `model/modules/attn.py:143-171`). Three of the
-four exchanges per layer happen inside compute kernels (`_QKVProjectScatter`:
-QKV projection + RoPE + seq->head in the GEMM epilogue; `_AttnOutProject`:
-head->seq in the attention epilogue, and in backward seq->head in the epilogue
-of the output projection's data-gradient GEMM); the packed gradient's way back
-is one scatter kernel (`csrc/ulysses.cu`) that also applies the transposed
-rotation. Every exchange ends with a flag barrier:
+`ulysses.py` (and the reference's `model/modules/attn.py:143-171`). On the fused
+path (`_UlyssesAttention`) all four exchanges of a layer happen inside compute
+kernels: QKV projection + RoPE + seq->head in the GEMM epilogue; head->seq of O
+in the attention epilogue; in backward seq->head of dO in the epilogue of the
+output projection's data-gradient GEMM, and head->seq of the packed gradient
+(with the transposed rotation) from the attention-backward kernels themselves.
+Shapes the head-scatter GEMM epilogue does not take (head dim 32, sequence
+chunks that are not a multiple of 32) use `_SeqToHead` / `_HeadToSeq`, whose
+exchanges are one scatter kernel each (`csrc/ulysses.cu`). Every exchange ends
+with a flag barrier:
 
   forward   qkv  [B, T_l, Hq+2Hkv, hd] --RoPE + scatter--> every head owner's
             [B, T_full, q_l+2kv_l, hd]; attention; o [B, T_full, q_l, hd]
@@ -62,12 +65,12 @@ class PeerState:
     _instance = None
 
     def __init__(self, group):
-        from ..symm import symm_alloc, _Peer
+        from ..symm import alloc_flags, _Peer
         self.group = group
         self.sp = dist.get_world_size(group)
         self.me = dist.get_rank(group)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.flags_t = symm_alloc(64, torch.int32, dev)
+        self.flags_t = alloc_flags(dev)
         self.flags = _Peer(self.flags_t, group)
         self.buffers: dict = {}
         self.tables: dict = {}
@@ -188,86 +191,72 @@ def _dqkv_table(st: PeerState, n_q, n_kv, q_l, kv_l, device) -> torch.Tensor:
     return st.table(("h2s_dqkv", n_q, n_kv), rows, device)
 
 
-class _QKVProjectScatter(torch.autograd.Function):
-    """`h [B*T_l, D]` -> rotated `[B, T_full, q_l + 2 kv_l, hd]` of my heads, with ONE kernel doing the
-    projection GEMM, RoPE and the seq->head exchange: the GEMM epilogue stores every (32-row, head) tile with
-    a TMA tile store into the memory of the rank that owns the head (`csrc/gemm.cu`, head-scatter epilogue).
-    Backward: the packed gradient returns head->seq with the transposed rotation (one scatter kernel) and
-    feeds the weight- and data-gradient GEMMs."""
+class _UlyssesAttention(torch.autograd.Function):
+    """The whole attention block under Ulysses as one autograd node, `h [B*T_l, D]` -> `[B*T_l, D]`, with all
+    four exchanges of a layer inside compute kernels:
+
+      forward   QKV GEMM epilogue: RoPE + packed layout + seq->head stores into the head owners' memory;
+                attention epilogue: head->seq stores of O into the sequence owners' memory; output GEMM.
+      backward  output-projection dgrad GEMM epilogue: seq->head stores of dO into the head owners' memory;
+                attention backward: dQ (while it is converted from its fp32 accumulator) and dK / dV (as they
+                leave tensor memory) get the transposed RoPE and are stored head->seq into the sequence owners'
+                packed gradient buffer, which feeds the QKV weight- and data-gradient GEMMs.
+
+    No stand-alone scatter kernel is left; each exchange ends with a flag barrier."""
 
     @staticmethod
-    def forward(ctx, h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
+    def forward(ctx, h, w_qkv, w_out, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
+        from ...ops import attention_cuda
         st = PeerState.get(group)
         sp, me = st.sp, st.me
         _, q_l, kv_l = ulysses.head_plan(n_q, n_kv, sp)
         hpr = q_l + 2 * kv_l
-        ex = st.buffer((layer_key, "qkv"), (B, sp * T_l, hpr, hd), h.device)
-        native.gemm_heads(h, weight, False, ex.peer.ptr_array, sp, B, T_l, sp * T_l, hpr, me * T_l, n_q, n_kv,
+        T_full = sp * T_l
+        ex_qkv = st.buffer((layer_key, "qkv"), (B, T_full, hpr, hd), h.device)
+        native.gemm_heads(h, w_qkv, False, ex_qkv.peer.ptr_array, sp, B, T_l, T_full, hpr, me * T_l, n_q, n_kv,
                           q_l, kv_l, hd, n_q + n_kv, cs_l)
         st.barrier()
-        ctx.meta = (n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd)
-        ctx.weight = weight
-        ctx.save_for_backward(h, cos_f, sin_f)
-        return _fresh(ex.tensor)
-
-    @staticmethod
-    def backward(ctx, d_full):
-        from ...ops.functional import _main_grad
-        n_q, n_kv, q_l, kv_l, layer_key, group, B, T_l, hd = ctx.meta
-        h, cos_f, sin_f = ctx.saved_tensors
-        w = ctx.weight
-        st = PeerState.get(group)
-        table = _dqkv_table(st, n_q, n_kv, q_l, kv_l, d_full.device)
-        ex = st.buffer((layer_key, "dqkv"), (B, T_l, n_q + 2 * n_kv, hd), d_full.device)
-        _scatter(st, d_full.contiguous(), ex, table, 1, cos_f, sin_f, 0)
-        d2 = ex.tensor.view(B * T_l, -1)
-        native.gemm_tn_accum(d2, h, _main_grad(w))
-        dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
-        return (dh,) + (None,) * 11
-
-
-class _AttnOutProject(torch.autograd.Function):
-    """Causal attention over my heads `[B, T_full, q_l + 2 kv_l, hd]` followed by the output projection
-    on my sequence chunk -> `[B*T_l, D]`, with both exchanges inside compute kernels:
-
-      forward   the attention epilogue stores each output row into the memory of the rank that owns the
-                row's sequence chunk (head->seq), then the output GEMM runs on the assembled rows;
-      backward  the data-gradient GEMM `dy @ W` has the head-scatter epilogue, so d(o) goes straight from
-                the accumulator to the head owners (seq->head), where the attention backward consumes it.
-    """
-
-    @staticmethod
-    def forward(ctx, qkv_l, weight, n_q, n_kv, layer_key, group):
-        from ...ops import attention_cuda
-        st = PeerState.get(group)
-        sp, me = st.sp, st.me
-        B, T_full, _, hd = qkv_l.shape
-        q_l, kv_l, T_l = n_q // sp, n_kv // sp, T_full // sp
-        ex = st.buffer((layer_key, "o"), (B, T_l, n_q, hd), qkv_l.device)
-        o, lse = attention_cuda.fwd_scatter(qkv_l, q_l, kv_l, ex.peer.ptr_array, sp, T_l, n_q, me * q_l)
+        qkv_l = ex_qkv.tensor
+        ex_o = st.buffer((layer_key, "o"), (B, T_l, n_q, hd), h.device)
+        o, lse = attention_cuda.fwd_scatter(qkv_l, q_l, kv_l, ex_o.peer.ptr_array, sp, T_l, n_q, me * q_l)
         st.barrier()
-        o_seq = ex.tensor.view(B * T_l, n_q * hd)
-        ctx.meta = (n_q, q_l, kv_l, layer_key, group, B, T_full, T_l, hd)
-        ctx.weight = weight
-        ctx.save_for_backward(qkv_l, o, lse, o_seq)
-        return native.gemm_nt(o_seq, weight)
+        o_seq = ex_o.tensor.view(B * T_l, n_q * hd)
+        ctx.meta = (n_q, n_kv, q_l, kv_l, hd, layer_key, group, B, T_l)
+        ctx.w_qkv, ctx.w_out = w_qkv, w_out
+        ctx.save_for_backward(h, qkv_l, o, lse, o_seq, cos_f, sin_f)
+        return native.gemm_nt(o_seq, w_out)
 
     @staticmethod
     def backward(ctx, dy):
         from ...ops import attention_cuda
         from ...ops.functional import _main_grad
-        n_q, q_l, kv_l, layer_key, group, B, T_full, T_l, hd = ctx.meta
-        qkv_l, o, lse, o_seq = ctx.saved_tensors
-        w = ctx.weight
+        n_q, n_kv, q_l, kv_l, hd, layer_key, group, B, T_l = ctx.meta
+        h, qkv_l, o, lse, o_seq, cos_f, sin_f = ctx.saved_tensors
+        w_qkv, w_out = ctx.w_qkv, ctx.w_out
         st = PeerState.get(group)
+        sp, me = st.sp, st.me
+        T_full = sp * T_l
         dy = dy.contiguous()
-        native.gemm_tn_accum(dy, o_seq, _main_grad(w))
-        ex = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), dy.device)
-        native.gemm_heads(dy, w, True, ex.peer.ptr_array, st.sp, B, T_l, T_full, q_l, st.me * T_l, n_q, 0, q_l, 1,
+        native.gemm_tn_accum(dy, o_seq, _main_grad(w_out))
+        ex_do = st.buffer((layer_key, "do"), (B, T_full, q_l, hd), dy.device)
+        native.gemm_heads(dy, w_out, True, ex_do.peer.ptr_array, sp, B, T_l, T_full, q_l, me * T_l, n_q, 0, q_l, 1,
                           hd, 0, None)
         st.barrier()
-        dqkv = attention_cuda.bwd(ex.tensor, qkv_l, o, lse, q_l, kv_l, True)
-        return dqkv, None, None, None, None, None
+        Ht = n_q + 2 * n_kv
+        ex_d = st.buffer((layer_key, "dqkv"), (B, T_l, Ht, hd), dy.device)
+        attention_cuda.bwd_scatter(ex_do.tensor, qkv_l, o, lse, q_l, kv_l, (cos_f, sin_f), ex_d.peer.ptr_array, sp, T_l, Ht,
+                                   me * q_l, n_q + me * kv_l, n_q + n_kv + me * kv_l)
+        st.barrier()
+        d2 = ex_d.tensor.view(B * T_l, -1)
+        native.gemm_tn_accum(d2, h, _main_grad(w_qkv))
+        dh = native.gemm_nn(d2, w_qkv) if ctx.needs_input_grad[0] else None
+        return (dh,) + (None,) * 12
+
+
+def attention_block(h, w_qkv, w_out, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
+    """`cs_l` = `native.rope_table_fp16` of this rank's positions; `cos_f` / `sin_f`: fp32 tables of the full sequence."""
+    return _UlyssesAttention.apply(h, w_qkv, w_out, n_q, n_kv, hd, B, T_l, cs_l, cos_f.contiguous(), sin_f.contiguous(),
+                                   layer_key, group)
 
 
 def fused_ok(n_q: int, n_kv: int, sp: int, hd: int, T_l: int) -> bool:
@@ -275,15 +264,6 @@ def fused_ok(n_q: int, n_kv: int, sp: int, hd: int, T_l: int) -> bool:
     import os
     return (supported(n_q, n_kv, sp, hd) and native.heads_epilogue_ok(hd, T_l, sp)
             and os.environ.get("TLM_SP_FUSED", "1") != "0")       # 0: keep the stand-alone scatter kernels
-
-
-def qkv_project_scatter(h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
-    """`cs_l` = `native.rope_table_fp16` of this rank's positions; `cos_f` / `sin_f`: fp32 tables of the full sequence."""
-    return _QKVProjectScatter.apply(h, weight, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group)
-
-
-def attention_out_project(qkv_l, weight, n_q, n_kv, layer_key, group):
-    return _AttnOutProject.apply(qkv_l, weight, n_q, n_kv, layer_key, group)
 
 
 def seq_to_head(qkv, n_q, n_kv, cos_l, sin_l, cos_f, sin_f, layer_key, group):

@@ -39,11 +39,64 @@ import torch.distributed as dist
 from ..ops import native
 
 
+# Debug aids that stand in for a device-side memory checker (both off by default):
+#   TLM_SYMM_CANARY=1  every symmetric buffer gets guard bands in front of and behind its payload, filled with a
+#                      pattern that `check_guards()` verifies: a peer store that misses its destination tile shows up
+#                      as a damaged band instead of silent corruption of a neighbouring allocation.
+#   TLM_EPOCH0=<int>   first value of every flag epoch counter (default 0). An odd value swaps the parity of all
+#                      double-buffered slots, a value just below 2^31 makes the counters wrap during a short run; the
+#                      results of a run must not depend on it.
+_GUARD_ELEMS = 2048
+_GUARDED: list = []
+
+
+def _canary_on() -> bool:
+    return os.environ.get("TLM_SYMM_CANARY", "0") == "1"
+
+
+def epoch0() -> int:
+    v = int(os.environ.get("TLM_EPOCH0", "0"))
+    return ((v + 2 ** 31) % 2 ** 32) - 2 ** 31          # as int32
+
+
+def _guard_pattern(dtype: torch.dtype):
+    return -12345 if not dtype.is_floating_point else -24672.0       # exactly representable in bf16 and fp32
+
+
 def symm_alloc(numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
     import torch.distributed._symmetric_memory as symm_mem
-    t = symm_mem.empty(numel, dtype=dtype, device=device)
-    t.zero_()
+    if not _canary_on():
+        t = symm_mem.empty(numel, dtype=dtype, device=device)
+        t.zero_()
+        return t
+    g = _GUARD_ELEMS
+    whole = symm_mem.empty(numel + 2 * g, dtype=dtype, device=device)
+    whole.fill_(_guard_pattern(dtype))
+    payload = whole[g:g + numel]
+    payload.zero_()
+    _GUARDED.append((whole, numel))
+    return payload
+
+
+def alloc_flags(device: torch.device, n: int = 64) -> torch.Tensor:
+    """Symmetric int32 flag array whose words (flags and the self-counted epoch) all start at `epoch0()`."""
+    t = symm_alloc(n, torch.int32, device)
+    if epoch0():
+        t.fill_(epoch0())
     return t
+
+
+def check_guards() -> list[str]:
+    """Damaged guard bands of this rank's symmetric buffers (empty list = intact). Call after a synchronize."""
+    bad = []
+    for i, (whole, numel) in enumerate(_GUARDED):
+        g = _GUARD_ELEMS
+        pat = _guard_pattern(whole.dtype)
+        for name, band in (("front", whole[:g]), ("back", whole[g + numel:])):
+            n_bad = int((band != pat).sum().item())
+            if n_bad:
+                bad.append(f"buffer {i} ({whole.dtype}, {numel} elements): {n_bad} damaged words in the {name} guard band")
+    return bad
 
 
 def use_symm() -> bool:
@@ -59,9 +112,13 @@ class _Peer:
         self.handle = symm_mem.rendezvous(tensor, group=group)
         self.n = self.handle.world_size
         self.rank = self.handle.rank
-        ptrs = list(self.handle.buffer_ptrs)
+        # the handle describes the allocation; `tensor` may be a view into it (payload behind a guard band)
+        off = tensor.data_ptr() - int(self.handle.buffer_ptrs[self.rank])
+        assert 0 <= off < (1 << 40), "the tensor does not lie in its symmetric allocation"
+        ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
         self.ptr_array = (ctypes.c_void_p * self.n)(*ptrs)
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        mc = mc + off if mc else 0
         # TLM_NVLS: 1 = always use the NVSwitch multicast mapping, 0 = never, unset = from 4 ranks up (at 2 ranks
         # plain peer loads are faster than the in-switch reduction: 0.90 ms vs 1.64 ms on a 512 MiB shard)
         mode = os.environ.get("TLM_NVLS", "auto")
@@ -83,7 +140,9 @@ class PeerCollectives:
         self.wire_dtype = "fp32"
         self.comm_stream = None
         self._forked = False
-        self.overlap_blocks = int(os.environ.get("TLM_RS_OVERLAP_BLOCKS", "48"))
+        # grid of a reduce-scatter that runs under the backward pass (blocks of 128 threads); 0: no overlap, every
+        # bucket is reduced after the backward pass with the full grid
+        self.overlap_blocks = int(os.environ.get("TLM_RS_OVERLAP_BLOCKS", "296"))
 
     @classmethod
     def create(cls, fused, wire_dtype: str = "fp32") -> "PeerCollectives":
@@ -97,8 +156,10 @@ class PeerCollectives:
             dev = s.buf.params.device
             if self.comm_stream is None:
                 self.comm_stream = torch.cuda.Stream(device=dev, priority=-1)
-            flags = symm_alloc(64, torch.int32, dev)
+            flags = alloc_flags(dev)
             ready = symm_alloc(L.tlm_ready_ints(), torch.int32, dev)
+            if epoch0():                       # flag words and update counts start at epoch0; block counters at 0
+                ready[:L.tlm_ready_max_buckets() * 17].fill_(epoch0())
             st = {
                 "grad": _Peer(s.buf.main_grad, s.group),
                 "param": _Peer(s.buf.params, s.group),
@@ -221,7 +282,7 @@ class PeerScalar:
     def __init__(self, group, device):
         self.group = group
         self.slots_t = symm_alloc(32, torch.float32, device)
-        self.flags_t = symm_alloc(64, torch.int32, device)
+        self.flags_t = alloc_flags(device)
         self.slots, self.flags = _Peer(self.slots_t, group), _Peer(self.flags_t, group)
         dist.barrier(group=group)
 

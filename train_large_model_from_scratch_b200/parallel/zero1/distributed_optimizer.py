@@ -210,7 +210,7 @@ class FusedAdamW:
         """Backward pass has left layer group `g`: on the step's last micro-step the gradients of the group's
         buckets are final, so their reduce-scatter starts now, on the communication stream, under the rest
         of the backward pass (what DDP's bucketed all-reduce gives the reference, `training/trainer.py:133,247`)."""
-        if self._comm is None or not self.last_micro_step:
+        if self._comm is None or not self.last_micro_step or self._comm.overlap_blocks <= 0:
             return
         for s in self.shards:
             if not self._comm.handles(s):
