@@ -1,6 +1,6 @@
 """Per-kernel timing against the measured roofline.
 
-    python -m benchmarks.kernels [--what gemm,mlp,attn,elementwise,moe] [--small] [--once]
+    python -m benchmarks.kernels [--what gemm,mlp,attn,elementwise,moe,lmhead,experts] [--small] [--once]
 
 Times each kernel with CUDA events on the launching stream after warm-up,
 flushing L2 (a 256 MB write) between timed launches, and prints one JSON line
@@ -158,6 +158,54 @@ def bench_attn(small: bool):
         print(json.dumps(rec), flush=True)
 
 
+def bench_lmhead(small: bool):
+    """LM head without logits: statistics pass (GEMM + log-sum-exp epilogue + fold) and gradient-tile pass."""
+    pk = _peaks().get("bf16_tflops")
+    M, V, K = (2048 if small else 8192), 50304, 1024
+    h = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(V, K, device="cuda") * 0.02).bfloat16()
+    t = torch.randint(0, V, (M,), device="cuda")
+    sc = torch.tensor(1.0 / M, device="cuda")
+    _, lse = native.linear_cross_entropy_sum(h, w, t, -100, want_lse=True)
+    out = torch.empty(M, V, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * V * K
+    for name, fn in (("lm_head loss, no logits (gemm EPI_LSE + lse_finish)", lambda: native.linear_cross_entropy_sum(h, w, t, -100)),
+                     ("lm_head gradient tiles (gemm + softmax-minus-onehot epilogue)", lambda: native.gemm_dlogits(h, w, lse, t, sc, -100, out=out)),
+                     ("lm_head logits (plain gemm_nt, for comparison)", lambda: native.gemm_nt(h, w, out=out))):
+        med, best = _time(fn)
+        rec = {"kernel": name, "M": M, "V": V, "K": K, "ms": round(med, 4), "tflops": round(fl / med / 1e9, 1)}
+        if pk:
+            rec["frac_of_measured_peak"] = round(fl / med / 1e9 / pk, 3)
+        print(json.dumps(rec), flush=True)
+
+
+def bench_experts(small: bool):
+    """MoE expert MLP on expert-grouped rows: grouped gate|up GEMM with the SwiGLU epilogue, grouped down dgrad with the
+    SwiGLU-backward epilogue (8 experts, uneven groups)."""
+    pk = _peaks().get("bf16_tflops")
+    E, D, I = 8, 1024, 2048
+    R = 4096 if small else 32768
+    base = R // E
+    counts = [base + (i % 3 - 1) * (base // 4) for i in range(E)]
+    counts[-1] += R - sum(counts)
+    rs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    dc = native.DeviceCounts(rs, max(counts))
+    x = torch.randn(R, D, device="cuda").bfloat16()
+    dy = torch.randn(R, D, device="cuda").bfloat16()
+    w_pair = (torch.randn(2 * E, I, D, device="cuda") * 0.02).bfloat16()
+    w_down = (torch.randn(E, D, I, device="cuda") * 0.02).bfloat16()
+    gu, act = native.grouped_gemm_swiglu(x, w_pair, dc)
+    for name, fn, fl in (("grouped gate|up GEMM + SwiGLU epilogue", lambda: native.grouped_gemm_swiglu(x, w_pair, dc), 2.0 * R * 2 * I * D),
+                         ("grouped gate|up GEMM, separate SwiGLU kernel", lambda: native.swiglu_fwd(native.grouped_gemm_pair_fwd(x, w_pair, dc)), 2.0 * R * 2 * I * D),
+                         ("grouped down dgrad + SwiGLU-backward epilogue", lambda: native.grouped_gemm_swiglu_bwd(dy, w_down, gu, dc), 2.0 * R * I * D),
+                         ("grouped down dgrad, separate SwiGLU-backward kernel", lambda: native.swiglu_bwd(native.grouped_gemm_nn(dy, w_down, dc), gu), 2.0 * R * I * D)):
+        med, best = _time(fn)
+        rec = {"kernel": name, "rows": R, "experts": E, "D": D, "I": I, "ms": round(med, 4), "tflops": round(fl / med / 1e9, 1)}
+        if pk:
+            rec["frac_of_measured_peak"] = round(fl / med / 1e9 / pk, 3)
+        print(json.dumps(rec), flush=True)
+
+
 def bench_moe(small: bool):
     """Routing, gather / combine and the head-scatter (QKV + RoPE) GEMM epilogue."""
     import ctypes
@@ -206,5 +254,6 @@ if __name__ == "__main__":
     _ONCE = a.once
     torch.cuda.set_device(0)
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "mlp": bench_mlp, "elementwise": bench_elementwise, "attn": bench_attn, "moe": bench_moe}[w](a.small)
+        {"gemm": bench_gemm, "mlp": bench_mlp, "elementwise": bench_elementwise, "attn": bench_attn, "moe": bench_moe,
+         "lmhead": bench_lmhead, "experts": bench_experts}[w](a.small)
     native.raise_on_device_status()

@@ -408,3 +408,104 @@ def test_moe_plan_kernel_matches_table_arithmetic(nat):
             rows = ps["send_row"][to_me]
             assert bool((back_rank[rows] == s).all())
             assert torch.equal(back_row[rows], torch.arange(orders.numel(), device="cuda")[to_me])
+
+
+@pytest.mark.parametrize("counts,I,D", [([300, 0, 129, 511], 256, 256), ([128, 128], 512, 192), ([1, 700, 3, 64, 0, 0, 257, 33], 256, 512)])
+def test_grouped_swiglu_epilogues(nat, counts, I, D):
+    """MoE expert gate|up GEMM with the SwiGLU epilogue and the down projection's data-gradient GEMM with the
+    SwiGLU-backward epilogue, per expert group (groups that end inside a 128-row tile, empty groups), against fp32."""
+    E, R = len(counts), sum(counts)
+    pad = 40                                                     # rows behind the last group: never read, never written
+    x = _rand(R + pad, D, seed=31)
+    w_pair = _rand(2 * E, I, D, seed=32, scale=0.05)
+    w_down = _rand(E, D, I, seed=33, scale=0.05)
+    dy = _rand(R + pad, D, seed=34)
+    rs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    dc = nat.DeviceCounts(rs, max(counts))
+    gu, act = nat.grouped_gemm_swiglu(x, w_pair, dc)
+    nat.raise_on_device_status()
+    r = 0
+    for e, c in enumerate(counts):
+        xe = x[r:r + c].float()
+        g, u = xe @ w_pair[e].float().t(), xe @ w_pair[E + e].float().t()
+        if c:
+            assert _rel_err(gu[r:r + c, :I], g) < 6e-3 and _rel_err(gu[r:r + c, I:], u) < 6e-3
+            gb, ub = gu[r:r + c, :I].float(), gu[r:r + c, I:].float()
+            assert _rel_err(act[r:r + c], torch.nn.functional.silu(gb) * ub) < 6e-3
+        r += c
+    # backward: d(gate_up) from dy, w_down and the saved gate_up
+    dgu = nat.grouped_gemm_swiglu_bwd(dy, w_down, gu, dc)
+    nat.raise_on_device_status()
+    r = 0
+    for e, c in enumerate(counts):
+        if c:
+            dact = (dy[r:r + c].float() @ w_down[e].float()).to(torch.bfloat16).float()
+            g, u = gu[r:r + c, :I].float(), gu[r:r + c, I:].float()
+            sig = torch.sigmoid(g)
+            ref = torch.cat([dact * u * sig * (1 + g * (1 - sig)), dact * g * sig], -1)
+            assert _rel_err(dgu[r:r + c], ref) < 8e-3
+        r += c
+
+
+@pytest.mark.parametrize("M,V,K", [(300, 50304, 256), (128, 2048, 128), (1000, 33000, 512)])
+def test_lm_head_loss_without_logits(nat, M, V, K):
+    """Loss of the LM head from (max, sum-of-exp) statistics kept in the logits GEMM's epilogue, no logits in memory:
+    against fp32 `log_softmax` of the bf16-rounded logits, with ignored rows, at the 50304 vocabulary (its last
+    256-column tile is half empty)."""
+    h, w = _rand(M, K, seed=41), _rand(V, K, seed=42, scale=0.3)
+    t = torch.randint(0, V, (M,), device="cuda")
+    t[::7] = -100
+    t[5] = V - 1
+    loss, lse = nat.linear_cross_entropy_sum(h, w, t, -100, want_lse=True)
+    nat.raise_on_device_status()
+    # the statistics are taken of the bf16-rounded logits; the GEMM that stores logits rounds the same accumulators
+    # (a float reference GEMM sums in another order and lands on the other side of a bf16 rounding now and then)
+    logits = nat.gemm_nt(h, w).float()
+    assert _rel_err(logits, h.float() @ w.float().t()) < 6e-3
+    ref = torch.nn.functional.cross_entropy(logits, t, ignore_index=-100, reduction="sum")
+    torch.testing.assert_close(loss, ref, rtol=2e-4, atol=1e-2)
+    torch.testing.assert_close(lse, torch.logsumexp(logits, -1), rtol=1e-4, atol=2e-3)
+    # and through the differentiable op in no-grad mode (the evaluation path)
+    from train_large_model_from_scratch_b200.ops import functional as F_ops
+    with torch.no_grad():
+        got = F_ops.linear_cross_entropy(h, w, t, torch.tensor(1.0, device="cuda"), -100)
+    torch.testing.assert_close(got, ref, rtol=2e-4, atol=1e-2)
+
+
+@pytest.mark.parametrize("M,V,K", [(300, 50304, 256), (520, 2048, 128)])
+def test_lm_head_gradient_tiles_from_recomputed_logits(nat, M, V, K):
+    """Second pass of the LM head without logits: `scale * (softmax - onehot)` written by the logits GEMM's epilogue
+    from the rows' log-sum-exp, against autograd of fp32 cross-entropy on the same bf16 logits."""
+    h, w = _rand(M, K, seed=43), _rand(V, K, seed=44, scale=0.3)
+    t = torch.randint(0, V, (M,), device="cuda")
+    t[::5] = -100
+    scale = torch.tensor(0.37, device="cuda")
+    loss, lse = nat.linear_cross_entropy_sum(h, w, t, -100, want_lse=True)
+    dl = nat.gemm_dlogits(h, w, lse, t, scale, -100)
+    nat.raise_on_device_status()
+    lf = nat.gemm_nt(h, w).float().requires_grad_()
+    (torch.nn.functional.cross_entropy(lf, t, ignore_index=-100, reduction="sum") * 0.37).backward()
+    assert _rel_err(dl, lf.grad) < 8e-3
+    assert (dl[::5] == 0).all()
+
+
+def test_lm_head_recompute_mode_matches_in_place_mode(nat, monkeypatch):
+    from train_large_model_from_scratch_b200.ops import functional as F_ops
+    M, V, K = 4096 + 512, 8192, 256
+    h0, w0 = _rand(M, K, seed=45), _rand(V, K, seed=46, scale=0.2)
+    t = torch.randint(0, V, (M,), device="cuda")
+    t[::9] = -100
+    out = {}
+    for mode in ("inplace", "recompute"):
+        monkeypatch.setenv("TLM_LM_HEAD", mode)
+        h = h0.clone().requires_grad_()
+        w = w0.clone().requires_grad_()
+        w.main_grad = torch.zeros(V, K, device="cuda")
+        gs = torch.tensor(1.0 / M, device="cuda")
+        loss = F_ops.linear_cross_entropy(h, w, t, gs, -100) * gs
+        loss.backward()
+        nat.raise_on_device_status()
+        out[mode] = (loss.detach().clone(), h.grad.clone(), w.main_grad.clone())
+    torch.testing.assert_close(out["inplace"][0], out["recompute"][0], rtol=1e-4, atol=1e-4)
+    assert _rel_err(out["recompute"][1], out["inplace"][1]) < 1e-2
+    assert _rel_err(out["recompute"][2], out["inplace"][2]) < 1e-2

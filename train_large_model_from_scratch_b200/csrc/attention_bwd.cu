@@ -21,21 +21,21 @@
 //      TMA reduce-add tile stores because several KV tiles contribute to one query row.
 //      For hd = 64 the next step's S / dP MMAs are issued while the softmax
 //      warps still work on the current step.
-//   3. dq (fp32, [B,Hq,T,hd]) -> bf16 into dqkv.
+//   3. dq (fp32, [B,Hq,T,hd]) -> bf16 into dqkv; with RoPE tables this pass also applies the transposed rotation to
+//      dQ (from the fp32 accumulator) and to the dK slots the main kernel wrote, so the packed gradient that leaves
+//      is the gradient of the UN-rotated q and k and no separate RoPE pass runs.
+// A second instantiation of the main kernel (SCATTER) serves Ulysses sequence parallelism: its dK / dV epilogue
+// rotates dK itself and stores the rows straight into the sequence owners' packed gradient buffers, and the
+// conversion pass does the same for dQ. The plain instantiation carries none of that code: this kernel's main loop
+// is sensitive to anything that changes its register allocation, and in-step timing (not the isolated kernel
+// benchmark) decides what stays in it.
 // Every wait is bounded; on a timeout the CTA records a status code, leaves its
 // loops and still releases its tensor memory.
 #include "common.cuh"
 
 namespace tlm {
 
-constexpr int AB_TILE = 128, AB_MAX_DST = 8;
-// Four warpgroups: 0 = TMA producer (warp 0) + MMA issuer (warp 1), 1 and 2 = softmax (the two column halves),
-// 3 = dQ flush. Registers are moved from the light warpgroups to the softmax ones with setmaxnreg.
-constexpr int AB_THREADS = 512;
-constexpr int AB_REGS_CTRL = 104, AB_REGS_FLUSH = 88, AB_REGS_SOFTMAX = 160;   // 128 * (104 + 88) + 256 * 160 = 65536
-
-template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+constexpr int AB_TILE = 128, AB_THREADS = 320, AB_MAX_DST = 8;
 
 struct AttnBwdDst {
   __nv_bfloat16* p[AB_MAX_DST];
@@ -51,17 +51,15 @@ struct AttnBwdParams {
   float scale, scale_log2;
   unsigned int* status;
   int hd;                   // head dim in memory; 32 runs on the HD = 64 kernel with zero-filled upper columns
-  // Optional transposed RoPE on the way out: with tables cos / sin [T, hd] (fp32, row = position) the kernels
-  // return the gradient of the UN-rotated q and k, i.e. dx[j] = dy[j] c[j] + dy[j+h] s[j+h] and
-  // dx[j+h] = dy[j+h] c[j+h] - dy[j] s[j] (h = hd / 2) applied in fp32 while dQ / dK are still unrounded.
+  // Transposed RoPE on the way out (tables cos / sin [T, hd], fp32, row = position; nullptr: off):
+  //   dx[j] = dy[j] c[j] + dy[j+h] s[j+h],  dx[j+h] = dy[j+h] c[j+h] - dy[j] s[j]   (h = hd / 2).
   const float* cosT;
   const float* sinT;
-  // Optional head -> sequence return of the packed gradient (Ulysses backward): instead of dqkv, row t of local
+  // SCATTER instantiation only: head -> sequence return of the packed gradient (Ulysses backward). Row t of local
   // head slot s is stored into
   //   dst[t / dst_rows][b, t % dst_rows, head(s), :]     (bf16 [B, dst_rows, dst_heads, hd] per rank)
-  // with head(s) = dst_q0 + s for q slots, dst_k0 + s for k, dst_v0 + s for v: the rows go straight from the
-  // kernels to the ranks that own those sequence chunks (peer-mapped addresses, plain 16-byte stores).
-  // n_dst == 0: off.
+  // with head(s) = dst_q0 + s for q slots, dst_k0 + s for k, dst_v0 + s for v (peer-mapped addresses, plain
+  // 16-byte stores).
   __nv_bfloat16* dst[AB_MAX_DST];
   int n_dst, dst_rows, dst_heads, dst_q0, dst_k0, dst_v0;
 };
@@ -142,24 +140,38 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 
 // dq_acc (fp32 [B, Hq, T, hd]) * scale -> bf16 q-head slots of dqkv, 8 low columns and their 8 partner columns
 // (j + hd / 2) per thread so that the transposed rotation (see AttnBwdParams) can be applied on the way.
+// `rot_k` (only without a head -> sequence return): the Hkv k-head slots of dqkv, written as bf16 by the main kernel, are
+// rotated in place by further work items (heads Hq .. Hq + Hkv - 1).
 __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int B, int T,
                                        int Hq, int heads_total, int hd, float scale, const float* __restrict__ cosT,
-                                       const float* __restrict__ sinT, const AttnBwdDst d, int dst_q0) {
+                                       const float* __restrict__ sinT, const AttnBwdDst d, int dst_q0, int rot_k) {
   const int half = hd / 2, vec = half / 8;
-  const long long total = (long long)B * Hq * T * vec;
+  const int heads = Hq + rot_k;
+  const long long total = (long long)B * heads * T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int j = (int)(i % vec) * 8;
     long long r = i / vec;
     const int t = (int)(r % T); r /= T;
-    const int h = (int)(r % Hq); const long long b = r / Hq;
-    const float* src = dq_acc + (((long long)b * Hq + h) * T + t) * hd + j;
+    const int h = (int)(r % heads); const long long b = r / heads;
     float lo[8], hi[8];
-    *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
-    *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
-    *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + half);
-    *reinterpret_cast<float4*>(hi + 4) = *reinterpret_cast<const float4*>(src + half + 4);
+    if (h < Hq) {
+      const float* src = dq_acc + (((long long)b * Hq + h) * T + t) * hd + j;
+      *reinterpret_cast<float4*>(lo) = *reinterpret_cast<const float4*>(src);
+      *reinterpret_cast<float4*>(lo + 4) = *reinterpret_cast<const float4*>(src + 4);
+      *reinterpret_cast<float4*>(hi) = *reinterpret_cast<const float4*>(src + half);
+      *reinterpret_cast<float4*>(hi + 4) = *reinterpret_cast<const float4*>(src + half + 4);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) { lo[k] *= scale; hi[k] *= scale; }
+      for (int k = 0; k < 8; ++k) { lo[k] *= scale; hi[k] *= scale; }
+    } else {                                             // a k head: bf16 in, rotated bf16 out, same place
+      const __nv_bfloat16* src = dqkv + ((b * T + t) * heads_total + h) * (long long)hd + j;
+      const uint4 a = *reinterpret_cast<const uint4*>(src), c = *reinterpret_cast<const uint4*>(src + half);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = unpack_bf16(aw[k]), y = unpack_bf16(cw[k]);
+        lo[2 * k] = x.x; lo[2 * k + 1] = x.y; hi[2 * k] = y.x; hi[2 * k + 1] = y.y;
+      }
+    }
     if (cosT != nullptr) {
       const float* c = cosT + (long long)t * hd + j;
       const float* sn = sinT + (long long)t * hd + j;
@@ -192,7 +204,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ dq_acc, __nv_bf
   }
 }
 
-template <int HD>
+template <int HD, bool SCATTER>
 __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams p) {
@@ -219,7 +231,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const int heads_total = p.Hq + 2 * p.Hkv;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == 0 || i == 1) ? 4 : (i == 6 || i == 7 || i == 9) ? 8 : 1);
+    for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i == 0 || i == 1 || i == 6 || i == 7 || i == 9) ? 8 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -232,8 +244,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
-  reg_dec<AB_REGS_CTRL>();
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -333,58 +343,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         umma_commit(bar(13 + st));
       }
     }
-  }                                                 // warps 2, 3: no role (they complete warpgroup 0)
-  } else if (warp >= 12) {
-    reg_dec<AB_REGS_FLUSH>();
-    // ---------------------------------------------------------------- dQ flush warps (warps 12..15, hd 64)
-    // dQ of step `it` leaves its tensor-memory buffer here, so that the softmax warps go straight from publishing
-    // P / dS to the next step's S / dP. Each warp owns the 32 query rows of its lane quarter: [32 rows][64 columns]
-    // fp32 -> two swizzled [32][32] boxes in shared memory -> TMA reduce-add tile stores into the fp32 dQ buffer
-    // (several KV tiles add into the same query rows), one bulk operation per 4 KB instead of 256 vector atomics.
-    if (C::PIPELINED) {
-      const int q4 = warp & 3;
-      const uint32_t t_lane = tmem + ((uint32_t)(q4 * 32) << 16);
-      uint8_t* stg = sal + C::OFF_DQS + (warp - 12) * 8192;
-      const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 12) * 8192;
-      for (int it = 0; it < n_it; ++it) {
-        if (!mbar_wait(bar(8), (uint32_t)it & 1u, 32, abort_flag, p.status)) break;     // dQ(it) complete
-        tc_fence_after();
-        const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
-        const int y0 = qi * AB_TILE + q4 * 32;               // first of this warp's 32 query rows
-        uint32_t r0[32], r1[32];
-        tmem_ld32(t_lane + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS, r0);
-        tmem_ld32(t_lane + C::DQ_COL + (uint32_t)(it & 1) * C::DQ_BUF_COLS + 32, r1);
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // both staging boxes free again
-        __syncwarp();
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(it & 1));             // the tensor-memory buffer may take dQ of step it + 2
-        uint8_t* rowp = stg + lane * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_uint4(r0[4 * ch], r0[4 * ch + 1], r0[4 * ch + 2], r0[4 * ch + 3]);
-          *reinterpret_cast<uint4*>(rowp + 4096 + ((ch ^ (lane & 7)) << 4)) = make_uint4(r1[4 * ch], r1[4 * ch + 1], r1[4 * ch + 2], r1[4 * ch + 3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (y0 < p.T) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-              if (c * 32 < p.hd)
-                asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-                             ::"l"((uint64_t)&tm_dq), "r"(stg_s + c * 4096), "r"(c * 32), "r"(y0), "r"(b * p.Hq + hq) : "memory");
-          }
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-      }
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // dQ reductions have landed
-    }
   } else {
-    // ---------------------------------------------------------------- softmax warpgroups (warps 4..11)
-    reg_inc<AB_REGS_SOFTMAX>();
-    const int q4 = warp & 3, half = (warp - 4) >> 2;
+    // ---------------------------------------------------------------- softmax warpgroups (warps 2..9)
+    const int q4 = warp & 3, half = (warp - 2) >> 2;
     const int row = q4 * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(q4 * 32) << 16);
     constexpr float LOG2E = 1.4426950408889634f;
@@ -394,8 +355,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     // part into swizzled [32][32 fp32] boxes in shared memory and one lane hands them to the TMA unit as
     // reduce-add tile stores (several KV tiles add into the same query rows), so the SM issues one bulk
     // operation per 4 KB instead of 256 vector atomics.
-    uint8_t* stg = sal + C::OFF_DQS + (warp - 4) * 4096;
-    const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 4) * 4096;
+    uint8_t* stg = sal + C::OFF_DQS + (warp - 2) * 4096;
+    const uint32_t stg_s = sbase + C::OFF_DQS + (warp - 2) * 4096;
     auto flush_dq = [&](int it) {
       const int hq = kvh * rep + it / per_head, qi = j + it % per_head;
       const int y0 = qi * AB_TILE + q4 * 32;                 // first of this warp's 32 query rows
@@ -441,13 +402,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         tmem_ld32(t_lane + C::S_COL + half * 64 + c, s);
         tmem_ld32(t_lane + C::DP_COL + half * 64 + c, dp);
         tmem_ld_wait();
-        if (c == 32) {
-          // all of this thread's S / dP columns are in registers: hand the tensor-memory columns back before the
-          // second half of the arithmetic, so that the next step's S / dP MMAs can be issued under it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(6));
-        }
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -464,6 +418,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           dd[(c + i) >> 1] = pack_bf16(ds.x, ds.y);
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(6));           // S / dP columns may be overwritten
       if (it > 0) {                                 // MMAs of step it-1 done: P / dS free, dQ(it-1) ready
         if (!mbar_wait(bar(8), par ^ 1u, 29, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
@@ -479,82 +436,116 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(7));
-      if (!C::PIPELINED) {                          // hd 128: dQ shares the S columns, this warp drains it itself
+      if (C::PIPELINED) {
+        if (it > 0) flush_dq(it - 1);
+      } else {
         if (!mbar_wait(bar(8), par, 30, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         flush_dq(it);
       }
     }
     if (ok && n_it > 0) {
-      if (C::PIPELINED) {                           // the last step's MMAs: dV, dK complete
-        if (!mbar_wait(bar(8), (uint32_t)(n_it - 1) & 1u, 31, abort_flag, p.status)) ok = false;
+      if (C::PIPELINED) {
+        if (mbar_wait(bar(8), (uint32_t)(n_it - 1) & 1u, 31, abort_flag, p.status)) { tc_fence_after(); flush_dq(n_it - 1); } else ok = false;
       }
       if (ok) {
-        // dV, dK accumulators -> bf16 rows of the packed gradient tensor
-        tc_fence_after();
-        const int t_row = j * AB_TILE + row;
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
-          const float osc = which == 0 ? 1.f : p.scale;
-          const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
-          __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * p.hd + half * (HD / 2);
-          bool dst_ok = true;
-          if (p.n_dst > 0) {
-            const int owner = t_row / p.dst_rows, tl = t_row - owner * p.dst_rows;
-            dst_ok = owner < p.n_dst;
-            if (dst_ok)
-              dst = p.dst[owner] + (((long long)b * p.dst_rows + tl) * p.dst_heads + (which == 0 ? p.dst_v0 : p.dst_k0) + kvh) * p.hd
-                    + half * (HD / 2);
-          }
-#pragma unroll
-          for (int c = 0; c < HD / 2; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(t_lane + col0 + c, r);
-            tmem_ld_wait();
-            // transposed RoPE on dK (fp32): column j pairs with j +- hd / 2. `rot` is warp-uniform (the
-            // tensor-memory load of the partner columns must be executed by the whole warp).
-            const int colg = half * (HD / 2) + c;                      // first of this thread's 32 columns
-            const bool rot = which == 1 && p.cosT != nullptr && colg < p.hd;
-            uint32_t q2[32];
-            if (rot && p.hd == HD) {                                   // partner columns sit in the other half-row
-              tmem_ld32(t_lane + C::DK_COL + (1 - half) * (HD / 2) + c, q2);
+        if constexpr (SCATTER) {
+          // dV, dK accumulators -> bf16 rows of the packed gradient tensor
+          tc_fence_after();
+          const int t_row = j * AB_TILE + row;
+  #pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
+            const float osc = which == 0 ? 1.f : p.scale;
+            const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
+            __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * p.hd + half * (HD / 2);
+            bool dst_ok = true;
+            if (p.n_dst > 0) {
+              const int owner = t_row / p.dst_rows, tl = t_row - owner * p.dst_rows;
+              dst_ok = owner < p.n_dst;
+              if (dst_ok)
+                dst = p.dst[owner] + (((long long)b * p.dst_rows + tl) * p.dst_heads + (which == 0 ? p.dst_v0 : p.dst_k0) + kvh) * p.hd
+                      + half * (HD / 2);
+            }
+  #pragma unroll
+            for (int c = 0; c < HD / 2; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(t_lane + col0 + c, r);
               tmem_ld_wait();
-            }
-            if (rot && t_row < p.T) {
-              const float* cr = p.cosT + (long long)t_row * p.hd;
-              const float* sr = p.sinT + (long long)t_row * p.hd;
-              if (p.hd == HD) {
-                const int pc = (1 - half) * (HD / 2) + c;             // partner's first column
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  const float a = __uint_as_float(r[i]), bb = __uint_as_float(q2[i]);
-                  r[i] = __float_as_uint(half == 0 ? a * cr[colg + i] + bb * sr[pc + i] : a * cr[colg + i] - bb * sr[pc + i]);
-                }
-              } else {                                                // hd 32 on the 64-wide kernel: both halves are in r
-                float o[32];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  const float a = __uint_as_float(r[i]), bb = __uint_as_float(r[i + 16]);
-                  o[i] = a * cr[i] + bb * sr[i + 16];
-                  o[i + 16] = bb * cr[i + 16] - a * sr[i];
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(o[i]);
+              // transposed RoPE on dK (fp32): column j pairs with j +- hd / 2. `rot` is warp-uniform (the
+              // tensor-memory load of the partner columns must be executed by the whole warp).
+              const int colg = half * (HD / 2) + c;                      // first of this thread's 32 columns
+              const bool rot = which == 1 && p.cosT != nullptr && colg < p.hd;
+              uint32_t q2[32];
+              if (rot && p.hd == HD) {                                   // partner columns sit in the other half-row
+                tmem_ld32(t_lane + C::DK_COL + (1 - half) * (HD / 2) + c, q2);
+                tmem_ld_wait();
               }
-            }
-            if (t_row < p.T && dst_ok && half * (HD / 2) + c < p.hd) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[i]) * osc, __uint_as_float(r[i + 1]) * osc);
-                v.y = pack_bf16(__uint_as_float(r[i + 2]) * osc, __uint_as_float(r[i + 3]) * osc);
-                v.z = pack_bf16(__uint_as_float(r[i + 4]) * osc, __uint_as_float(r[i + 5]) * osc);
-                v.w = pack_bf16(__uint_as_float(r[i + 6]) * osc, __uint_as_float(r[i + 7]) * osc);
-                *reinterpret_cast<uint4*>(dst + c + i) = v;
+              if (rot && t_row < p.T) {
+                const float* cr = p.cosT + (long long)t_row * p.hd;
+                const float* sr = p.sinT + (long long)t_row * p.hd;
+                if (p.hd == HD) {
+                  const int pc = (1 - half) * (HD / 2) + c;             // partner's first column
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const float a = __uint_as_float(r[i]), bb = __uint_as_float(q2[i]);
+                    r[i] = __float_as_uint(half == 0 ? a * cr[colg + i] + bb * sr[pc + i] : a * cr[colg + i] - bb * sr[pc + i]);
+                  }
+                } else {                                                // hd 32 on the 64-wide kernel: both halves are in r
+                  float o[32];
+  #pragma unroll
+                  for (int i = 0; i < 16; ++i) {
+                    const float a = __uint_as_float(r[i]), bb = __uint_as_float(r[i + 16]);
+                    o[i] = a * cr[i] + bb * sr[i + 16];
+                    o[i + 16] = bb * cr[i + 16] - a * sr[i];
+                  }
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(o[i]);
+                }
+              }
+              if (t_row < p.T && dst_ok && half * (HD / 2) + c < p.hd) {
+  #pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 v;
+                  v.x = pack_bf16(__uint_as_float(r[i]) * osc, __uint_as_float(r[i + 1]) * osc);
+                  v.y = pack_bf16(__uint_as_float(r[i + 2]) * osc, __uint_as_float(r[i + 3]) * osc);
+                  v.z = pack_bf16(__uint_as_float(r[i + 4]) * osc, __uint_as_float(r[i + 5]) * osc);
+                  v.w = pack_bf16(__uint_as_float(r[i + 6]) * osc, __uint_as_float(r[i + 7]) * osc);
+                  *reinterpret_cast<uint4*>(dst + c + i) = v;
+                }
               }
             }
           }
+
+        } else {
+          // dV, dK accumulators -> bf16 rows of the packed gradient tensor
+          tc_fence_after();
+          const int t_row = j * AB_TILE + row;
+  #pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const int head = which == 0 ? p.Hq + p.Hkv + kvh : p.Hq + kvh;
+            const float osc = which == 0 ? 1.f : p.scale;
+            const uint32_t col0 = (which == 0 ? C::DV_COL : C::DK_COL) + half * (HD / 2);
+            __nv_bfloat16* dst = p.dqkv + (((long long)b * p.T + t_row) * heads_total + head) * p.hd + half * (HD / 2);
+  #pragma unroll
+            for (int c = 0; c < HD / 2; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(t_lane + col0 + c, r);
+              tmem_ld_wait();
+              if (t_row < p.T && half * (HD / 2) + c < p.hd) {
+  #pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 v;
+                  v.x = pack_bf16(__uint_as_float(r[i]) * osc, __uint_as_float(r[i + 1]) * osc);
+                  v.y = pack_bf16(__uint_as_float(r[i + 2]) * osc, __uint_as_float(r[i + 3]) * osc);
+                  v.z = pack_bf16(__uint_as_float(r[i + 4]) * osc, __uint_as_float(r[i + 5]) * osc);
+                  v.w = pack_bf16(__uint_as_float(r[i + 6]) * osc, __uint_as_float(r[i + 7]) * osc);
+                  *reinterpret_cast<uint4*>(dst + c + i) = v;
+                }
+              }
+            }
+          }
+
         }
       }
     }
@@ -566,18 +557,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-template <int HD>
+template <int HD, bool SCATTER>
 static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mdq, const AttnBwdParams& p,
                       cudaStream_t st) {
   using C = AttnBwdCfg<HD>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<HD, SCATTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((p.T + AB_TILE - 1) / AB_TILE, p.B * p.Hkv);
-  attn_bwd_kernel<HD><<<grid, AB_THREADS, C::TOTAL, st>>>(mq, mdo, mdq, p);
+  attn_bwd_kernel<HD, SCATTER><<<grid, AB_THREADS, C::TOTAL, st>>>(mq, mdo, mdq, p);
   count_launch();
   return launch_status();
 }
@@ -626,12 +617,16 @@ static int attn_bwd_impl(const void* qkv, const void* o, const void* dout, const
     e = make_tmap_f32(&mdq, dq_acc, 3, dims, strides, box);
     if (e) return e;
   }
-  e = hd == 128 ? launch_bwd<128>(mq, mdo, mdq, p, st) : launch_bwd<64>(mq, mdo, mdq, p, st);
+  if (n_dst > 0) e = hd == 128 ? launch_bwd<128, true>(mq, mdo, mdq, p, st) : launch_bwd<64, true>(mq, mdo, mdq, p, st);
+  else e = hd == 128 ? launch_bwd<128, false>(mq, mdo, mdq, p, st) : launch_bwd<64, false>(mq, mdo, mdq, p, st);
   if (e) return e;
-  long long items = rows * (hd / 16);
+  // without a return scatter the main kernel has written un-rotated dK into dqkv: this pass rotates it in place
+  const int rot_k = (n_dst == 0 && cosT != nullptr) ? Hkv : 0;
+  long long items = (long long)B * T * (Hq + rot_k) * (hd / 16);
   int cb = (int)((items + 255) / 256);
   if (cb > num_sms() * 16) cb = num_sms() * 16;
-  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale, cosT, sinT, dd, dst_q0);
+  attn_dq_convert_kernel<<<cb, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, B, T, Hq, Hq + 2 * Hkv, hd, scale, cosT, sinT, dd, dst_q0,
+                                             rot_k);
   count_launch();
   return launch_status();
 }

@@ -750,6 +750,55 @@ TLM_API int tlm_adamw(float* p, float* m, float* v, const float* g, void* p_out,
   return launch_status();
 }
 
+// Second half of the LM head without logits: fold the per-tile (max, sum of exp) pairs of each row into its
+// log-sum-exp, lse[row] = m + log(sum_i s_i exp(m_i - m)), and add the valid rows' (lse - target logit) into *loss_sum.
+// One warp per row; rows whose target equals ignore_index contribute nothing. Targets outside [0, V) are reported
+// through the status word (site 71) and skipped.
+__global__ void lse_finish_kernel(const float2* __restrict__ part, int tiles, const float* __restrict__ tgt_logit,
+                                  const long long* __restrict__ targets, long long ignore_index, long long V,
+                                  float* __restrict__ lse_out, float* __restrict__ loss_sum, int rows, unsigned int* status) {
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  float block_acc = 0.f;
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    float m = -INFINITY;
+    for (int i = lane; i < tiles; i += 32) m = fmaxf(m, part[(long long)row * tiles + i].x);
+    m = tlm::warp_max(m);
+    float sacc = 0.f;
+    for (int i = lane; i < tiles; i += 32) {
+      const float2 v = part[(long long)row * tiles + i];
+      sacc += v.y * __expf(v.x - m);
+    }
+    sacc = tlm::warp_sum(sacc);
+    if (lane == 0) {
+      const float lse = m + __logf(sacc);
+      if (lse_out != nullptr) lse_out[row] = lse;
+      const long long t = targets[row];
+      if (t != ignore_index) {
+        if (t >= 0 && t < V) block_acc += lse - tgt_logit[row];
+        else tlm::report_status(status, (71u << 8) | 1u);
+      }
+    }
+  }
+  if (lane == 0) red[warp] = block_acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < wpb; ++i) t += red[i];
+    if (t != 0.f) atomicAdd(loss_sum, t);
+  }
+}
+
+TLM_API int tlm_lse_finish(const void* part, int tiles, const float* tgt_logit, const long long* targets,
+                           long long ignore_index, long long V, float* lse_out, float* loss_sum, int rows, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (part == nullptr || tgt_logit == nullptr || targets == nullptr || loss_sum == nullptr || tiles <= 0) return -6;
+  lse_finish_kernel<<<grid_for((long long)rows * 32, 256), 256, 0, st>>>((const float2*)part, tiles, tgt_logit, targets,
+                                                                         ignore_index, V, lse_out, loss_sum, rows, status_word());
+  count_launch();
+  return launch_status();
+}
+
 // Contract check without a host sync: records status code (site << 8 | 2) when *a and *b differ by more than
 // rel_tol * max(|a|, |b|) (or either is not finite). The host sees it at its next look at the status word.
 __global__ void expect_close_kernel(const float* a, const float* b, float rel_tol, unsigned int site, unsigned int* status) {

@@ -38,7 +38,7 @@ constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5, EPI_LSE = 6 };
 
 // Destinations of the head-scatter epilogue: one 4-D map (hd, heads, T, B; box 64 x 1 x 32 x 1)
 // per rank of the sequence-parallel group; entry 0 alone when the output stays local.
@@ -77,6 +77,26 @@ struct GemmParams {
   //   columns from `aux` ([M, 2 I], row pitch 2 N) and writes d(gate), d(up) into C = d(gate_up) [M, 2 I].
   // Both round their GEMM result to bf16 first, so the numbers equal the separate GEMM + SwiGLU kernels'.
   const __nv_bfloat16* aux;
+  // Grouped SwiGLU (MoE experts): rows grouped like group_mode 1, B holds 2 * groups matrices (gate of group g at g,
+  // up at groups + g). A tile's rows past its group's end belong to the next group, so warps whose 32 rows cross
+  // that end store row by row with a mask instead of with TMA tile stores; `act` / `ld_act` locate the act tensor
+  // for those stores.
+  __nv_bfloat16* act;
+  long long ld_act;
+  // EPI_LSE (LM head without logits): nothing of C is stored. Each output row keeps, per 256-column tile, the
+  // maximum and the sum of exp(x - max) of its (bf16-rounded) logits in lse_part[row * lse_tiles + tile] and, in the
+  // tile that holds the row's target column, the target logit in tgt_logit[row]; a small second kernel folds the
+  // tiles into log-sum-exp and loss. The [M, V] logits never exist in memory.
+  float2* lse_part;
+  int lse_tiles;
+  const long long* targets;
+  float* tgt_logit;
+  // bf16 store with the cross-entropy gradient applied on the way out (dl_lse != nullptr): the tile holds logits x and
+  // what is stored is  *dl_scale * (exp(x - dl_lse[row]) - [col == targets[row]])  (0 for rows whose target is
+  // dl_ignore). Second pass of the LM head without logits: the gradient tile goes straight to the dgrad / wgrad GEMMs.
+  const float* dl_lse;
+  const float* dl_scale;
+  long long dl_ignore;
   // Paired groups (grouped rows, MoE gate|up): the B map has 2 * groups matrices, gate of group g at g and up at
   // groups + g. pair_n > 0: output columns >= pair_n come from the second matrix (forward: one GEMM writes
   // gate|up [R, 2 I]). pair_k > 0: reduction indices >= pair_k come from the second matrix (dgrad of both
@@ -142,7 +162,11 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in
   return t;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+// GATED: the producer warp first waits for the "parameters ready" words listed in p.wait_*. Only the kernels that can
+// be the first reader of a bucket's weights (the QKV projection: head-scatter GEMM, plain x W^T) have a gated
+// instantiation; every other kernel is compiled without the gate, whose mere presence in the producer warp's
+// preamble measurably slows the main loop (3 - 7 % on the weight-gradient shapes).
+template <bool A_MN, bool B_MN, int EPI, bool GATED = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                                           const GemmParams& p, const CUtensorMap* dst_maps) {
   extern __shared__ uint8_t smem_raw[];
@@ -195,7 +219,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     int tm = r % tiles_m, tn = r / tiles_m;
     int lo = p.row_start[g], hi = p.row_start[g + 1];
     if (p.group_mode == 1) {            // rows grouped: A rows [lo,hi), B = weight[g]
-      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = g; t.b_n0 = t.n0;
+      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * TILE_N; t.b_grp = g; t.b_n0 = t.n0;
       if (p.pair_n > 0 && t.n0 >= p.pair_n) { t.b_grp = g + p.groups; t.b_n0 = t.n0 - p.pair_n; }
       t.k_lo = 0; t.k_hi = p.K; t.m_end = hi; t.c_off = 0; t.valid = t.m0 < hi;
     } else {                            // reduction grouped: K range [lo,hi), C = C_base + g * stride
@@ -207,17 +231,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (p.wait_flags[0] != nullptr) {
+    bool gate_ok = true;
+    if (GATED) {
       // weights of this GEMM may still be on their way from the ranks that own their optimizer shards
-      bool ready = true;
 #pragma unroll
       for (int w = 0; w < 2; ++w)
-        if (p.wait_flags[w] != nullptr) ready &= wait_params_ready(p.wait_flags[w], p.wait_bucket[w], p.wait_n[w], lane, p.status, 45);
-      if (!ready) *abort_flag = 1;
-      __syncwarp();
+        if (p.wait_flags[w] != nullptr) gate_ok &= wait_params_ready(p.wait_flags[w], p.wait_bucket[w], p.wait_n[w], lane, p.status, 45);
+      gate_ok = __all_sync(0xffffffffu, gate_ok);
+      if (!gate_ok) *abort_flag = 1;
       asm volatile("fence.proxy.async;" ::: "memory");      // the peers' (generic-proxy) stores before this warp's TMA reads
     }
-    if (lane == 0 && !*abort_flag) {
+    if (lane == 0 && (!GATED || gate_ok)) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -239,8 +263,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * BOX_MN_BYTES, &tmB, full_bar(stage), t.b_n0 + 64 * j, bk, bg);
           } else if (EPI == EPI_SWIGLU) {       // 128 gate rows, then the matching 128 up rows
-            tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, 0);
-            tma_load_3d(sb + B_BYTES / 2, &tmB, full_bar(stage), k0, p.N + t.n0, 0);
+            if (p.groups > 0) {                 // experts: gate matrix of the group, then its up matrix
+              tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, t.b_grp);
+              tma_load_3d(sb + B_BYTES / 2, &tmB, full_bar(stage), k0, t.n0, t.b_grp + p.groups);
+            } else {
+              tma_load_3d(sb, &tmB, full_bar(stage), k0, t.n0, 0);
+              tma_load_3d(sb + B_BYTES / 2, &tmB, full_bar(stage), k0, p.N + t.n0, 0);
+            }
           } else {
             tma_load_3d(sb, &tmB, full_bar(stage), bk, t.b_n0, bg);
           }
@@ -314,7 +343,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         // gate / up of the NEXT tile start moving into L2 now, a whole tile time before they are read
         auto prefetch_aux = [&](const TileCoord& tt) {
           const int prow = tt.m0 + q * 32 + lane, pcol = tt.n0 + ((warp - 2) >> 2) * (BN / 2);
-          if (prow < p.M) {
+          if (prow < tt.m_end) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int c = pcol + (i & 1) * 64;
@@ -446,7 +475,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         const int row0 = t.m0 + q * 32;
         int bsel = 0;
         // 64 bf16 columns (32 packed words) of this lane's row -> swizzled staging tile -> TMA store at (col, row0)
-        auto put = [&](const uint32_t* w, const CUtensorMap* map, int col) {
+        // warps whose 32 rows all belong to the tile's row range use TMA tile stores; a warp that straddles the end
+        // of its group (grouped mode) stores its rows one by one: `base` / `ld` locate the same tensor for that
+        const bool whole = row0 + 32 <= t.m_end;               // warp-uniform
+        auto put = [&](const uint32_t* w, const CUtensorMap* map, int col, __nv_bfloat16* base, long long ld) {
+          if (!whole) {
+            if (row0 + lane < t.m_end) {
+              uint4* dst = reinterpret_cast<uint4*>(base + (long long)(row0 + lane) * ld + col);
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch) dst[ch] = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+            }
+            return;
+          }
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           __syncwarp();
           uint8_t* rowp = ebuf + bsel * EPI_BUF_BYTES + lane * 128;
@@ -485,9 +525,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
               }
             }
             const int col = t.n0 + h * 64;
-            put(pg, &tmC, col);
-            put(pu, &tmC, p.N + col);
-            put(pa, dst_maps, col);
+            put(pg, &tmC, col, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc);
+            put(pu, &tmC, p.N + col, reinterpret_cast<__nv_bfloat16*>(p.C), p.ldc);
+            put(pa, dst_maps, col, p.act, p.ld_act);
           }
         } else {
           // d(act) leaves tensor memory one row per lane, but the derivative is elementwise, so the warp stages
@@ -526,7 +566,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             for (int i = 0; i < 8; ++i) {
               const int grow = row0 + i * 4 + sub_row;
               gv[i] = make_uint4(0, 0, 0, 0); uv[i] = gv[i];
-              if (grow < p.M && col + chunk * 8 < p.N) {
+              if (grow < t.m_end && col + chunk * 8 < p.N) {
                 const __nv_bfloat16* gp = p.aux + (long long)grow * 2 * p.N + col + chunk * 8;
                 gv[i] = *reinterpret_cast<const uint4*>(gp);
                 uv[i] = *reinterpret_cast<const uint4*>(gp + p.N);
@@ -538,7 +578,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
               const int r = i * 4 + sub_row;                   // row within the warp's 32
               const int grow = row0 + r;
               const uint32_t off = r * 128 + ((chunk ^ (r & 7)) << 4);
-              const bool live = grow < p.M && col + chunk * 8 < p.N;
+              const bool live = grow < t.m_end && col + chunk * 8 < p.N;
               const uint4 dv = *reinterpret_cast<const uint4*>(buf + off);
               const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w}, gw[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w},
                              uw[4] = {uv[i].x, uv[i].y, uv[i].z, uv[i].w};
@@ -559,6 +599,39 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             __syncwarp();
           }
         }
+      } else if (EPI == EPI_LSE) {
+        // this thread's row of the tile: running maximum and sum of exponentials over 256 columns, 32 at a time
+        const long long tgt = row_ok ? p.targets[row] : -1;
+        float m_run = -INFINITY, s_run = 0.f;
+        constexpr float LOG2E = 1.4426950408889634f;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c, r);
+          tmem_ld_wait();
+          const int col = t.n0 + c;
+          if (col >= p.N) break;                                  // warp-uniform
+          float v[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {                       // logits as the bf16 values a stored tile would hold
+            const float2 f = unpack_bf16(pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+            v[j] = col + j < p.N ? f.x : -INFINITY;
+            v[j + 1] = col + j + 1 < p.N ? f.y : -INFINITY;
+            cmax = fmaxf(cmax, fmaxf(v[j], v[j + 1]));
+          }
+          if (tgt >= col && tgt < col + 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (tgt == col + j) p.tgt_logit[row] = v[j];
+          }
+          const float m_new = fmaxf(m_run, cmax);
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc += ex2_approx((v[j] - m_new) * LOG2E);
+          s_run = s_run * ex2_approx((m_run - m_new) * LOG2E) + acc;
+          m_run = m_new;
+        }
+        if (row_ok) p.lse_part[(long long)row * p.lse_tiles + t.n0 / BN] = make_float2(m_run, s_run);
       } else if (EPI == EPI_BF16 && p.tma_store) {
         // 64-column slabs: TMEM -> bf16 -> swizzled staging tile -> TMA store (clips at the matrix edge).
         uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
@@ -572,6 +645,26 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // this buffer's previous store has read it
           __syncwarp();
           tmem_ld_wait();
+          if (p.dl_lse != nullptr) {
+            constexpr float LOG2E = 1.4426950408889634f;
+            const long long tg = row_ok ? p.targets[row] : p.dl_ignore;
+            const float sc = tg != p.dl_ignore ? *p.dl_scale : 0.f;
+            const float nl = row_ok ? -p.dl_lse[row] * LOG2E : 0.f;
+            const int col0 = t.n0 + slab * 64;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float2 a = unpack_bf16(pack_bf16(__uint_as_float(r0[j]), __uint_as_float(r0[j + 1])));
+              const float2 b = unpack_bf16(pack_bf16(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1])));
+              float pa0 = ex2_approx(fmaf(a.x, LOG2E, nl)), pa1 = ex2_approx(fmaf(a.y, LOG2E, nl));
+              float pb0 = ex2_approx(fmaf(b.x, LOG2E, nl)), pb1 = ex2_approx(fmaf(b.y, LOG2E, nl));
+              if (tg == col0 + j) pa0 -= 1.f;
+              if (tg == col0 + j + 1) pa1 -= 1.f;
+              if (tg == col0 + 32 + j) pb0 -= 1.f;
+              if (tg == col0 + 32 + j + 1) pb1 -= 1.f;
+              r0[j] = __float_as_uint(pa0 * sc); r0[j + 1] = __float_as_uint(pa1 * sc);
+              r1[j] = __float_as_uint(pb0 * sc); r1[j + 1] = __float_as_uint(pb1 * sc);
+            }
+          }
           uint8_t* rowp = ebuf + bsel * EPI_BUF_BYTES + lane * 128;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
@@ -667,19 +760,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   }
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, bool GATED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  gemm_body<A_MN, B_MN, EPI>(tmA, tmB, tmC, p, nullptr);
+  gemm_body<A_MN, B_MN, EPI, GATED>(tmA, tmB, tmC, p, nullptr);
 }
 
 // Same main loop, head-scatter epilogue: the output maps (one per destination rank) replace the C map.
-template <bool B_MN>
+template <bool B_MN, bool GATED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_heads_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ HeadDstMaps dst, const GemmParams p) {
-  gemm_body<false, B_MN, EPI_HEADS>(tmA, tmB, tmA, p, dst.m);
+  gemm_body<false, B_MN, EPI_HEADS, GATED>(tmA, tmB, tmA, p, dst.m);
 }
 
 // MLP forward / backward with the SwiGLU math in the epilogue: `tmC` is the [M, 2 I] tensor the epilogue
@@ -724,11 +817,11 @@ static int build_map(CUtensorMap* map, const Operand& o, int box_rows) {
   return make_tmap_bf16(map, o.ptr, rank, dims, strides, box);
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, bool GATED = false>
 static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p, int tiles,
                     cudaStream_t st) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  auto kern = gemm_kernel<A_MN, B_MN, EPI, GATED>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -750,19 +843,23 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
     uint32_t box[2] = {64, 32};
     if (make_tmap_bf16(&mc, p.C, 2, dims, strides, box) == 0) p.tma_store = 1;
   }
+  if (p.dl_lse != nullptr && !p.tma_store) return -6;       // the gradient transform lives in the TMA-store epilogue
+  // x W^T with a pending "parameters ready" gate: the gated instantiation (see gemm_body)
+  if (!a_mn && !b_mn && epi == EPI_BF16 && p.wait_flags[0] != nullptr)
+    return launch_t<false, false, EPI_BF16, true>(ma, mb, mc, p, tiles, st);
 #define TLM_CASE(A, B, E) if (a_mn == A && b_mn == B && epi == E) return launch_t<A, B, E>(ma, mb, mc, p, tiles, st);
   TLM_CASE(false, false, EPI_BF16) TLM_CASE(false, true, EPI_BF16) TLM_CASE(true, true, EPI_F32_ACC)
   TLM_CASE(false, false, EPI_F32) TLM_CASE(true, true, EPI_F32) TLM_CASE(false, false, EPI_F32_ACC)
-  TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32)
+  TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32) TLM_CASE(false, false, EPI_LSE)
 #undef TLM_CASE
   return -2;
 }
 
-template <bool B_MN>
+template <bool B_MN, bool GATED = false>
 static int launch_heads(const CUtensorMap& ma, const CUtensorMap& mb, const HeadDstMaps& dst, const GemmParams& p,
                         int tiles, cudaStream_t st) {
   static bool configured = false;
-  auto kern = gemm_heads_kernel<B_MN>;
+  auto kern = gemm_heads_kernel<B_MN, GATED>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -808,12 +905,13 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   }
   for (int r = n_dst; r < MAX_HEAD_DST; ++r) dst.m[r] = dst.m[0];
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
+  if (!b_mn) take_pending_waits(p);               // x W^T: may be the first reader of its weights after an optimizer step
   p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
   p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cs = (const __half2*)cs;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (!b_mn && p.wait_flags[0] != nullptr) return launch_heads<false, true>(ma, mb, dst, p, tiles, stream);
   return b_mn ? launch_heads<true>(ma, mb, dst, p, tiles, stream) : launch_heads<false>(ma, mb, dst, p, tiles, stream);
 }
 
@@ -840,8 +938,8 @@ TLM_API int tlm_gemm_swiglu(const void* x, const void* w_gu, void* gate_up, void
   e = store_map_bf16(&md, act, M, I, I);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
+  p.act = (__nv_bfloat16*)act; p.ld_act = I;
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
@@ -870,7 +968,6 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   e = store_map_bf16(&mc, d_gate_up, M, 2LL * I, 2LL * I);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
   p.aux = (const __nv_bfloat16*)gate_up;
   static bool configured = false;
@@ -886,9 +983,11 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   return launch_status();
 }
 
-// Arms a "parameters ready" gate for the NEXT GEMM launched through this library (any entry point): its producer
-// warp waits until all `n` ranks' updates of `bucket` have arrived (`ready_local`: this rank's READY_INTS-word flag
-// array in symmetric memory). Up to two gates can be pending; the launch that takes them clears them.
+// Arms a "parameters ready" gate for the next forward-projection GEMM launched through this library (tlm_gemm with
+// x W^T and a bf16 result, or tlm_gemm_heads): its producer warp waits until all `n` ranks' updates of `bucket` have
+// arrived (`ready_local`: this rank's READY_INTS-word flag array in symmetric memory). Up to two gates can be pending;
+// the launch that takes them clears them. Other GEMM entry points leave pending gates alone;
+// tlm_gemm_flush_param_waits turns gates that nobody took into stand-alone wait kernels.
 TLM_API int tlm_gemm_arm_param_wait(const int* ready_local, int bucket, int n) {
   if (ready_local == nullptr || bucket < 0 || bucket >= READY_MAX_BUCKETS || n < 1 || n > READY_STRIDE) return -6;
   if (g_n_pending_wait >= 2) return -7;
@@ -899,6 +998,129 @@ TLM_API int tlm_gemm_arm_param_wait(const int* ready_local, int bucket, int n) {
   return 0;
 }
 TLM_API void tlm_gemm_clear_param_waits() { g_n_pending_wait = 0; }
+TLM_API int tlm_wait_params_ready(const int* ready_local, int bucket, int n, cudaStream_t st);
+// Queue every pending gate as a one-warp wait kernel on `stream` (the gates' GEMM never came) and clear them.
+TLM_API int tlm_gemm_flush_param_waits(cudaStream_t stream) {
+  int rc = 0;
+  for (int i = 0; i < g_n_pending_wait && rc == 0; ++i)
+    rc = tlm_wait_params_ready(g_pending_wait[i].flags, g_pending_wait[i].bucket, g_pending_wait[i].n, stream);
+  g_n_pending_wait = 0;
+  return rc;
+}
+
+// MoE experts, forward: rows of x [R, K] are grouped by expert (`row_start`, device, groups + 1 ints); group g gets
+//   gate_up[rows_g] = x[rows_g] * [W_g ; W_{groups+g}]^T   (W: 2 * groups matrices [I, K], `w_group_stride` apart)
+//   act[rows_g]     = silu(gate) * up
+// in one kernel (the dense MLP's SwiGLU epilogue with the expert picked per tile). I % 128 == 0.
+TLM_API int tlm_gemm_swiglu_grouped(const void* x, const void* w_pair, void* gate_up, void* act, const int* row_start,
+                                    int groups, int R, int I, int K, long long lda, long long w_group_stride,
+                                    int max_rows_per_group, cudaStream_t stream) {
+  if (R <= 0 || I <= 0 || K <= 0 || groups <= 0) return 0;
+  if (I % 128 != 0) return -4;
+  Operand oa{x, R, K, lda, false, 0, 0}, ob{w_pair, I, K, K, false, 2LL * groups, w_group_stride};
+  CUtensorMap ma, mb, mc, md;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, 128);
+  if (e) return e;
+  e = store_map_bf16(&mc, gate_up, R, 2LL * I, 2LL * I);
+  if (e) return e;
+  e = store_map_bf16(&md, act, R, I, I);
+  if (e) return e;
+  GemmParams p{};
+  p.M = R; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
+  p.act = (__nv_bfloat16*)act; p.ld_act = I;
+  p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  const int tiles = groups * p.max_tiles_m * (I / 128);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_swiglu_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ma, mb, mc, md, p);
+  count_launch();
+  return launch_status();
+}
+
+// MoE experts, backward of the down projection + SwiGLU: for the rows of each group g
+//   d(gate_up)[rows_g] = swiglu'(gate_up[rows_g]) applied to dy[rows_g] * W_down[g]      (W_down: [groups, D, I])
+// d(act) never reaches memory (the dense MLP's SwiGLU-backward epilogue with the expert picked per tile). I % 8 == 0.
+TLM_API int tlm_gemm_swiglu_bwd_grouped(const void* dy, const void* w_down, const void* gate_up, void* d_gate_up,
+                                        const int* row_start, int groups, int R, int I, int D, long long lda,
+                                        long long w_group_stride, int max_rows_per_group, cudaStream_t stream) {
+  if (R <= 0 || I <= 0 || D <= 0 || groups <= 0) return 0;
+  if (I % 8 != 0) return -4;
+  Operand oa{dy, R, D, lda, false, 0, 0}, ob{w_down, I, D, I, true, groups, w_group_stride};
+  CUtensorMap ma, mb, mc;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  e = store_map_bf16(&mc, d_gate_up, R, 2LL * I, 2LL * I);
+  if (e) return e;
+  GemmParams p{};
+  p.M = R; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
+  p.aux = (const __nv_bfloat16*)gate_up;
+  p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  const int tiles = groups * p.max_tiles_m * ((I + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  gemm_swiglu_bwd_kernel<<<grid, GEMM_THREADS_WIDE, GEMM_SMEM, stream>>>(ma, mb, mc, p);
+  count_launch();
+  return launch_status();
+}
+
+// Log-sum-exp statistics of logits = x [M, K] * w [N, K]^T without storing the logits (see GemmParams, EPI_LSE):
+//   part [M, tiles] float2 (max, sum of exp(logit - max)) per 256-column tile, tiles = ceil(N / 256);
+//   tgt_logit [M]: logit of column targets[row] (rows whose target is outside [0, N) keep their old value).
+TLM_API int tlm_gemm_lse(const void* x, const void* w, int M, int N, int K, long long lda, long long ldb, void* part,
+                         const long long* targets, float* tgt_logit, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (part == nullptr || targets == nullptr || tgt_logit == nullptr) return -6;
+  Operand oa{x, M, K, lda, false, 0, 0}, ob{w, N, K, ldb, false, 1, (long long)N * K};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
+  p.split_k = 1; p.k_chunk = K;
+  p.lse_part = (float2*)part; p.lse_tiles = (N + BN - 1) / BN; p.targets = targets; p.tgt_logit = tgt_logit;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return dispatch(false, false, EPI_LSE, ma, mb, p, tiles, stream);
+}
+
+// dlogits [M, N] (bf16, row pitch ldc) = scale * (softmax(x w^T) - onehot(targets)) from the rows' log-sum-exp
+// (see GemmParams, dl_*): the logits are recomputed tile by tile and leave as their own gradient.
+// Requirements: ldc % 8 == 0 and a 16-byte aligned output (the tile stores go through TMA).
+TLM_API int tlm_gemm_dlogits(const void* x, const void* w, void* dlogits, int M, int N, int K, long long lda, long long ldb,
+                             long long ldc, const float* lse, const long long* targets, const float* scale,
+                             long long ignore_index, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (lse == nullptr || targets == nullptr || scale == nullptr || ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(dlogits) & 15)) return -6;
+  Operand oa{x, M, K, lda, false, 0, 0}, ob{w, N, K, ldb, false, 1, (long long)N * K};
+  CUtensorMap ma, mb;
+  int e = build_map(&ma, oa, BM);
+  if (e) return e;
+  e = build_map(&mb, ob, BN);
+  if (e) return e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = dlogits; p.ldc = ldc; p.status = status_word(); p.groups = 0;
+  p.split_k = 1; p.k_chunk = K;
+  p.dl_lse = lse; p.targets = targets; p.dl_scale = scale; p.dl_ignore = ignore_index;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return dispatch(false, false, EPI_BF16, ma, mb, p, tiles, stream);
+}
 
 // C[M,N] = A * B^T with arbitrary operand majors.
 //   a_mn = 0: A is [M,K] (lda); a_mn = 1: A is [K,M] (lda)
@@ -914,8 +1136,8 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
+  if (!a_mn && !b_mn && epi == EPI_BF16) take_pending_waits(p);     // x W^T: may be the first reader of its weights
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   p.split_k = 1; p.k_chunk = K;
   if (epi == EPI_F32_ACC && !g_deterministic) {
@@ -960,7 +1182,6 @@ TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const i
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -987,7 +1208,6 @@ TLM_API int tlm_gemm_grouped_pair(const void* A, const void* W, void* C, const i
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = R; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -1012,7 +1232,6 @@ TLM_API int tlm_gemm_grouped_rows_scatter(const void* A, const void* B, const in
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
@@ -1036,7 +1255,6 @@ TLM_API int tlm_gemm_grouped_k(const void* A, const void* B, void* C, const int*
   e = build_map(&mb, ob, BN);
   if (e) return e;
   GemmParams p{};
-  take_pending_waits(p);
   p.M = M; p.N = N; p.K = R; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 2; p.c_group_stride = c_group_stride;
   int tiles = groups * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);

@@ -385,6 +385,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
     host sync on the hot path).
     """
 
+    RECOMPUTE_CHUNK_ROWS = 4096
     CHUNK_ROWS = 32768         # rows of logits alive at once on the GPU (3.3 GB of bf16 at V = 50304); measured on the
                                # headline step: 8192 rows 176.5 ms, 16384 rows 175.5 ms, 32768 rows 174.8 ms
     CHUNK_ROWS_CPU = 8192      # the fp32 path keeps its transient logits small
@@ -393,10 +394,35 @@ class _LinearCrossEntropy(torch.autograd.Function):
     def forward(ctx, h, weight, targets, grad_scale, ignore_index):
         M = h.shape[0]
         need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
+        if not need_grad and _use_native(h, weight) and weight.shape[0] % 8 == 0:
+            # evaluation: the loss needs no logits at all (statistics in the GEMM epilogue, see native)
+            ctx.dh = None
+            ctx.grad_scale = grad_scale
+            return native.linear_cross_entropy_sum(h.contiguous(), weight, targets, ignore_index)
         mg = _main_grad(weight) if need_grad else None
         dh = torch.empty_like(h) if need_grad else None
-        loss_sum = torch.zeros((), dtype=torch.float32, device=h.device)
         use_nat = _use_native(h, weight)
+        if use_nat and _lm_head_recompute() and weight.shape[0] % 8 == 0:
+            # Memory-lean variant: pass 1 keeps only per-tile statistics (no logits), pass 2 recomputes the logits a
+            # chunk of rows at a time and stores them as their own gradient, which feeds the dgrad / wgrad GEMMs.
+            # One extra logits GEMM per micro-step instead of the in-place softmax pass; the largest transient is
+            # RECOMPUTE_CHUNK_ROWS x V bf16 instead of M x V.
+            hc_all = h.contiguous()
+            loss_sum, lse = native.linear_cross_entropy_sum(hc_all, weight, targets, ignore_index, want_lse=True)
+            gs = grad_scale if torch.is_tensor(grad_scale) else torch.tensor(float(grad_scale), device=h.device)
+            gs = gs.reshape(()).float().contiguous()
+            step = _LinearCrossEntropy.RECOMPUTE_CHUNK_ROWS
+            work = torch.empty(min(step, M), weight.shape[0], dtype=torch.bfloat16, device=h.device)
+            for r0 in range(0, M, step):
+                r1 = min(M, r0 + step)
+                dl = native.gemm_dlogits(hc_all[r0:r1], weight, lse[r0:r1], targets[r0:r1].contiguous(), gs, ignore_index,
+                                         out=work[:r1 - r0])
+                native.gemm_nn(dl, weight, out=dh[r0:r1])
+                native.gemm_tn_accum(dl, hc_all[r0:r1], mg)
+            ctx.dh = dh
+            ctx.grad_scale = grad_scale
+            return loss_sum
+        loss_sum = torch.zeros((), dtype=torch.float32, device=h.device)
         step = _LinearCrossEntropy.CHUNK_ROWS if use_nat else _LinearCrossEntropy.CHUNK_ROWS_CPU
         for r0 in range(0, M, step):
             r1 = min(M, r0 + step)
@@ -440,6 +466,13 @@ class _LinearCrossEntropy(torch.autograd.Function):
                 raise RuntimeError("linear_cross_entropy: the upstream gradient differs from grad_scale; multiply "
                                    "the returned sum by exactly the grad_scale that was passed in")
         return dh, None, None, None, None
+
+
+def _lm_head_recompute() -> bool:
+    """`TLM_LM_HEAD=recompute`: the LM head never holds `[M, V]` logits in training either (see `_LinearCrossEntropy`).
+    Default off: at 0.3 B parameters the extra logits GEMM costs more time than the softmax pass it replaces."""
+    import os
+    return os.environ.get("TLM_LM_HEAD", "inplace") == "recompute"
 
 
 def linear_cross_entropy(h, weight, targets, grad_scale, ignore_index: int = -100) -> torch.Tensor:

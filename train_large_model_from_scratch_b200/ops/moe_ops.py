@@ -93,6 +93,38 @@ class _GroupedGateUp(torch.autograd.Function):
         return native.grouped_gemm_pair_dgrad(dgu, w, counts), None, None
 
 
+class _ExpertMLP(torch.autograd.Function):
+    """The expert MLP on expert-grouped rows, `down_e(silu(gate_e x) * up_e x)`, with the SwiGLU math inside the
+    grouped GEMMs' epilogues: forward = gate|up GEMM that also emits `act` + down GEMM; backward = two weight-gradient
+    GEMMs, the down projection's data-gradient GEMM whose epilogue turns d(act) into d(gate|up), and one
+    K-concatenated data-gradient GEMM for both projections. No stand-alone SwiGLU pass, d(act) never reaches memory."""
+
+    @staticmethod
+    def forward(ctx, x, w_pair, w_down, counts):
+        gu, act = native.grouped_gemm_swiglu(x, w_pair, counts)
+        ctx.save_for_backward(x, gu, act)
+        ctx.w_pair, ctx.w_down, ctx.counts = w_pair, w_down, counts
+        return native.grouped_gemm_nt(act, w_down, counts)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gu, act = ctx.saved_tensors
+        dx = expert_mlp_backward(dy.contiguous(), x, gu, act, ctx.w_pair, ctx.w_down, ctx.counts)
+        return dx, None, None, None
+
+
+def expert_mlp_backward(dy, x, gu, act, w_pair, w_down, counts):
+    """Shared by `_ExpertMLP` and the expert-parallel variant (`parallel.expert_parallel.peer`): accumulates the
+    three weight gradients into their `main_grad` buffers and returns the gradient of the grouped input rows."""
+    E, I = w_pair.shape[0] // 2, w_pair.shape[1]
+    native.grouped_gemm_tn_accum(dy, act, F_ops._main_grad(w_down), counts)
+    dgu = native.grouped_gemm_swiglu_bwd(dy, w_down, gu, counts)
+    mg = F_ops._main_grad(w_pair)
+    native.grouped_gemm_tn_accum(dgu[:, :I], x, mg[:E], counts)
+    native.grouped_gemm_tn_accum(dgu[:, I:], x, mg[E:], counts)
+    return native.grouped_gemm_pair_dgrad(dgu, w_pair, counts)
+
+
 def route(logits: torch.Tensor, k: int):
     """(weights [M,k] fp32, experts [M,k] int64); differentiable w.r.t. logits."""
     vals, experts = torch.topk(logits.float(), k, dim=-1)
@@ -175,6 +207,12 @@ def _moe_forward_device(x, logits, w_gate, w_up, w_down, k, num_experts, ep_grou
         per_expert = native.DeviceCounts(plan["row_start"], plan["R"])
         local_x = ep_peer.dispatch_tokens(x, pm, plan, order, pos, k, layer_key)
     valid = None if ep_size == 1 else plan["n_recv"]        # rows of the expert-side buffers that hold real pairs
+    if w_pair is not None and native.grouped_swiglu_ok(w_pair.shape[1]) and native.grouped_pair_ok(w_pair.shape[1]):
+        # SwiGLU inside the grouped GEMMs' epilogues (forward and backward)
+        if ep_size == 1:
+            y = _ExpertMLP.apply(local_x, w_pair, w_down, per_expert)
+            return _CombineDevice.apply(y, weights, order, pos, k), aux
+        return ep_peer.expert_mlp_combine(local_x, w_pair, w_down, weights, pm, plan, per_expert, order, pos, k, layer_key), aux
     if w_pair is not None and native.grouped_pair_ok(w_pair.shape[1]):
         gu = _GroupedGateUp.apply(local_x, w_pair, per_expert)
     else:

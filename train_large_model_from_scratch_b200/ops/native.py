@@ -14,7 +14,9 @@ import os
 import torch
 
 _LIB = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "libtlm_b200.so")
+# the in-tree build; TLM_LIB names another build of the same sources (A/B comparisons of kernel changes)
+_LIB_PATH = os.environ.get("TLM_LIB") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                                      "libtlm_b200.so")
 
 
 class NativeError(RuntimeError):
@@ -55,6 +57,8 @@ _SIGS = {
     "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "tlm_gemm_swiglu": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
     "tlm_gemm_swiglu_bwd": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
+    "tlm_gemm_swiglu_grouped": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _P]),
+    "tlm_gemm_swiglu_bwd_grouped": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _P]),
     "tlm_gemm_grouped_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_grouped_k": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _P]),
     "tlm_embedding_fwd": (_I, [_P, _P, _P, _I, _I, _LL, _P]),
@@ -83,6 +87,7 @@ _SIGS = {
     "tlm_wait_params_ready": (_I, [_P, _I, _I, _P]),
     "tlm_gemm_arm_param_wait": (_I, [_P, _I, _I]),
     "tlm_gemm_clear_param_waits": (None, []),
+    "tlm_gemm_flush_param_waits": (_I, [_P]),
     "tlm_peer_allreduce_scalar": (_I, [_P, _P, _P, _P, _F, _I, _I, _I, _P]),
     "tlm_peer_scatter_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "tlm_peer_put_i32": (_I, [_P, _I, _P, _I, _LL, _P]),
@@ -97,6 +102,9 @@ _SIGS = {
     "tlm_gemm_grouped_rows_scatter": (_I, [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _I, _I, _P, _P, _P, _I, _LL, _P]),
     "tlm_adamw": (_I, [_P, _P, _P, _P, _P, _P, _LL, _F, _F, _F, _F, _F, _F, _F, _P, _P]),
     "tlm_expect_close": (_I, [_P, _P, _F, _I, _P]),
+    "tlm_gemm_lse": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _P, _P, _P, _P]),
+    "tlm_gemm_dlogits": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _LL, _P]),
+    "tlm_lse_finish": (_I, [_P, _I, _P, _P, _LL, _LL, _P, _P, _I, _P]),
 }
 
 
@@ -387,6 +395,44 @@ def ce_fwd_bwd_inplace(logits, targets, grad_scale, loss_sum, ignore_index: int,
                                 rows, V, logits.stride(0), ignore_index, int(write_grad), _stream()), "ce_inplace")
 
 
+def linear_cross_entropy_sum(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100,
+                             want_lse: bool = False):
+    """`sum_i CE(h_i @ weight^T, target_i)` over the valid rows WITHOUT logits in memory: the logits GEMM's epilogue
+    keeps a (max, sum-of-exp) pair per row and 256-column tile plus the target logit, a second kernel folds them
+    (`csrc/gemm.cu` EPI_LSE, `csrc/elementwise.cu` lse_finish_kernel). Side buffers: 8 bytes per row and tile
+    (V = 50304: 1.6 KB per row instead of 100 KB of logits). Returns the loss sum (0-d fp32) and, with `want_lse`,
+    the per-row log-sum-exp. Forward only (evaluation, or the first pass of a recomputing backward)."""
+    M, K, lda = _rows(h)
+    V, K2, ldb = _rows(weight)
+    assert K == K2 and targets.numel() == M and targets.dtype == torch.int64
+    tiles = (V + 255) // 256
+    part = torch.empty(M, tiles, 2, dtype=torch.float32, device=h.device)
+    tgt = torch.zeros(M, dtype=torch.float32, device=h.device)
+    loss = torch.zeros((), dtype=torch.float32, device=h.device)
+    lse = torch.empty(M, dtype=torch.float32, device=h.device) if want_lse else None
+    t = targets.contiguous()
+    _check(lib().tlm_gemm_lse(h.data_ptr(), weight.data_ptr(), M, V, K, lda, ldb, part.data_ptr(), t.data_ptr(),
+                              tgt.data_ptr(), _stream()), "gemm_lse")
+    _check(lib().tlm_lse_finish(part.data_ptr(), tiles, tgt.data_ptr(), t.data_ptr(), ignore_index, V, _ptr(lse),
+                                loss.data_ptr(), M, _stream()), "lse_finish")
+    return (loss, lse) if want_lse else loss
+
+
+def gemm_dlogits(h: torch.Tensor, weight: torch.Tensor, lse: torch.Tensor, targets: torch.Tensor, scale: torch.Tensor,
+                 ignore_index: int = -100, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`scale * (softmax(h @ weight^T) - onehot(targets))` as bf16 `[M, V]` from the rows' log-sum-exp: the logits
+    are recomputed by the GEMM and turned into their gradient in its epilogue (rows with an ignored target give 0)."""
+    M, K, lda = _rows(h)
+    V, K2, ldb = _rows(weight)
+    assert K == K2 and V % 8 == 0 and lse.dtype == torch.float32 and lse.numel() == M and scale.dtype == torch.float32
+    if out is None:
+        out = torch.empty(M, V, dtype=torch.bfloat16, device=h.device)
+    _check(lib().tlm_gemm_dlogits(h.data_ptr(), weight.data_ptr(), out.data_ptr(), M, V, K, lda, ldb, out.stride(0),
+                                  lse.data_ptr(), targets.data_ptr(), scale.data_ptr(), ignore_index, _stream()),
+           "gemm_dlogits")
+    return out
+
+
 _SUMSQ_SCRATCH: dict = {}
 
 
@@ -581,6 +627,42 @@ def moe_pair_dot(d_out: torch.Tensor, y: torch.Tensor, pos: torch.Tensor, k: int
     _check(lib().tlm_moe_pair_dot(d_out.data_ptr(), y.data_ptr(), pos.data_ptr(), dw.data_ptr(), P, D, k, _stream()),
            "moe_pair_dot")
     return dw
+
+
+def grouped_swiglu_ok(I: int) -> bool:
+    return I % 128 == 0
+
+
+def grouped_gemm_swiglu(x: torch.Tensor, w_pair: torch.Tensor, counts):
+    """MoE gate | up + SwiGLU in one grouped GEMM: `w_pair [2E, I, D]` (gate matrices, then up matrices); for the rows
+    of group e, `gate_up = [x @ w_pair[e]^T | x @ w_pair[E + e]^T]` and `act = silu(gate) * up`.
+    Returns `(gate_up [R, 2 I], act [R, I])`; rows outside every group are left untouched."""
+    R, D, lda = _rows(x)
+    E2, I, D2 = w_pair.shape
+    assert D == D2 and E2 % 2 == 0 and w_pair.is_contiguous() and grouped_swiglu_ok(I)
+    gu = torch.empty(R, 2 * I, dtype=torch.bfloat16, device=x.device)
+    act = torch.empty(R, I, dtype=torch.bfloat16, device=x.device)
+    if R == 0:
+        return gu, act
+    rs, bound = _grouping(counts, x.device)
+    _check(lib().tlm_gemm_swiglu_grouped(x.data_ptr(), w_pair.data_ptr(), gu.data_ptr(), act.data_ptr(), rs.data_ptr(),
+                                         E2 // 2, R, I, D, lda, I * D, bound, _stream()), "grouped_gemm_swiglu")
+    return gu, act
+
+
+def grouped_gemm_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, counts) -> torch.Tensor:
+    """`d(gate_up) [R, 2 I]` for the rows of each group e from `dy [R, D]`, `w_down [E, D, I]` and the saved `gate_up`:
+    the grouped data-gradient GEMM `dy @ w_down[e]` with the SwiGLU derivative in its epilogue."""
+    R, D, lda = _rows(dy)
+    E, D2, I = w_down.shape
+    assert D == D2 and w_down.is_contiguous() and gu.shape == (R, 2 * I) and gu.is_contiguous()
+    dgu = torch.empty_like(gu)
+    if R == 0:
+        return dgu
+    rs, bound = _grouping(counts, dy.device)
+    _check(lib().tlm_gemm_swiglu_bwd_grouped(dy.data_ptr(), w_down.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rs.data_ptr(),
+                                             E, R, I, D, lda, D * I, bound, _stream()), "grouped_gemm_swiglu_bwd")
+    return dgu
 
 
 def grouped_pair_ok(I: int) -> bool:

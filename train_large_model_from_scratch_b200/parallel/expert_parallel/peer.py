@@ -198,6 +198,45 @@ class _DownCombine(torch.autograd.Function):
         return d_act, None, dw, None, None, None, None, None, None, None
 
 
+class _ExpertMLPCombine(torch.autograd.Function):
+    """Expert MLP + combine on the experts' owner: gate|up GEMM with the SwiGLU epilogue, then the down projection
+    whose epilogue stores every output row into the token owner's buffer, where `out[t] = sum_s w[t,s] * row(t,s)` is
+    formed. Backward: `w * d_out[token]` is pushed to the experts' owners, and the expert MLP's backward runs there
+    with the SwiGLU derivative inside the down projection's data-gradient GEMM."""
+
+    @staticmethod
+    def forward(ctx, x_local, w_pair, w_down, weights, pm: PeerMoE, plan: dict, per_expert, order, pos, k: int, key):
+        gu, act = native.grouped_gemm_swiglu(x_local, w_pair, per_expert)
+        D = w_down.shape[1]
+        comb = pm.buffer((key, "comb"), plan["P"], D)
+        native.grouped_gemm_nt_scatter(act, w_down, per_expert, plan["back_rank"], plan["back_row"],
+                                       comb[1].ptr_array, pm.ep, plan["P"])
+        pm.barrier()
+        M = weights.shape[0]
+        out = native.moe_combine(comb[0], pos, weights, M, k)
+        ctx.pm, ctx.plan, ctx.key, ctx.k, ctx.per_expert = pm, plan, key, k, per_expert
+        ctx.w_pair, ctx.w_down = w_pair, w_down
+        ctx.save_for_backward(x_local, gu, act, weights, order, pos, comb[0])
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from ...ops.moe_ops import expert_mlp_backward
+        pm, plan, k = ctx.pm, ctx.plan, ctx.k
+        x_local, gu, act, weights, order, pos, comb = ctx.saved_tensors
+        d_out = d_out.contiguous()
+        dw = native.moe_pair_dot(d_out, comb, pos, k).view_as(weights)
+        dst = pm.buffer((ctx.key, "comb_bwd"), plan["R"], d_out.shape[1])
+        pm.scatter(d_out, plan["send_rank"], plan["send_row"], dst, None, plan["P"], src_idx=order, src_div=k,
+                   row_scale=weights)
+        dx = expert_mlp_backward(dst[0], x_local, gu, act, ctx.w_pair, ctx.w_down, ctx.per_expert)
+        return dx, None, None, dw, None, None, None, None, None, None, None
+
+
+def expert_mlp_combine(x_local, w_pair, w_down, weights, pm, plan, per_expert, order, pos, k, key):
+    return _ExpertMLPCombine.apply(x_local, w_pair, w_down, weights, pm, plan, per_expert, order, pos, k, key)
+
+
 def dispatch_tokens(x, pm, plan, order, pos, k, key):
     return _DispatchTokens.apply(x, pm, plan, order, pos, k, key)
 

@@ -251,7 +251,8 @@ class PeerCollectives:
     def wait_first_buckets(self, shards) -> None:
         """Stream-ordered bounded wait for the buckets of layer group 0 (embedding, first norm; every bucket of
         a buffer whose buckets are not tied to layer groups): no GEMM is their first reader."""
-        native.lib().tlm_gemm_clear_param_waits()
+        # gates armed for a GEMM that never came (a forward pass that was cut short) become plain wait kernels
+        native._check(native.lib().tlm_gemm_flush_param_waits(native._stream()), "flush_param_waits")
         for s in shards:
             st = self.state.get(id(s))
             if st is None:
@@ -265,6 +266,8 @@ class PeerCollectives:
         """The next GEMM launched waits, in its producer warp, for every rank's update of group `g`'s buckets."""
         if g == 0:
             return
+        # gates of the previous group that no projection GEMM took (a block that does not start with one)
+        native._check(native.lib().tlm_gemm_flush_param_waits(native._stream()), "flush_param_waits")
         for s in shards:
             st = self.state.get(id(s))
             if st is None:
