@@ -37,6 +37,11 @@ constexpr int GEMM_THREADS_WIDE = 320;               // 8 epilogue warps (two pe
 constexpr int EPI_BUF_BYTES = 32 * 128;              // one warp's 32 rows x 64 bf16 staging tile
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;     // 4 epilogue warps x 2 buffers = 32 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+// CTA pairs (see gemm_body, PAIR): each CTA stages its own 128 rows of A and HALF of the tile's B rows, so a stage is
+// 32 KB per CTA and the ring is six stages deep.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;
+constexpr int GEMM_SMEM_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + EPI_BYTES + 1024 + 256;
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5, EPI_LSE = 6 };
 
@@ -143,21 +148,22 @@ struct TileCoord {
   bool valid;
 };
 
-__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n, int tile_n) {
+__device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in, int tiles_m, int tiles_n, int tile_n,
+                                                int tile_m = BM, int m_shift = 0) {
   // split-major order: CTAs that run together work on different output tiles, so the red.global passes of
   // the k-splits of one tile do not collide in time
   const int n_out = tiles_m * tiles_n;
   const int ks = tile_in / n_out, tile = tile_in - ks * n_out;
   // bands of 16 row-tiles, column-tiles fastest inside a band -> the CTAs that
   // run together share a handful of A and B tiles in L2
-  constexpr int GROUP_M = 16;
+  const int GROUP_M = tile_m == BM ? 16 : 8;        // 2048 rows per band either way
   int band = tile / (GROUP_M * tiles_n);
   int first_m = band * GROUP_M;
   int gm = min(GROUP_M, tiles_m - first_m);
   int r = tile - band * GROUP_M * tiles_n;
   int tm = first_m + r % gm, tn = r / gm;
   TileCoord t;
-  t.m0 = tm * BM; t.n0 = tn * tile_n; t.a_row0 = t.m0; t.b_grp = 0; t.b_n0 = t.n0;
+  t.m0 = tm * tile_m + m_shift; t.n0 = tn * tile_n; t.a_row0 = t.m0; t.b_grp = 0; t.b_n0 = t.n0;
   t.k_lo = ks * p.k_chunk; t.k_hi = min(p.K, t.k_lo + p.k_chunk); t.m_end = p.M; t.c_off = 0; t.valid = t.k_hi > t.k_lo;
   return t;
 }
@@ -166,13 +172,30 @@ __device__ __forceinline__ TileCoord plain_tile(const GemmParams& p, int tile_in
 // be the first reader of a bucket's weights (the QKV projection: head-scatter GEMM, plain x W^T) have a gated
 // instantiation; every other kernel is compiled without the gate, whose mere presence in the producer warp's
 // preamble measurably slows the main loop (3 - 7 % on the weight-gradient shapes).
-template <bool A_MN, bool B_MN, int EPI, bool GATED = false>
+//
+// PAIR: the kernel runs as clusters of two CTAs on one 256 x 256 tile (plain GEMMs only). Rank r of the pair owns
+// output rows [128 r, 128 r + 128) of the tile: it loads those rows of A and rows [128 r, +128) of the tile's B
+// operand (for the SwiGLU forward: rank 0 the gate rows, rank 1 the up rows) with its own TMA producer, and reads its
+// accumulator half from its own tensor memory with its own epilogue warps. Rank 0's MMA lane issues M = 256
+// cta_group::2 MMAs that read both CTAs' shared memory, so every CTA pulls 32 KB per k-block out of L2 instead of
+// 48 KB. Barriers: `full` lives in rank 0 (both producers' loads complete on it), `empty` and `accumulator full` are
+// signalled in both CTAs by the leader's commits, `accumulator empty` lives in rank 0 and collects both CTAs'
+// epilogue warps.
+template <bool A_MN, bool B_MN, int EPI, bool GATED = false, bool PAIR = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                                           const GemmParams& p, const CUtensorMap* dst_maps) {
+  static_assert(!(PAIR && GATED), "the gated instantiations run as single CTAs");
+  constexpr int STAGES = PAIR ? PAIR_STAGES : tlm::STAGES;
+  constexpr int B_TILE_BYTES = PAIR ? B_BYTES / 2 : B_BYTES;
+  constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES + EPI_BYTES);
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;        // tile walker id and count
+  const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   // barrier slots: full[0..S), empty[S..2S), acc_full[2S..2S+2), acc_empty[2S+2..2S+4)
   const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES + EPI_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -189,30 +212,32 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS); }
+    for (int a = 0; a < 2; ++a) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), EPI_WARPS * (PAIR ? 2 : 1)); }
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   constexpr int TILE_N = EPI == EPI_SWIGLU ? 128 : BN;      // output columns per tile (SwiGLU: 128 gate + 128 up)
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;                // rows per tile walker
   const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
   int tiles_m, total_tiles;
-  if (p.groups == 0) { tiles_m = (p.M + BM - 1) / BM; total_tiles = tiles_m * tiles_n * p.split_k; }
+  if (p.groups == 0) { tiles_m = (p.M + TILE_M - 1) / TILE_M; total_tiles = tiles_m * tiles_n * p.split_k; }
   else if (p.group_mode == 1) { tiles_m = p.max_tiles_m; total_tiles = p.groups * tiles_m * tiles_n; }
   else { tiles_m = (p.M + BM - 1) / BM; total_tiles = p.groups * tiles_m * tiles_n; }
 
   auto get_tile = [&](int tile) -> TileCoord {
-    if (p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n, TILE_N);
+    if (PAIR || p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n, TILE_N, TILE_M, (int)cta_rank * BM);
     TileCoord t;
     int per = tiles_m * tiles_n;
     int g = tile / per, r = tile - g * per;
@@ -244,12 +269,34 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     if (lane == 0 && (!GATED || gate_ok)) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < total_tiles && ok; tile += n_workers) {
         TileCoord t = get_tile(tile);
         if (!t.valid) continue;
         for (int k0 = t.k_lo; k0 < t.k_hi; k0 += BK) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, abort_flag, p.status)) { ok = false; break; }
           const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          if (PAIR) {
+            // both CTAs' loads of this stage complete on the leader's barrier
+            const uint32_t fb = mapa_shared(full_bar(stage), 0);
+            if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * BOX_MN_BYTES, &tmA, fb, t.a_row0 + 64 * j, k0);
+            } else {
+              tma_load_2d_pair(sa, &tmA, fb, k0, t.a_row0);
+            }
+            const int half_n0 = (int)cta_rank * (BN / 2);       // this CTA's half of the tile's B rows
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j) tma_load_3d_pair(sb + j * BOX_MN_BYTES, &tmB, fb, t.b_n0 + half_n0 + 64 * j, k0, 0);
+            } else if (EPI == EPI_SWIGLU) {                     // rank 0: 128 gate rows, rank 1: the matching up rows
+              tma_load_3d_pair(sb, &tmB, fb, k0, (leader ? 0 : p.N) + t.n0, 0);
+            } else {
+              tma_load_3d_pair(sb, &tmB, fb, k0, t.b_n0 + half_n0, 0);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
@@ -281,11 +328,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     // ------------------------------------------------------------ MMA issuer
     // The whole warp walks the loop (so it can clean a ragged reduction tail in
     // shared memory); lane 0 alone issues the MMAs and commits.
-    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0;
     int acc = 0; uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    bool ok = !PAIR || leader;                      // the follower's MMA warp only allocates and frees tensor memory
+    for (int tile = worker; tile < total_tiles && ok; tile += n_workers) {
       TileCoord t = get_tile(tile);
       if (!t.valid) continue;
       if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, 2, abort_flag, p.status)) { ok = false; break; }
@@ -316,18 +363,26 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           // MN-major: 16 k-rows = two 8-row groups = 2048 B further.
           const uint64_t ad0 = A_MN ? umma_smem_desc(sa, BOX_MN_BYTES, 1024) : umma_smem_desc(sa, 16, 1024);
           const uint64_t bd0 = B_MN ? umma_smem_desc(sb, BOX_MN_BYTES, 1024) : umma_smem_desc(sb, 16, 1024);
+          if (PAIR) {
+            umma_bf16_pair(tmem_d, ad0, bd0, idesc, accumulate);
+#pragma unroll
+            for (int kk = 1; kk < BK / UMMA_K; ++kk)
+              umma_bf16_pair(tmem_d, umma_desc_advance(ad0, kk * (A_MN ? 2048 : 32)), umma_desc_advance(bd0, kk * (B_MN ? 2048 : 32)), idesc, 1u);
+            umma_commit_pair(empty_bar(stage));   // both CTAs' producers may refill the stage
+          } else {
           umma_bf16(tmem_d, ad0, bd0, idesc, accumulate);
 #pragma unroll
           for (int kk = 1; kk < BK / UMMA_K; ++kk)
             umma_bf16_acc(tmem_d, umma_desc_advance(ad0, kk * (A_MN ? 2048 : 32)), umma_desc_advance(bd0, kk * (B_MN ? 2048 : 32)), idesc);
-          accumulate = 1;
           umma_commit(empty_bar(stage));          // stage reusable once these MMAs retire
+          }
+          accumulate = 1;
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
-      if (lane == 0) umma_commit(accf_bar(acc));  // accumulator complete
+      if (lane == 0) { if (PAIR) umma_commit_pair(accf_bar(acc)); else umma_commit(accf_bar(acc)); }  // accumulator complete
       __syncwarp();
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
@@ -336,7 +391,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int tile = worker; tile < total_tiles && ok; tile += n_workers) {
       TileCoord t = get_tile(tile);
       if (!t.valid) continue;
       if (EPI == EPI_SWIGLU_BWD) {
@@ -352,8 +407,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             }
           }
         };
-        if (tile == (int)blockIdx.x) prefetch_aux(t);
-        const int nxt = tile + gridDim.x;
+        if (tile == worker) prefetch_aux(t);
+        const int nxt = tile + n_workers;
         if (nxt < total_tiles) { const TileCoord tn = get_tile(nxt); if (tn.valid) prefetch_aux(tn); }
       }
       if (!mbar_wait(accf_bar(acc), acc_phase, 4, abort_flag, p.status)) { ok = false; break; }
@@ -744,7 +799,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(acc));
+      if (lane == 0) {
+        if (PAIR && !leader) mbar_arrive_cluster(mapa_shared(acce_bar(acc), 0));
+        else mbar_arrive(acce_bar(acc));
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (((EPI == EPI_BF16 && p.tma_store) || EPI == EPI_HEADS || EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) && lane == 0)
@@ -753,10 +811,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();          // neither CTA leaves (or frees tensor memory) while its peer may still signal or read it
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -788,7 +847,48 @@ gemm_swiglu_bwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   gemm_body<false, true, EPI_SWIGLU_BWD>(tmA, tmB, tmC, p, nullptr);
 }
 
+// CTA-pair instantiations (clusters of two CTAs, see gemm_body): plain GEMMs and the dense fused epilogues.
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  gemm_body<A_MN, B_MN, EPI, false, true>(tmA, tmB, tmC, p, nullptr);
+}
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_heads_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ HeadDstMaps dst, const GemmParams p) {
+  gemm_body<false, B_MN, EPI_HEADS, false, true>(tmA, tmB, tmA, p, dst.m);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_swiglu_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+                        const GemmParams p) {
+  gemm_body<false, false, EPI_SWIGLU, false, true>(tmA, tmB, tmC, p, &tmD);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS_WIDE, 1)
+gemm_swiglu_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                            const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  gemm_body<false, true, EPI_SWIGLU_BWD, false, true>(tmA, tmB, tmC, p, nullptr);
+}
+
 // ---- host side ---------------------------------------------------------------------------------
+// CTA pairs are used for every plain (ungrouped, ungated) GEMM of at least 256 rows unless switched off
+// (TLM_GEMM_PAIR=0 in the environment, or tlm_gemm_set_pair).
+static int g_pair_mode = -1;
+static bool pair_enabled() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("TLM_GEMM_PAIR");
+    g_pair_mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pair_mode != 0;
+}
+static bool use_pair(int M) { return pair_enabled() && M >= 2 * BM && num_sms() >= 2; }
+// grid of a pair kernel: two CTAs per tile walker, at most one walker per SM pair
+static int pair_grid(long long tiles) {
+  const int walkers = num_sms() / 2;
+  return 2 * (int)(tiles < walkers ? tiles : walkers);
+}
 // Operand description: `ptr` points at element (0,0); K-major operands are
 // [rows, K] with leading dimension `ld`; MN-major operands are [K, rows] with
 // leading dimension `ld`. `groups`/`group_stride` add an outer dimension (B only).
@@ -834,8 +934,26 @@ static int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
   return launch_status();
 }
 
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p,
+                         int tiles, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = pair_grid(tiles);
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM_PAIR, st>>>(ma, mb, mc, p);
+  count_launch();
+  return launch_status();
+}
+
+// `pair`: `tiles` counts 256-row tiles and the B map was built with 128-row boxes (see pair_maps)
 static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p,
-                    int tiles, cudaStream_t st) {
+                    int tiles, cudaStream_t st, bool pair = false) {
   CUtensorMap mc = ma;                      // placeholder when the TMA-store epilogue is off
   if (p.split_k < 1) { p.split_k = 1; p.k_chunk = p.K; }
   if (epi == EPI_BF16 && p.groups == 0 && p.ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
@@ -847,7 +965,10 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
   // x W^T with a pending "parameters ready" gate: the gated instantiation (see gemm_body)
   if (!a_mn && !b_mn && epi == EPI_BF16 && p.wait_flags[0] != nullptr)
     return launch_t<false, false, EPI_BF16, true>(ma, mb, mc, p, tiles, st);
-#define TLM_CASE(A, B, E) if (a_mn == A && b_mn == B && epi == E) return launch_t<A, B, E>(ma, mb, mc, p, tiles, st);
+  if (pair && (p.groups != 0 || p.wait_flags[0] != nullptr)) return -8;
+#define TLM_CASE(A, B, E)                                                          \
+  if (a_mn == A && b_mn == B && epi == E)                                          \
+    return pair ? launch_pair_t<A, B, E>(ma, mb, mc, p, tiles, st) : launch_t<A, B, E>(ma, mb, mc, p, tiles, st);
   TLM_CASE(false, false, EPI_BF16) TLM_CASE(false, true, EPI_BF16) TLM_CASE(true, true, EPI_F32_ACC)
   TLM_CASE(false, false, EPI_F32) TLM_CASE(true, true, EPI_F32) TLM_CASE(false, false, EPI_F32_ACC)
   TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32) TLM_CASE(false, false, EPI_LSE)
@@ -872,9 +993,33 @@ static int launch_heads(const CUtensorMap& ma, const CUtensorMap& mb, const Head
   return launch_status();
 }
 
+template <bool B_MN>
+static int launch_heads_pair(const CUtensorMap& ma, const CUtensorMap& mb, const HeadDstMaps& dst, const GemmParams& p,
+                             int tiles, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = gemm_heads_pair_kernel<B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = pair_grid(tiles);
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM_PAIR, st>>>(ma, mb, dst, p);
+  count_launch();
+  return launch_status();
+}
+
 }  // namespace tlm
 
 using namespace tlm;
+
+// CTA-pair GEMMs on / off at run time (tests and A/B measurements); returns the previous setting.
+TLM_API int tlm_gemm_set_pair(int on) {
+  const int was = pair_enabled() ? 1 : 0;
+  g_pair_mode = on ? 1 : 0;
+  return was;
+}
 
 // Projection GEMM whose epilogue applies RoPE and scatters heads (see GemmParams):
 //   A [M = batch * rows_per_batch, K] (lda);  B [N, K] K-major (b_mn = 0) or [K, N] MN-major (b_mn = 1),
@@ -892,11 +1037,14 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   if (Hkv > 0 && (kv_l <= 0 || Hkv % kv_l != 0)) return -5;
   if (Hq / q_l > n_dst || (Hkv > 0 && Hkv / kv_l > n_dst)) return -5;
   if (n_rot > 0 && cs == nullptr) return -5;
+  GemmParams p{};
+  if (!b_mn) take_pending_waits(p);               // x W^T: may be the first reader of its weights after an optimizer step
+  const bool pair = use_pair(M) && p.wait_flags[0] == nullptr;
   Operand oa{A, M, K, lda, false, 0, 0}, ob{B, N, K, ldb, b_mn != 0, 1, (long long)N * K};
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   HeadDstMaps dst;
   for (int r = 0; r < n_dst; ++r) {
@@ -904,12 +1052,14 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
     if (e) return e;
   }
   for (int r = n_dst; r < MAX_HEAD_DST; ++r) dst.m[r] = dst.m[0];
-  GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
-  if (!b_mn) take_pending_waits(p);               // x W^T: may be the first reader of its weights after an optimizer step
   p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
   p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cs = (const __half2*)cs;
+  if (pair) {
+    const int ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    return b_mn ? launch_heads_pair<true>(ma, mb, dst, p, ptiles, stream) : launch_heads_pair<false>(ma, mb, dst, p, ptiles, stream);
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   if (!b_mn && p.wait_flags[0] != nullptr) return launch_heads<false, true>(ma, mb, dst, p, tiles, stream);
   return b_mn ? launch_heads<true>(ma, mb, dst, p, tiles, stream) : launch_heads<false>(ma, mb, dst, p, tiles, stream);
@@ -940,6 +1090,18 @@ TLM_API int tlm_gemm_swiglu(const void* x, const void* w_gu, void* gate_up, void
   GemmParams p{};
   p.M = M; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
   p.act = (__nv_bfloat16*)act; p.ld_act = I;
+  if (use_pair(M)) {               // the B map's 128-row boxes serve both forms: rank 0 loads gate rows, rank 1 up rows
+    static bool pconfigured = false;
+    if (!pconfigured) {
+      cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+      if (ce != cudaSuccess) return (int)ce;
+      pconfigured = true;
+    }
+    const int pgrid = pair_grid((long long)((M + 2 * BM - 1) / (2 * BM)) * (I / 128));
+    gemm_swiglu_pair_kernel<<<pgrid, GEMM_THREADS, GEMM_SMEM_PAIR, stream>>>(ma, mb, mc, md, p);
+    count_launch();
+    return launch_status();
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
@@ -970,6 +1132,18 @@ TLM_API int tlm_gemm_swiglu_bwd(const void* dy, const void* w_down, const void* 
   GemmParams p{};
   p.M = M; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
   p.aux = (const __nv_bfloat16*)gate_up;
+  if (use_pair(M)) {               // MN-major B: 64-wide boxes in both forms
+    static bool pconfigured = false;
+    if (!pconfigured) {
+      cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+      if (ce != cudaSuccess) return (int)ce;
+      pconfigured = true;
+    }
+    const int pgrid = pair_grid((long long)((M + 2 * BM - 1) / (2 * BM)) * ((I + BN - 1) / BN));
+    gemm_swiglu_bwd_pair_kernel<<<pgrid, GEMM_THREADS_WIDE, GEMM_SMEM_PAIR, stream>>>(ma, mb, mc, p);
+    count_launch();
+    return launch_status();
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
@@ -1090,14 +1264,15 @@ TLM_API int tlm_gemm_lse(const void* x, const void* w, int M, int N, int K, long
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  const bool pair = use_pair(M);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
   p.lse_part = (float2*)part; p.lse_tiles = (N + BN - 1) / BN; p.targets = targets; p.tgt_logit = tgt_logit;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return dispatch(false, false, EPI_LSE, ma, mb, p, tiles, stream);
+  const int tiles = ((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * ((N + BN - 1) / BN);
+  return dispatch(false, false, EPI_LSE, ma, mb, p, tiles, stream, pair);
 }
 
 // dlogits [M, N] (bf16, row pitch ldc) = scale * (softmax(x w^T) - onehot(targets)) from the rows' log-sum-exp
@@ -1112,14 +1287,15 @@ TLM_API int tlm_gemm_dlogits(const void* x, const void* w, void* dlogits, int M,
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  const bool pair = use_pair(M);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = dlogits; p.ldc = ldc; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
   p.dl_lse = lse; p.targets = targets; p.dl_scale = scale; p.dl_ignore = ignore_index;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return dispatch(false, false, EPI_BF16, ma, mb, p, tiles, stream);
+  const int tiles = ((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * ((N + BN - 1) / BN);
+  return dispatch(false, false, EPI_BF16, ma, mb, p, tiles, stream, pair);
 }
 
 // C[M,N] = A * B^T with arbitrary operand majors.
@@ -1129,23 +1305,25 @@ TLM_API int tlm_gemm_dlogits(const void* x, const void* w, void* dlogits, int M,
 TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                      long long ldc, int a_mn, int b_mn, int epi, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
+  if (!a_mn && !b_mn && epi == EPI_BF16) take_pending_waits(p);     // x W^T: may be the first reader of its weights
+  const bool pair = use_pair(M) && p.wait_flags[0] == nullptr;
   Operand oa{A, M, K, lda, a_mn != 0, 0, 0}, ob{B, N, K, ldb, b_mn != 0, 1, (long long)N * K};
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
-  GemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word(); p.groups = 0;
-  if (!a_mn && !b_mn && epi == EPI_BF16) take_pending_waits(p);     // x W^T: may be the first reader of its weights
-  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tile_m = pair ? 2 * BM : BM;
+  int tiles = ((M + tile_m - 1) / tile_m) * ((N + BN - 1) / BN);
   p.split_k = 1; p.k_chunk = K;
   if (epi == EPI_F32_ACC && !g_deterministic) {
     // Weight gradients: few output tiles, long reduction. The persistent grid runs work items (tile x k-split)
     // of equal size in waves of one item per SM, so time ~ waves * (k-blocks per item + E), E = cost of one
     // epilogue pass (fp32 read-modify-write or red.global of a 128 KB tile) in k-block units (measured ~8).
     // Items keep at least 64 k-blocks.
-    const int sms = num_sms();
+    const int sms = pair ? num_sms() / 2 : num_sms();     // tile walkers
     const int kblocks = (K + BK - 1) / BK;
     int max_split = kblocks / 64;
     if (max_split > 16) max_split = 16;
@@ -1163,7 +1341,7 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
       p.split_k = (kblocks + per - 1) / per;
     }
   }
-  return dispatch(a_mn != 0, b_mn != 0, epi, ma, mb, p, tiles * p.split_k, stream);
+  return dispatch(a_mn != 0, b_mn != 0, epi, ma, mb, p, tiles * p.split_k, stream, pair);
 }
 
 // Grouped forward / dgrad: rows of A and C are grouped (`row_start`, device,

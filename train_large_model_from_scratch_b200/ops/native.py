@@ -53,6 +53,7 @@ _SIGS = {
     "tlm_num_sms": (_I, []),
     "tlm_set_deterministic": (None, [_I]),
     "tlm_get_deterministic": (_I, []),
+    "tlm_gemm_set_pair": (_I, [_I]),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
     "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "tlm_gemm_swiglu": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
@@ -148,6 +149,12 @@ def set_deterministic(on: bool) -> None:
     replaced by the single-pass accumulate. The attention backward's dQ reduction and the MoE / embedding
     scatter-adds still sum in hardware order."""
     lib().tlm_set_deterministic(int(bool(on)))
+
+
+def set_gemm_pairs(on: bool) -> bool:
+    """Plain GEMMs of at least 256 rows run as CTA pairs (`cta_group::2`, one 256 x 256 tile per two SMs) unless this
+    is switched off (also `TLM_GEMM_PAIR=0`); returns the previous setting. For tests and A/B measurements."""
+    return bool(lib().tlm_gemm_set_pair(int(bool(on))))
 
 
 def take_device_status() -> int:
