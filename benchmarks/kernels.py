@@ -64,7 +64,7 @@ def bench_gemm(small: bool):
     pk = _peaks().get("bf16_tflops")
     M = 4096 if small else 32768
     shapes = [("qkv_fwd", M, 2048, 1024), ("out_fwd", M, 1024, 1024), ("gate_up_fwd", M, 8192, 1024),
-              ("down_fwd", M, 1024, 4096), ("lm_head_chunk", 4096, 50304, 1024)]
+              ("down_fwd", M, 1024, 4096), ("lm_head_chunk", 4096, 50304, 1024)] + ([] if small else [("lm_head", 32768, 50304, 1024)])
     for name, m, n, k in shapes:
         x = torch.randn(m, k, device="cuda").bfloat16()
         w = torch.randn(n, k, device="cuda").bfloat16()

@@ -742,6 +742,35 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
+      } else if (EPI == EPI_F32_ACC && p.tma_store) {
+        // C += accumulator through TMA reduce-add: 32-column fp32 slabs are staged (swizzled) in shared memory and added
+        // to C in L2 as whole 128-byte rows. No C value travels to the SM, nothing waits on a global load, and a
+        // split reduction's partial sums meet in L2 the same way (their order is then not fixed; an unsplit GEMM adds
+        // exactly one value to each element and stays deterministic).
+        uint8_t* ebuf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const uint32_t ebuf_s = smem_base + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const int row0 = t.m0 + q * 32;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int bsel = (c >> 5) & 1;
+          uint32_t r[32];
+          tmem_ld32(taddr + c, r);
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // this buffer's previous reduce has read it
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = ebuf + bsel * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (t.n0 + c < p.N && row0 < p.M)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"((uint64_t)&tmC), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(t.n0 + c), "r"(row0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
       } else {
       __nv_bfloat16* scat = nullptr;                 // row-scatter destination of this thread's row
       bool row_live = row_ok;
@@ -805,7 +834,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (((EPI == EPI_BF16 && p.tma_store) || EPI == EPI_HEADS || EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) && lane == 0)
+    if ((((EPI == EPI_BF16 || EPI == EPI_F32_ACC) && p.tma_store) || EPI == EPI_HEADS || EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_BWD) && lane == 0)
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
@@ -960,6 +989,13 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
     uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.M}, strides[1] = {(uint64_t)p.ldc * 2};
     uint32_t box[2] = {64, 32};
     if (make_tmap_bf16(&mc, p.C, 2, dims, strides, box) == 0) p.tma_store = 1;
+  }
+  static int f32_reduce = -1;                 // TLM_GEMM_TMA_REDUCE=0: fp32 accumulation with loads and stores / red.global
+  if (f32_reduce < 0) { const char* v = getenv("TLM_GEMM_TMA_REDUCE"); f32_reduce = (v != nullptr && v[0] == '0') ? 0 : 1; }
+  if (epi == EPI_F32_ACC && f32_reduce && p.groups == 0 && p.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+    uint64_t dims[2] = {(uint64_t)p.N, (uint64_t)p.M}, strides[1] = {(uint64_t)p.ldc * 4};
+    uint32_t box[2] = {32, 32};
+    if (make_tmap_f32(&mc, p.C, 2, dims, strides, box) == 0) p.tma_store = 1;
   }
   if (p.dl_lse != nullptr && !p.tma_store) return -6;       // the gradient transform lives in the TMA-store epilogue
   // x W^T with a pending "parameters ready" gate: the gated instantiation (see gemm_body)
@@ -1325,14 +1361,21 @@ TLM_API int tlm_gemm(const void* A, const void* B, void* C, int M, int N, int K,
     // Items keep at least 64 k-blocks.
     const int sms = pair ? num_sms() / 2 : num_sms();     // tile walkers
     const int kblocks = (K + BK - 1) / BK;
-    int max_split = kblocks / 64;
-    if (max_split > 16) max_split = 16;
+    static int min_kb = -1, e_cost = -1, cap = -1;
+    if (min_kb < 0) {
+      const char* v;
+      min_kb = (v = getenv("TLM_SPLITK_MINKB")) ? atoi(v) : 64;
+      e_cost = (v = getenv("TLM_SPLITK_E")) ? atoi(v) : 8;
+      cap = (v = getenv("TLM_SPLITK_MAX")) ? atoi(v) : 16;
+    }
+    int max_split = kblocks / min_kb;
+    if (max_split > cap) max_split = cap;
     int best = 1;
     double best_cost = 1e30;
     for (int sp = 1; sp <= (max_split > 1 ? max_split : 1); ++sp) {
       const long long items = (long long)tiles * sp;
       const long long waves = (items + sms - 1) / sms;
-      const double cost = (double)waves * ((double)((kblocks + sp - 1) / sp) + 8.0);
+      const double cost = (double)waves * ((double)((kblocks + sp - 1) / sp) + (double)e_cost);
       if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
     }
     if (best > 1) {
