@@ -51,3 +51,46 @@ def test_reference_arm_reports_unavailable_without_cuda():
     assert r.returncode == 0, r.stderr[-500:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_extra_configurations_run_as_child_jobs_and_failures_stay_contained(tmp_path, monkeypatch):
+    """`run_extras` starts one child job per extra configuration with the launcher's rank variables removed, keeps
+    the keys of the child's JSON line, and reports a child that fails or hangs as `unavailable` without raising."""
+    bench = _load_bench()
+    fake = tmp_path / "fake_bench.py"
+    fake.write_text(
+        "import json, os, sys, time\n"
+        "cfg = sys.argv[sys.argv.index('--config') + 1]\n"
+        "assert 'RANK' not in os.environ and 'MASTER_PORT' not in os.environ, 'launcher variables leaked'\n"
+        "assert '--no-extras' in sys.argv\n"
+        "if cfg == 'C':\n"
+        "    mode = os.environ.get('FAKE_MODE', 'ok')\n"
+        "    if mode == 'fail':\n"
+        "        print('boom', file=sys.stderr); sys.exit(3)\n"
+        "    if mode == 'hang':\n"
+        "        time.sleep(60)\n"
+        "print('noise before the result')\n"
+        "print(json.dumps({'metric': 'm', 'value': 1.5, 'unit': 'tokens/s', 'ms_per_step': 2.0, 'steps': 20,\n"
+        "                  'config': {'model': cfg}, 'e2e': {'value': 1.25}, 'clocks': {'sm_mhz': 1500}}))\n")
+    monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+    os.rename(fake, tmp_path / "bench.py")
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setenv("MASTER_PORT", "1234")
+
+    class Args:
+        gpus, steps, warmup, impl, ref_compile, moe_fallback, extra_timeout = 1, 50, 3, "ours", 1, 1, 20
+
+    out = bench.run_extras(Args)
+    assert set(out) == {k for k, _ in bench.EXTRAS}
+    assert out["moe"]["value"] == 1.5 and out["moe"]["config"]["model"] == "D" and out["moe"]["steps"] == 20
+    assert out["ulysses"]["e2e"]["value"] == 1.25 and "wall_s" in out["ulysses"]
+
+    monkeypatch.setenv("FAKE_MODE", "fail")
+    out = bench.run_extras(Args)
+    assert "unavailable" in out["ulysses"] and "exit code 3" in out["ulysses"]["unavailable"] and "boom" in out["ulysses"]["unavailable"]
+    assert out["moe"]["value"] == 1.5
+
+    monkeypatch.setenv("FAKE_MODE", "hang")
+    Args.extra_timeout = 2
+    out = bench.run_extras(Args)
+    assert "no result within 2 s" in out["ulysses"]["unavailable"] and out["moe"]["value"] == 1.5

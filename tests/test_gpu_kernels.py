@@ -16,6 +16,15 @@ def nat():
     assert native.take_device_status() == 0
 
 
+@pytest.fixture(params=["pairs", "single"])
+def gemm_mode(request, nat):
+    """Plain GEMMs run as CTA pairs (cta_group::2, the default) and as single CTAs: both forms must agree with the
+    fp32 reference, on every operand layout and epilogue."""
+    was = nat.set_gemm_pairs(2 if request.param == "pairs" else 0)     # 2: row-grouped GEMMs with small groups as well
+    yield request.param
+    nat.set_gemm_pairs(was)
+
+
 def _rand(*shape, scale=1.0, seed=0):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
@@ -30,7 +39,7 @@ GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (384, 768, 192), (200, 264, 72),
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_gemm_nt(nat, M, N, K):
+def test_gemm_nt(nat, gemm_mode, M, N, K):
     x, w = _rand(M, K, seed=1), _rand(N, K, seed=2)
     y = nat.gemm_nt(x, w)
     ref = x.float() @ w.float().t()
@@ -39,7 +48,7 @@ def test_gemm_nt(nat, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_gemm_nn(nat, M, N, K):
+def test_gemm_nn(nat, gemm_mode, M, N, K):
     dy, w = _rand(M, N, seed=3), _rand(N, K, seed=4)
     dx = nat.gemm_nn(dy, w)
     ref = dy.float() @ w.float()
@@ -47,7 +56,7 @@ def test_gemm_nn(nat, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_gemm_tn_accum(nat, M, N, K):
+def test_gemm_tn_accum(nat, gemm_mode, M, N, K):
     dy, x = _rand(M, N, seed=5), _rand(M, K, seed=6)
     acc = torch.ones(N, K, device="cuda")
     nat.gemm_tn_accum(dy, x, acc)
@@ -58,7 +67,7 @@ def test_gemm_tn_accum(nat, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(32768, 1024, 1024), (16384, 4096, 1024), (20000, 520, 264)])
-def test_gemm_tn_accum_long_reductions(nat, M, N, K):
+def test_gemm_tn_accum_long_reductions(nat, gemm_mode, M, N, K):
     """Weight-gradient shapes: long reductions with few output tiles (split-K with atomic adds)."""
     dy, x = _rand(M, N, seed=25, scale=0.5), _rand(M, K, seed=26, scale=0.5)
     ref = 1.0 + dy.float().t() @ x.float()
@@ -70,9 +79,9 @@ def test_gemm_tn_accum_long_reductions(nat, M, N, K):
     assert _rel_err(acc, 2 * ref - 1.0) < 1e-4
 
 
-def test_gemm_strided_output_and_guard_rows(nat):
+def test_gemm_strided_output_and_guard_rows(nat, gemm_mode):
     """Output written into a slice of a larger buffer must not touch its neighbours."""
-    M, N, K = 200, 264, 72
+    M, N, K = (200, 264, 72) if gemm_mode == "single" else (456, 264, 72)     # 456 rows: a pair tile with a ragged second half
     x, w = _rand(M, K, seed=7), _rand(N, K, seed=8)
     big = torch.full((M + 16, N + 24), 7.0, device="cuda", dtype=torch.bfloat16)
     out = big[8:8 + M, 8:8 + N]
@@ -141,7 +150,7 @@ def test_rope(nat, hd, variant):
 
 @pytest.mark.parametrize("hd,Hq,Hkv,B,T,K", [(64, 4, 2, 2, 96, 192), (128, 2, 1, 1, 160, 256), (64, 16, 8, 1, 256, 1024),
                                               (64, 3, 1, 2, 32, 64)])
-def test_gemm_heads_rope_epilogue(nat, hd, Hq, Hkv, B, T, K):
+def test_gemm_heads_rope_epilogue(nat, gemm_mode, hd, Hq, Hkv, B, T, K):
     """QKV projection whose epilogue rotates q/k heads and writes the packed tensor, against GEMM -> RoPE in fp32."""
     import ctypes
     from train_large_model_from_scratch_b200.ops import oracle
@@ -159,7 +168,7 @@ def test_gemm_heads_rope_epilogue(nat, hd, Hq, Hkv, B, T, K):
     assert _rel_err(out[:, :, Hq + Hkv:], ref[:, :, Hq + Hkv:]) < 6e-3
 
 
-def test_gemm_heads_scatter_plan(nat):
+def test_gemm_heads_scatter_plan(nat, gemm_mode):
     """Two destinations (both local buffers here) with the Ulysses head plan and a row offset; MN-major weight."""
     import ctypes
     hd, Hq, B, T_l, sp, me = 64, 4, 2, 64, 2, 1
@@ -176,7 +185,7 @@ def test_gemm_heads_scatter_plan(nat):
 
 
 @pytest.mark.parametrize("M,I,K", [(200, 128, 64), (512, 384, 256), (4096, 1024, 512)])
-def test_gemm_swiglu_epilogues(nat, M, I, K):
+def test_gemm_swiglu_epilogues(nat, gemm_mode, M, I, K):
     """gate|up GEMM that also emits act, and the down-projection dgrad that emits d(gate|up), against the
     separate GEMM and SwiGLU kernels' math in fp32."""
     x, w = _rand(M, K, seed=50), _rand(2 * I, K, scale=0.1, seed=51)
@@ -252,8 +261,9 @@ def test_adamw_matches_torch(nat):
     torch.testing.assert_close(out, p.to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("counts,N,K", [([130, 0, 64, 257], 512, 256), ([5, 300, 1, 90], 264, 72), ([0, 0, 128], 256, 64)])
-def test_grouped_gemms(nat, counts, N, K):
+@pytest.mark.parametrize("counts,N,K", [([130, 0, 64, 257], 512, 256), ([5, 300, 1, 90], 264, 72), ([0, 0, 128], 256, 64),
+                                        ([700, 0, 1300, 257], 512, 256)])
+def test_grouped_gemms(nat, gemm_mode, counts, N, K):
     R, E = sum(counts), len(counts)
     x, w = _rand(R, K, seed=20), _rand(E, N, K, seed=21)
     dy = _rand(R, N, seed=22)
@@ -312,7 +322,7 @@ def test_moe_route_and_row_movement(nat, M, E, k):
     assert _rel_err(dl, lf.grad) < 1e-2
 
 
-def test_grouped_gemm_row_scatter_epilogue(nat):
+def test_grouped_gemm_row_scatter_epilogue(nat, gemm_mode):
     """Grouped GEMM whose epilogue stores each output row at a looked-up (buffer, row): two local buffers
     stand in for two ranks; rows flagged -1 are dropped."""
     import ctypes
@@ -342,7 +352,7 @@ def test_grouped_gemm_row_scatter_epilogue(nat):
         assert _rel_err(bufs[b], ref[b]) < 6e-3
 
 
-def test_grouped_pair_gemms(nat):
+def test_grouped_pair_gemms(nat, gemm_mode):
     """gate | up of all experts in one grouped GEMM, and the data gradient of both in one GEMM with K = 2 I."""
     E, I, D = 3, 256, 192
     counts = [70, 0, 130]
@@ -411,7 +421,7 @@ def test_moe_plan_kernel_matches_table_arithmetic(nat):
 
 
 @pytest.mark.parametrize("counts,I,D", [([300, 0, 129, 511], 256, 256), ([128, 128], 512, 192), ([1, 700, 3, 64, 0, 0, 257, 33], 256, 512)])
-def test_grouped_swiglu_epilogues(nat, counts, I, D):
+def test_grouped_swiglu_epilogues(nat, gemm_mode, counts, I, D):
     """MoE expert gate|up GEMM with the SwiGLU epilogue and the down projection's data-gradient GEMM with the
     SwiGLU-backward epilogue, per expert group (groups that end inside a 128-row tile, empty groups), against fp32."""
     E, R = len(counts), sum(counts)
@@ -448,7 +458,7 @@ def test_grouped_swiglu_epilogues(nat, counts, I, D):
 
 
 @pytest.mark.parametrize("M,V,K", [(300, 50304, 256), (128, 2048, 128), (1000, 33000, 512)])
-def test_lm_head_loss_without_logits(nat, M, V, K):
+def test_lm_head_loss_without_logits(nat, gemm_mode, M, V, K):
     """Loss of the LM head from (max, sum-of-exp) statistics kept in the logits GEMM's epilogue, no logits in memory:
     against fp32 `log_softmax` of the bf16-rounded logits, with ignored rows, at the 50304 vocabulary (its last
     256-column tile is half empty)."""
@@ -473,7 +483,7 @@ def test_lm_head_loss_without_logits(nat, M, V, K):
 
 
 @pytest.mark.parametrize("M,V,K", [(300, 50304, 256), (520, 2048, 128)])
-def test_lm_head_gradient_tiles_from_recomputed_logits(nat, M, V, K):
+def test_lm_head_gradient_tiles_from_recomputed_logits(nat, gemm_mode, M, V, K):
     """Second pass of the LM head without logits: `scale * (softmax - onehot)` written by the logits GEMM's epilogue
     from the rows' log-sum-exp, against autograd of fp32 cross-entropy on the same bf16 logits."""
     h, w = _rand(M, K, seed=43), _rand(V, K, seed=44, scale=0.3)

@@ -198,3 +198,37 @@ def test_adamw_matches_torch():
         opt.step()
         oracle.adamw_step(p, g, m, v, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
     torch.testing.assert_close(p, ref.detach(), rtol=1e-5, atol=1e-6)
+
+
+def test_attention_dropout_trains_and_is_off_in_eval():
+    """`--dropout > 0` (reference: attn.py:159): active in training mode only, and the step still back-propagates."""
+    import warnings
+
+    from train_large_model_from_scratch_b200.models import GPT
+    from train_large_model_from_scratch_b200.training.config import ModelConfig
+
+    def build(p):
+        cfg = ModelConfig(block_size=32, vocab_size=128, num_layer=2, num_attention_heads=4, num_key_value_heads=2,
+                          hidden_size=64, intermediate_size=128, dropout=p)
+        return GPT(cfg, device="cpu")
+
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, 128, (2, 32), generator=g)
+    tgt = torch.randint(0, 128, (2, 32), generator=g)
+    plain, drop = build(0.0), build(0.5)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        drop.train()
+        torch.manual_seed(0)
+        _, loss_d, _ = drop(idx, tgt)
+        _, loss_p, _ = plain(idx, tgt)
+        assert torch.isfinite(loss_d) and abs(float(loss_d) - float(loss_p)) > 1e-6
+        loss_d.backward()
+        grads = [p.main_grad if hasattr(p, "main_grad") else p.grad for p in drop.parameters()]
+        assert any(gr is not None and float(gr.abs().sum()) > 0 for gr in grads)
+        drop.eval()
+        with torch.no_grad():
+            _, loss_e, _ = drop(idx, tgt)
+            plain.eval()
+            _, loss_pe, _ = plain(idx, tgt)
+        assert abs(float(loss_e) - float(loss_pe)) < 1e-6

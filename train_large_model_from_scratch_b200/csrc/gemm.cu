@@ -237,16 +237,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   else { tiles_m = (p.M + BM - 1) / BM; total_tiles = p.groups * tiles_m * tiles_n; }
 
   auto get_tile = [&](int tile) -> TileCoord {
-    if (PAIR || p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n, TILE_N, TILE_M, (int)cta_rank * BM);
+    if (p.groups == 0) return plain_tile(p, tile, tiles_m, tiles_n, TILE_N, TILE_M, (int)cta_rank * BM);
     TileCoord t;
     int per = tiles_m * tiles_n;
     int g = tile / per, r = tile - g * per;
     int tm = r % tiles_m, tn = r / tiles_m;
     int lo = p.row_start[g], hi = p.row_start[g + 1];
     if (p.group_mode == 1) {            // rows grouped: A rows [lo,hi), B = weight[g]
-      t.m0 = lo + tm * BM; t.a_row0 = t.m0; t.n0 = tn * TILE_N; t.b_grp = g; t.b_n0 = t.n0;
+      // PAIR: both CTAs of a pair must agree on whether the tile exists, so that is decided on the pair's first row;
+      // a second half that starts past the group's end runs with every row masked
+      const int m_first = lo + tm * TILE_M;
+      t.m0 = m_first + (int)cta_rank * BM; t.a_row0 = t.m0; t.n0 = tn * TILE_N; t.b_grp = g; t.b_n0 = t.n0;
       if (p.pair_n > 0 && t.n0 >= p.pair_n) { t.b_grp = g + p.groups; t.b_n0 = t.n0 - p.pair_n; }
-      t.k_lo = 0; t.k_hi = p.K; t.m_end = hi; t.c_off = 0; t.valid = t.m0 < hi;
+      t.k_lo = 0; t.k_hi = p.K; t.m_end = hi; t.c_off = 0; t.valid = m_first < hi;
     } else {                            // reduction grouped: K range [lo,hi), C = C_base + g * stride
       t.m0 = tm * BM; t.a_row0 = t.m0; t.n0 = tn * BN; t.b_grp = 0; t.b_n0 = t.n0;
       t.k_lo = lo; t.k_hi = hi; t.m_end = p.M; t.c_off = (long long)g * p.c_group_stride; t.valid = hi > lo;
@@ -286,13 +289,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
               tma_load_2d_pair(sa, &tmA, fb, k0, t.a_row0);
             }
             const int half_n0 = (int)cta_rank * (BN / 2);       // this CTA's half of the tile's B rows
+            int pbk = k0, pbg = t.b_grp;
+            if (p.pair_k > 0 && k0 >= p.pair_k) { pbk = k0 - p.pair_k; pbg += p.groups; }
             if (B_MN) {
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j) tma_load_3d_pair(sb + j * BOX_MN_BYTES, &tmB, fb, t.b_n0 + half_n0 + 64 * j, k0, 0);
+              for (int j = 0; j < BN / 128; ++j) tma_load_3d_pair(sb + j * BOX_MN_BYTES, &tmB, fb, t.b_n0 + half_n0 + 64 * j, pbk, pbg);
             } else if (EPI == EPI_SWIGLU) {                     // rank 0: 128 gate rows, rank 1: the matching up rows
-              tma_load_3d_pair(sb, &tmB, fb, k0, (leader ? 0 : p.N) + t.n0, 0);
+              if (p.groups > 0) tma_load_3d_pair(sb, &tmB, fb, k0, t.n0, t.b_grp + (leader ? 0 : p.groups));
+              else tma_load_3d_pair(sb, &tmB, fb, k0, (leader ? 0 : p.N) + t.n0, 0);
             } else {
-              tma_load_3d_pair(sb, &tmB, fb, k0, t.b_n0 + half_n0, 0);
+              tma_load_3d_pair(sb, &tmB, fb, pbk, t.b_n0 + half_n0, pbg);
             }
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             continue;
@@ -913,6 +919,9 @@ static bool pair_enabled() {
   return g_pair_mode != 0;
 }
 static bool use_pair(int M) { return pair_enabled() && M >= 2 * BM && num_sms() >= 2; }
+// row-grouped GEMMs: a pair tile's second half is wasted at the end of every group, so pairs need large groups
+// (mode 2, set by tests: pairs for every row-grouped launch, so that small ragged groups exercise that path)
+static bool use_pair_grouped(int M, int groups) { return use_pair(M) && (g_pair_mode == 2 || (long long)M >= 512LL * groups); }
 // grid of a pair kernel: two CTAs per tile walker, at most one walker per SM pair
 static int pair_grid(long long tiles) {
   const int walkers = num_sms() / 2;
@@ -1001,7 +1010,7 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
   // x W^T with a pending "parameters ready" gate: the gated instantiation (see gemm_body)
   if (!a_mn && !b_mn && epi == EPI_BF16 && p.wait_flags[0] != nullptr)
     return launch_t<false, false, EPI_BF16, true>(ma, mb, mc, p, tiles, st);
-  if (pair && (p.groups != 0 || p.wait_flags[0] != nullptr)) return -8;
+  if (pair && ((p.groups != 0 && p.group_mode != 1) || p.wait_flags[0] != nullptr)) return -8;
 #define TLM_CASE(A, B, E)                                                          \
   if (a_mn == A && b_mn == B && epi == E)                                          \
     return pair ? launch_pair_t<A, B, E>(ma, mb, mc, p, tiles, st) : launch_t<A, B, E>(ma, mb, mc, p, tiles, st);
@@ -1050,10 +1059,12 @@ static int launch_heads_pair(const CUtensorMap& ma, const CUtensorMap& mb, const
 
 using namespace tlm;
 
-// CTA-pair GEMMs on / off at run time (tests and A/B measurements); returns the previous setting.
-TLM_API int tlm_gemm_set_pair(int on) {
-  const int was = pair_enabled() ? 1 : 0;
-  g_pair_mode = on ? 1 : 0;
+// CTA-pair GEMMs at run time (tests and A/B measurements): 0 off, 1 on, 2 on and also for row-grouped GEMMs with
+// small groups. Returns the previous setting.
+TLM_API int tlm_gemm_set_pair(int mode) {
+  pair_enabled();
+  const int was = g_pair_mode;
+  g_pair_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return was;
 }
 
@@ -1241,6 +1252,19 @@ TLM_API int tlm_gemm_swiglu_grouped(const void* x, const void* w_pair, void* gat
   p.M = R; p.N = I; p.K = K; p.C = gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = K;
   p.act = (__nv_bfloat16*)act; p.ld_act = I;
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  if (use_pair_grouped(R, groups)) {
+    p.max_tiles_m = (max_rows_per_group + 2 * BM - 1) / (2 * BM);
+    static bool pconfigured = false;
+    if (!pconfigured) {
+      cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+      if (ce != cudaSuccess) return (int)ce;
+      pconfigured = true;
+    }
+    const int pgrid = pair_grid((long long)groups * p.max_tiles_m * (I / 128));
+    gemm_swiglu_pair_kernel<<<pgrid, GEMM_THREADS, GEMM_SMEM_PAIR, stream>>>(ma, mb, mc, md, p);
+    count_launch();
+    return launch_status();
+  }
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
   static bool configured = false;
   if (!configured) {
@@ -1275,6 +1299,19 @@ TLM_API int tlm_gemm_swiglu_bwd_grouped(const void* dy, const void* w_down, cons
   p.M = R; p.N = I; p.K = D; p.C = d_gate_up; p.ldc = 2LL * I; p.status = status_word(); p.split_k = 1; p.k_chunk = D;
   p.aux = (const __nv_bfloat16*)gate_up;
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
+  if (use_pair_grouped(R, groups)) {
+    p.max_tiles_m = (max_rows_per_group + 2 * BM - 1) / (2 * BM);
+    static bool pconfigured = false;
+    if (!pconfigured) {
+      cudaError_t ce = cudaFuncSetAttribute(gemm_swiglu_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_PAIR);
+      if (ce != cudaSuccess) return (int)ce;
+      pconfigured = true;
+    }
+    const int pgrid = pair_grid((long long)groups * p.max_tiles_m * ((I + BN - 1) / BN));
+    gemm_swiglu_bwd_pair_kernel<<<pgrid, GEMM_THREADS_WIDE, GEMM_SMEM_PAIR, stream>>>(ma, mb, mc, p);
+    count_launch();
+    return launch_status();
+  }
   p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
   static bool configured = false;
   if (!configured) {
@@ -1400,14 +1437,15 @@ TLM_API int tlm_gemm_grouped_rows(const void* A, const void* B, void* C, const i
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  const bool pair = use_pair_grouped(M, groups);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
-  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  p.max_tiles_m = (max_rows_per_group + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM);
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
-  return dispatch(false, b_mn != 0, epi, ma, mb, p, tiles, stream);
+  return dispatch(false, b_mn != 0, epi, ma, mb, p, tiles, stream, pair);
 }
 
 // Paired grouped GEMMs for the MoE gate / up projections. `W` holds 2 * groups matrices [I, D] (gate of
@@ -1426,15 +1464,16 @@ TLM_API int tlm_gemm_grouped_pair(const void* A, const void* W, void* C, const i
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  const bool pair = use_pair_grouped(R, groups);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   GemmParams p{};
   p.M = R; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
-  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  p.max_tiles_m = (max_rows_per_group + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM);
   if (dgrad) p.pair_k = I; else p.pair_n = I;
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
-  return dispatch(false, dgrad != 0, EPI_BF16, ma, mb, p, tiles, stream);
+  return dispatch(false, dgrad != 0, EPI_BF16, ma, mb, p, tiles, stream, pair);
 }
 
 // Same as tlm_gemm_grouped_rows with a bf16 store, but output row r goes to dst_ptrs[dest_rank[r]] row dest_row[r]
@@ -1450,16 +1489,17 @@ TLM_API int tlm_gemm_grouped_rows_scatter(const void* A, const void* B, const in
   CUtensorMap ma, mb;
   int e = build_map(&ma, oa, BM);
   if (e) return e;
-  e = build_map(&mb, ob, BN);
+  const bool pair = use_pair_grouped(M, groups);
+  e = build_map(&mb, ob, pair ? BN / 2 : BN);
   if (e) return e;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.status = status_word();
   p.groups = groups; p.row_start = row_start; p.group_mode = 1;
-  p.max_tiles_m = (max_rows_per_group + BM - 1) / BM;
+  p.max_tiles_m = (max_rows_per_group + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM);
   p.rs_rank = dest_rank; p.rs_row = dest_row; p.rs_rows = dst_rows;
   for (int i = 0; i < n_dst; ++i) p.rs_dst[i] = dst_ptrs[i];
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
-  return dispatch(false, b_mn != 0, EPI_BF16, ma, mb, p, tiles, stream);
+  return dispatch(false, b_mn != 0, EPI_BF16, ma, mb, p, tiles, stream, pair);
 }
 
 // Grouped wgrad: C[g] ([M,N] fp32, `c_group_stride` apart) += A[rows_g, M]^T * B[rows_g, N]

@@ -71,9 +71,7 @@ class Attention(nn.Module):
         self.num_key_value_heads = config.num_key_value_heads
         self.head_dim = config.hidden_size // config.num_attention_heads
         self.n_embd = config.hidden_size
-        self.dropout = config.dropout
-        if self.dropout != 0.0:
-            raise NotImplementedError("attention dropout > 0 is not supported (the reference's scripts all use 0.0)")
+        self.dropout = config.dropout           # > 0: training steps take the library attention path (see forward)
         hd, D = self.head_dim, config.hidden_size
         self.q_proj = _Proj(self.num_attention_heads * hd, D, config.init_std, config.seed, device)
         self.k_proj = _Proj(self.num_key_value_heads * hd, D, config.init_std, config.seed, device)
@@ -131,6 +129,9 @@ class Attention(nn.Module):
         sp = parallel_state.get_sep_world_size()
         group = parallel_state.get_sep_group()
         cos, sin = self._rope(T_local, h.device)
+        dropout_p = self.dropout if self.training else 0.0      # reference: attn.py:159
+        if dropout_p > 0.0:
+            return self._forward_with_dropout(h, B, T_local, cos, sin, dropout_p, sp, group).view(shape)
         if F_ops.qkv_project_fused_ok(h, self._qkv_weight, hd, T_local):
             # CUDA: projection + RoPE (+ the seq->head exchange) are one GEMM with a head-scatter epilogue
             if sp == 1:
@@ -169,3 +170,29 @@ class Attention(nn.Module):
             o = F_ops.attention_packed(qkv, Hq, Hkv, True)
         y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
         return y.view(shape)
+
+    def _forward_with_dropout(self, h, B, T_local, cos, sin, dropout_p, sp, group) -> torch.Tensor:
+        """Attention-probability dropout (`--dropout > 0`, training mode). The flash kernels of this package carry no
+        dropout mask, so this configuration runs projection, RoPE and the Ulysses exchanges as separate ops and the
+        library's scaled-dot-product attention with `dropout_p` (what the reference calls, `attn.py:159-163`); every
+        reference script trains with 0.0, which takes the fused path."""
+        import warnings
+        Hq, Hkv, hd = self.num_attention_heads, self.num_key_value_heads, self.head_dim
+        warnings.warn("attention dropout > 0: using the library attention kernel instead of the sm_100a flash kernels",
+                      stacklevel=2)
+        if self._qkv_weight is not None:
+            qkv = F_ops.linear(h, self._qkv_weight)
+        else:
+            qkv = torch.cat([F_ops.linear(h, self.q_proj.weight), F_ops.linear(h, self.k_proj.weight),
+                             F_ops.linear(h, self.v_proj.weight)], dim=-1)
+        qkv = F_ops.rope_qk(qkv.view(B, T_local, Hq + 2 * Hkv, hd), cos, sin, Hq + Hkv)
+        q_l, kv_l = Hq, Hkv
+        if sp > 1:
+            qkv, q_l, kv_l = ulysses.seq_to_head(qkv, Hq, Hkv, group)
+        q, k, v = qkv.split([q_l, kv_l, kv_l], dim=2)
+        o = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dropout_p=dropout_p, is_causal=True,
+            enable_gqa=q_l != kv_l).transpose(1, 2).contiguous()
+        if sp > 1:
+            o = ulysses.head_to_seq(o, group)
+        return F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)

@@ -151,10 +151,11 @@ def set_deterministic(on: bool) -> None:
     lib().tlm_set_deterministic(int(bool(on)))
 
 
-def set_gemm_pairs(on: bool) -> bool:
-    """Plain GEMMs of at least 256 rows run as CTA pairs (`cta_group::2`, one 256 x 256 tile per two SMs) unless this
-    is switched off (also `TLM_GEMM_PAIR=0`); returns the previous setting. For tests and A/B measurements."""
-    return bool(lib().tlm_gemm_set_pair(int(bool(on))))
+def set_gemm_pairs(mode) -> int:
+    """Plain GEMMs of at least 256 rows, and row-grouped GEMMs with large groups, run as CTA pairs (`cta_group::2`, one
+    256 x 256 tile per two SMs). `mode`: 0 / False off (also `TLM_GEMM_PAIR=0`), 1 / True on (the default), 2 on and
+    also for row-grouped GEMMs with small groups. Returns the previous mode. For tests and A/B measurements."""
+    return int(lib().tlm_gemm_set_pair(int(mode)))
 
 
 def take_device_status() -> int:
