@@ -43,7 +43,8 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;
 constexpr int GEMM_SMEM_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + EPI_BYTES + 1024 + 256;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5, EPI_LSE = 6 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_HEADS = 3, EPI_SWIGLU = 4, EPI_SWIGLU_BWD = 5, EPI_LSE = 6,
+                EPI_ROWS = 7 /* bf16 rows stored at looked-up (buffer, row): the expert-parallel combine */ };
 
 // Destinations of the head-scatter epilogue: one 4-D map (hd, heads, T, B; box 64 x 1 x 32 x 1)
 // per rank of the sequence-parallel group; entry 0 alone when the output stays local.
@@ -780,7 +781,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       } else {
       __nv_bfloat16* scat = nullptr;                 // row-scatter destination of this thread's row
       bool row_live = row_ok;
-      if (EPI == EPI_BF16 && p.rs_rank != nullptr) {
+      if (EPI == EPI_ROWS) {
         const int dr = row_ok ? p.rs_rank[row] : -1;
         const long long drow = dr >= 0 ? p.rs_row[row] : -1;
         if (dr >= 0 && dr < MAX_HEAD_DST && drow >= 0 && drow < p.rs_rows)
@@ -796,7 +797,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         tmem_ld_wait();
         const int col = t.n0 + c;
         if (row_live && col < p.N) {
-          if (EPI == EPI_BF16) {
+          if (EPI == EPI_BF16 || EPI == EPI_ROWS) {
             __nv_bfloat16* out = scat != nullptr ? scat + col
                                                  : reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
 #pragma unroll
@@ -1017,6 +1018,7 @@ static int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const 
   TLM_CASE(false, false, EPI_BF16) TLM_CASE(false, true, EPI_BF16) TLM_CASE(true, true, EPI_F32_ACC)
   TLM_CASE(false, false, EPI_F32) TLM_CASE(true, true, EPI_F32) TLM_CASE(false, false, EPI_F32_ACC)
   TLM_CASE(true, true, EPI_BF16) TLM_CASE(false, true, EPI_F32) TLM_CASE(false, false, EPI_LSE)
+  TLM_CASE(false, false, EPI_ROWS) TLM_CASE(false, true, EPI_ROWS)
 #undef TLM_CASE
   return -2;
 }
@@ -1499,7 +1501,7 @@ TLM_API int tlm_gemm_grouped_rows_scatter(const void* A, const void* B, const in
   p.rs_rank = dest_rank; p.rs_row = dest_row; p.rs_rows = dst_rows;
   for (int i = 0; i < n_dst; ++i) p.rs_dst[i] = dst_ptrs[i];
   int tiles = groups * p.max_tiles_m * ((N + BN - 1) / BN);
-  return dispatch(false, b_mn != 0, EPI_BF16, ma, mb, p, tiles, stream, pair);
+  return dispatch(false, b_mn != 0, EPI_ROWS, ma, mb, p, tiles, stream, pair);
 }
 
 // Grouped wgrad: C[g] ([M,N] fp32, `c_group_stride` apart) += A[rows_g, M]^T * B[rows_g, N]
