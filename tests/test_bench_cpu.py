@@ -94,3 +94,23 @@ def test_extra_configurations_run_as_child_jobs_and_failures_stay_contained(tmp_
     Args.extra_timeout = 2
     out = bench.run_extras(Args)
     assert "no result within 2 s" in out["ulysses"]["unavailable"] and out["moe"]["value"] == 1.5
+
+
+def test_fused_path_rooflines_count_the_bytes_that_leave_a_gpu():
+    """benchmarks/fused_paths.py: FLOPs and NVLink bytes per call of the fused exchange kernels, from the configuration."""
+    sys.path.insert(0, ROOT)
+    try:
+        from benchmarks import fused_paths
+    finally:
+        sys.path.remove(ROOT)
+    bench = _load_bench()
+    bench._select_config("C", 8)                        # Ulysses over 8 ranks, 4096 tokens per rank, micro-batch 1
+    roofs = {label: (flops, nbytes) for _, label, flops, nbytes in fused_paths._rooflines(bench, 8)}
+    qkv = roofs["QKV GEMM + RoPE + seq->head scatter"]
+    assert qkv[0] == 2.0 * 4096 * 2048 * 1024 and qkv[1] == 4096 * 2048 * 2 * 7 / 8
+    o = roofs["attention forward + head->seq scatter of O"]
+    assert o[0] == 4.0 * 1 * 2 * 32768 * 32768 * 64 / 2 and o[1] == 32768 * 2 * 64 * 2 * 7 / 8
+    bench = _load_bench()
+    bench._select_config("D", 8)
+    moe = fused_paths._rooflines(bench, 8)
+    assert len(moe) == 2 and all(nbytes == 4 * 4096 // 8 * 2 * 1024 * 2 * 7 / 8 for _, _, _, nbytes in moe)
