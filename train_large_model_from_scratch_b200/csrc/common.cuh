@@ -415,6 +415,11 @@ int make_tmap_f32(CUtensorMap* map, const void* base, int rank, const uint64_t* 
 
 int num_sms();
 
+// Heads per group of the attention kernels' heavy-first block order (heavy_first_decode): as many heads as keep the
+// group's tensors (`bytes_per_head` each) within `budget_bytes` of L2, or the value of the environment variable `env`
+// (read on every call: a handful of launches per step); clamped to [1, n_heads].
+int attn_head_group(const char* env, long long bytes_per_head, long long budget_bytes, int n_heads);
+
 // 4-D bf16 map over a packed [B, T, heads, hd] tensor: dims (hd, heads, T, B), box (64, 1, box_rows, 1).
 int make_qkv_map(CUtensorMap* map, const void* base, int B, int T, int heads, int hd, int box_rows);
 
@@ -441,6 +446,20 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
       : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)));
   return d;
+}
+
+// Heavy-first order for causal attention grids. Tiles of one (batch, head) differ in work by the causal mask (rank 0
+// heaviest); blocks start in linear order, so the order decides the tail: with all tiles of one head adjacent, the last
+// head's heaviest tiles start when the grid is almost drained and run alone. Here the heads are taken in groups of
+// `group` (few enough that the group's tensors stay in L2), and inside a group all heads' rank-0 tiles come first, then
+// all rank-1 tiles, ...: every group, the last one included, ends on its lightest tiles.
+//   linear block id -> (rank of the tile within its head, head)
+__device__ __forceinline__ void heavy_first_decode(int linear, int n_tiles, int n_heads, int group, int& tile_rank, int& head) {
+  const int per_group = n_tiles * group;
+  const int g = linear / per_group, r = linear - g * per_group;
+  const int g_heads = min(group, n_heads - g * group);       // the last group may be smaller
+  tile_rank = r / g_heads;
+  head = g * group + (r - tile_rank * g_heads);
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -127,6 +127,14 @@ int num_sms() {
   return n;
 }
 
+int attn_head_group(const char* env, long long bytes_per_head, long long budget_bytes, int n_heads) {
+  long long g = bytes_per_head > 0 ? budget_bytes / bytes_per_head : 1;
+  const char* v = getenv(env);
+  if (v != nullptr && atoi(v) > 0) g = atoi(v);
+  if (g > n_heads) g = n_heads;
+  return g < 1 ? 1 : (int)g;
+}
+
 }  // namespace tlm
 
 TLM_API unsigned long long tlm_launch_count() { return tlm::g_launches; }
