@@ -25,7 +25,7 @@ communication themselves:
 norm / loss reductions, checkpoint traffic. Set `TLM_COMM=nccl` to run the
 optimizer collectives through NCCL instead (the baseline for comparisons), and
 `TLM_NVLS=0` / `1` to force plain peer loads / stores or the NVSwitch multicast
-mapping (default: multicast from 4 ranks up).
+mapping (default: multicast from 5 ranks up).
 """
 from __future__ import annotations
 
@@ -119,10 +119,12 @@ class _Peer:
         self.ptr_array = (ctypes.c_void_p * self.n)(*ptrs)
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         mc = mc + off if mc else 0
-        # TLM_NVLS: 1 = always use the NVSwitch multicast mapping, 0 = never, unset = from 4 ranks up (at 2 ranks
-        # plain peer loads are faster than the in-switch reduction: 0.90 ms vs 1.64 ms on a 512 MiB shard)
+        # TLM_NVLS: 1 = always use the NVSwitch multicast mapping, 0 = never, unset = from 5 ranks up. Measured on a
+        # 1 GiB fp32 buffer: reduce-scatter 0.90 ms (peer loads) vs 1.64 ms (in-switch reduction) at 2 ranks, 1.25 vs
+        # 1.57 ms at 4; AdamW + all-gather 0.64 vs 0.80 ms at 4. The peer form moves (n-1)/n of the buffer per rank at
+        # ~650 GB/s, the multicast form 1/n of it at ~170 GB/s, so they cross between 4 and 5 ranks.
         mode = os.environ.get("TLM_NVLS", "auto")
-        use = mode == "1" or (mode not in ("0", "1") and self.n >= 4)
+        use = mode == "1" or (mode not in ("0", "1") and self.n >= 5)
         self.mc_ptr = mc if use else 0
 
 
