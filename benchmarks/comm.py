@@ -12,6 +12,9 @@ and prints one JSON line per case with the bytes that must cross NVLink per rank
 fraction of the measured peer-copy bandwidth (770 GB/s per direction per GPU on this class of machine).
 For the reduce-scatter a rank receives (n-1)/n of its shard from peers ((n-1) shard-sized reads through P2P, one
 switch-reduced shard through NVLS); for the all-gather it sends its shard to n-1 peers (once through NVLS).
+The byte column counts what a rank RECEIVES. In the other direction a rank's links carry (n-1)/n of its buffer with
+peer loads but its whole buffer with the in-switch reduction (the switch pulls every rank's copy of every shard), which
+is why the multicast reduce-scatter takes the same time at every group size and never beats peer loads.
 """
 from __future__ import annotations
 

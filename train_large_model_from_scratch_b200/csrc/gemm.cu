@@ -778,18 +778,56 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
+      } else if (EPI == EPI_ROWS) {
+        // Each output row goes to a looked-up (buffer, row), usually in another GPU's memory. The accumulator leaves
+        // tensor memory one row per lane; stored that way every store instruction would write 32 separate 16-byte
+        // pieces, a poor packet size for NVLink. So each 64-column slab is staged in shared memory (swizzled, one
+        // 128-byte row per lane) and written back with 8 lanes per row: one instruction stores four whole 128-byte
+        // row pieces. The lane that owns a row holds its destination; the writers fetch it with shuffles.
+        uint8_t* buf = smem_al + STAGES * STAGE_BYTES + (warp - 2) * 2 * EPI_BUF_BYTES;
+        unsigned long long dst_bits = 0;               // 0: the row is dropped
+        {
+          const int dr = row_ok ? p.rs_rank[row] : -1;
+          const long long drow = dr >= 0 ? p.rs_row[row] : -1;
+          if (dr >= 0 && dr < MAX_HEAD_DST && drow >= 0 && drow < p.rs_rows)
+            dst_bits = reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16*>(p.rs_dst[dr]) + drow * p.ldc);
+          else if (dr >= 0)
+            report_status(p.status, (61u << 8) | 1u);
+        }
+        const int sub_row = lane >> 3, chunk = lane & 7;
+#pragma unroll 1
+        for (int slab = 0; slab < BN / 64; ++slab) {
+          const int col = t.n0 + slab * 64;
+          if (col >= p.N) break;                               // warp-uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld32(taddr + slab * 64, r0);
+          tmem_ld32(taddr + slab * 64 + 32, r1);
+          tmem_ld_wait();
+          uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t* r = ch < 4 ? r0 : r1;
+            const int j = (ch & 3) * 8;
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            v.y = pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            v.z = pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            v.w = pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = v;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + sub_row;                     // row within the warp's 32
+            const unsigned long long d = __shfl_sync(0xffffffffu, dst_bits, r);
+            const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((chunk ^ (r & 7)) << 4));
+            if (d != 0 && col + chunk * 8 < p.N)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(d) + col + chunk * 8) = v;
+          }
+          __syncwarp();
+        }
       } else {
-      __nv_bfloat16* scat = nullptr;                 // row-scatter destination of this thread's row
-      bool row_live = row_ok;
-      if (EPI == EPI_ROWS) {
-        const int dr = row_ok ? p.rs_rank[row] : -1;
-        const long long drow = dr >= 0 ? p.rs_row[row] : -1;
-        if (dr >= 0 && dr < MAX_HEAD_DST && drow >= 0 && drow < p.rs_rows)
-          scat = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[dr]) + drow * p.ldc;
-        else if (dr >= 0)
-          report_status(p.status, (61u << 8) | 1u);
-        row_live = scat != nullptr;
-      }
+      const bool row_live = row_ok;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -797,9 +835,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         tmem_ld_wait();
         const int col = t.n0 + c;
         if (row_live && col < p.N) {
-          if (EPI == EPI_BF16 || EPI == EPI_ROWS) {
-            __nv_bfloat16* out = scat != nullptr ? scat + col
-                                                 : reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
+          if (EPI == EPI_BF16) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + t.c_off + (long long)row * p.ldc + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col + j < p.N) {

@@ -25,7 +25,7 @@ communication themselves:
 norm / loss reductions, checkpoint traffic. Set `TLM_COMM=nccl` to run the
 optimizer collectives through NCCL instead (the baseline for comparisons), and
 `TLM_NVLS=0` / `1` to force plain peer loads / stores or the NVSwitch multicast
-mapping (default: multicast from 5 ranks up).
+mapping (default: plain peer loads / stores at every group size).
 """
 from __future__ import annotations
 
@@ -119,12 +119,14 @@ class _Peer:
         self.ptr_array = (ctypes.c_void_p * self.n)(*ptrs)
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         mc = mc + off if mc else 0
-        # TLM_NVLS: 1 = always use the NVSwitch multicast mapping, 0 = never, unset = from 5 ranks up. Measured on a
-        # 1 GiB fp32 buffer: reduce-scatter 0.90 ms (peer loads) vs 1.64 ms (in-switch reduction) at 2 ranks, 1.25 vs
-        # 1.57 ms at 4; AdamW + all-gather 0.64 vs 0.80 ms at 4. The peer form moves (n-1)/n of the buffer per rank at
-        # ~650 GB/s, the multicast form 1/n of it at ~170 GB/s, so they cross between 4 and 5 ranks.
-        mode = os.environ.get("TLM_NVLS", "auto")
-        use = mode == "1" or (mode not in ("0", "1") and self.n >= 5)
+        # TLM_NVLS=1 selects the NVSwitch multicast mapping (`multimem.ld_reduce` / `multimem.st`); the default is plain
+        # peer loads / stores. Measured on a 1 GiB fp32 buffer: reduce-scatter 0.85 - 0.90 ms (peer loads) vs 1.63 ms
+        # (in-switch reduction) at 2 ranks, 1.25 vs 1.57 ms at 4; AdamW + all-gather 0.64 vs 0.80 ms at 4. The in-switch
+        # reduction takes ~1.6 ms at any group size because every GPU sends its WHOLE buffer through its links (its own
+        # shard included), 1 GiB at ~670 GB/s, while peer loads send (n-1)/n of it; the multicast form only saves
+        # ingress, and the links are full duplex. More loads in flight per thread did not change it.
+        mode = os.environ.get("TLM_NVLS", "0")
+        use = mode == "1"
         self.mc_ptr = mc if use else 0
 
 
