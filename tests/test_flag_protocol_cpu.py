@@ -32,3 +32,16 @@ def test_protocol_properties_hold_under_random_arrival_orders(binary, ranks, rou
     r = subprocess.run([binary, str(ranks), str(rounds), str(seed), str(start)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.startswith("ok:")
+
+
+def test_attention_block_order_is_a_heavy_first_bijection():
+    """`csrc/tile_order.h` (the decode the attention kernels apply to their linear block id) as a host program."""
+    if shutil.which("g++") is None:
+        pytest.skip("no host compiler")
+    out = os.path.join(tempfile.mkdtemp(prefix="tlm_order_"), "tile_order_host_test")
+    cmd = ["g++", "-O2", "-std=c++17", "-I", os.path.join(ROOT, "train_large_model_from_scratch_b200", "csrc"),
+           "-o", out, os.path.join(ROOT, "tests", "tile_order_host_test.cpp")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([out], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr

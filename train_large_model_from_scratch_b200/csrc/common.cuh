@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #include "flag_protocol.h"
+#include "tile_order.h"
 
 #define TLM_API extern "C" __attribute__((visibility("default")))
 
@@ -446,20 +447,6 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
       : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)));
   return d;
-}
-
-// Heavy-first order for causal attention grids. Tiles of one (batch, head) differ in work by the causal mask (rank 0
-// heaviest); blocks start in linear order, so the order decides the tail: with all tiles of one head adjacent, the last
-// head's heaviest tiles start when the grid is almost drained and run alone. Here the heads are taken in groups of
-// `group` (few enough that the group's tensors stay in L2), and inside a group all heads' rank-0 tiles come first, then
-// all rank-1 tiles, ...: every group, the last one included, ends on its lightest tiles.
-//   linear block id -> (rank of the tile within its head, head)
-__device__ __forceinline__ void heavy_first_decode(int linear, int n_tiles, int n_heads, int group, int& tile_rank, int& head) {
-  const int per_group = n_tiles * group;
-  const int g = linear / per_group, r = linear - g * per_group;
-  const int g_heads = min(group, n_heads - g * group);       // the last group may be smaller
-  tile_rank = r / g_heads;
-  head = g * group + (r - tile_rank * g_heads);
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
