@@ -416,6 +416,9 @@ def run_extras(args) -> dict:
                    "--master-addr", "127.0.0.1", "--master-port", str(_free_port())] + tail
         else:
             cmd = [sys.executable] + tail
+            # a single-process child makes its own rendezvous: never on the port this process's (possibly still
+            # listening) store used
+            env["MASTER_ADDR"], env["MASTER_PORT"] = "127.0.0.1", str(_free_port())
         t0 = time.time()
         try:
             proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
