@@ -463,7 +463,7 @@ def main():
                          "type-checks for moe_intermediate_size == hidden_size)")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline configuration only: do not measure the MoE and Ulysses configurations afterwards")
-    ap.add_argument("--extra-timeout", type=int, default=900, help="time limit of one extra configuration's job (s)")
+    ap.add_argument("--extra-timeout", type=int, default=420, help="time limit of one extra configuration's job (s)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     _select_config(args.config, args.gpus)
