@@ -83,6 +83,20 @@ def test_ulysses_peer_path_matches_nccl_path():
     _close(ref["norms"], plain["norms"], 2e-2)
 
 
+def test_ulysses_with_fewer_kv_heads_than_ranks_matches_nccl_path():
+    """One KV head shared by both ranks' query heads (4 query heads, 1 KV head, sep 2): the QKV epilogue replicates
+    the head to both owners and the sequence owners sum the replicas' dK / dV; against the library-collective path
+    and against plain data parallelism."""
+    one_kv = [f if FLAGS[i - 1] != "--num_key_value_heads" else "1" for i, f in enumerate(FLAGS)]
+    flags = [f if FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(one_kv)] + ["--sep_size", "2"]
+    ref = _run(2, {"TLM_COMM": "nccl"}, flags)
+    peer = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, flags)
+    _close(ref["losses"], peer["losses"], 2e-3)
+    _close(ref["norms"], peer["norms"], 2e-2)
+    dp = _run(2, {"TLM_COMM": "symm", "TLM_NVLS": "0"}, one_kv + ["--sep_size", "1"])
+    _close(dp["losses"], peer["losses"], 5e-3)
+
+
 def test_expert_parallel_peer_path_matches_nccl_path_and_single_group():
     flags4 = [f if f != "2" or FLAGS[i - 1] != "--batch_size" else "4" for i, f in enumerate(FLAGS)]
     ref = _run(2, {"TLM_COMM": "nccl"}, flags4 + MOE + ["--sep_size", "2"])

@@ -73,7 +73,9 @@ struct GemmParams {
   // where owner / slot follow the Ulysses head plan: q head h -> (h / q_l, h % q_l), k head j ->
   // (j / kv_l, q_l + j % kv_l), v head j -> (j / kv_l, q_l + kv_l + j % kv_l). With one destination and
   // q_l = Hq, kv_l = Hkv this is the identity layout [B, T, Hq + 2 Hkv, hd].
-  int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot;
+  // kv_rep > 1 (fewer KV heads than destinations): k / v head j is needed by the kv_rep ranks that own its query
+  // heads, so its tile is stored kv_rep times: dst[j * kv_rep + c], slots q_l (k) and q_l + 1 (v), c < kv_rep.
+  int hd, rows_per_batch, row_off, Hq, Hkv, q_l, kv_l, n_rot, kv_rep;
   const __half2* cs;        // [rows_per_batch, hd] (cos, sin) pairs in fp16: |error| < 2^-11, below the bf16 rounding of
                             // the rotated outputs, and half the table bytes of two fp32 tables
   // EPI_SWIGLU (MLP forward): B is the fused [2 I, K] weight (gate rows, then up rows), N = I. A tile holds the
@@ -473,8 +475,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         for (int hh = 0; hh < heads_per_tile; ++hh) {
           const int head = t.n0 / hd + hh;
           const bool live = rows_ok && head < n_heads;          // warp-uniform
-          int dest, slot;
+          int dest, slot, copies = 1;
           if (head < p.Hq) { dest = head / p.q_l; slot = head - dest * p.q_l; }
+          else if (p.kv_rep > 1) {                              // replicated KV heads: one local k and one local v slot
+            const bool is_v = head >= p.Hq + p.Hkv;
+            dest = (head - p.Hq - (is_v ? p.Hkv : 0)) * p.kv_rep; slot = p.q_l + (is_v ? 1 : 0); copies = p.kv_rep;
+          }
           else if (head < p.Hq + p.Hkv) { const int k = head - p.Hq; dest = k / p.kv_l; slot = p.q_l + (k - dest * p.kv_l); }
           else { const int v = head - p.Hq - p.Hkv; dest = v / p.kv_l; slot = p.q_l + p.kv_l + (v - dest * p.kv_l); }
           const bool rot = head < p.n_rot;
@@ -495,9 +501,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             __syncwarp();
             if (lane == 0) {
               if (live)
-                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                             ::"l"((uint64_t)(dst_maps + dest)), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(0), "r"(slot),
-                               "r"(p.row_off + t0), "r"(bi) : "memory");
+                for (int c = 0; c < copies; ++c)
+                  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                               ::"l"((uint64_t)(dst_maps + dest + c)), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(0), "r"(slot),
+                                 "r"(p.row_off + t0), "r"(bi) : "memory");
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           } else {                                              // hd == 128: both staging tiles hold one head
@@ -519,11 +526,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             __syncwarp();
             if (lane == 0) {
               if (live) {
+                for (int c = 0; c < copies; ++c)
 #pragma unroll
-                for (int s2 = 0; s2 < 2; ++s2)
-                  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                               ::"l"((uint64_t)(dst_maps + dest)), "r"(ebuf_s + s2 * EPI_BUF_BYTES), "r"(s2 * 64), "r"(slot),
-                                 "r"(p.row_off + t0), "r"(bi) : "memory");
+                  for (int s2 = 0; s2 < 2; ++s2)
+                    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                                 ::"l"((uint64_t)(dst_maps + dest + c)), "r"(ebuf_s + s2 * EPI_BUF_BYTES), "r"(s2 * 64), "r"(slot),
+                                   "r"(p.row_off + t0), "r"(bi) : "memory");
               }
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
@@ -1116,12 +1124,18 @@ TLM_API int tlm_gemm_set_pair(int mode) {
 TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
                            void* const* dst_ptrs, int n_dst, int batch, int rows_per_batch, int dst_rows, int dst_heads,
                            int row_off, int Hq, int Hkv, int q_l, int kv_l, int hd, int n_rot, const void* cs,
-                           cudaStream_t stream) {
+                           int kv_rep, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((hd != 64 && hd != 128) || rows_per_batch % 32 != 0 || n_dst < 1 || n_dst > MAX_HEAD_DST) return -4;
   if (M != batch * rows_per_batch || N != (Hq + 2 * Hkv) * hd || q_l <= 0 || Hq % q_l != 0) return -5;
-  if (Hkv > 0 && (kv_l <= 0 || Hkv % kv_l != 0)) return -5;
-  if (Hq / q_l > n_dst || (Hkv > 0 && Hkv / kv_l > n_dst)) return -5;
+  if (kv_rep < 1) kv_rep = 1;
+  if (kv_rep > 1) {                     // replicated KV heads: every destination holds exactly one k and one v head
+    if (Hkv <= 0 || Hkv * kv_rep > n_dst || Hq / q_l > n_dst) return -5;
+    kv_l = 1;
+  } else {
+    if (Hkv > 0 && (kv_l <= 0 || Hkv % kv_l != 0)) return -5;
+    if (Hq / q_l > n_dst || (Hkv > 0 && Hkv / kv_l > n_dst)) return -5;
+  }
   if (n_rot > 0 && cs == nullptr) return -5;
   GemmParams p{};
   if (!b_mn) take_pending_waits(p);               // x W^T: may be the first reader of its weights after an optimizer step
@@ -1141,7 +1155,7 @@ TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, lo
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.status = status_word(); p.groups = 0;
   p.split_k = 1; p.k_chunk = K;
   p.hd = hd; p.rows_per_batch = rows_per_batch; p.row_off = row_off; p.Hq = Hq; p.Hkv = Hkv;
-  p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cs = (const __half2*)cs;
+  p.q_l = q_l; p.kv_l = kv_l > 0 ? kv_l : 1; p.n_rot = n_rot; p.cs = (const __half2*)cs; p.kv_rep = kv_rep;
   if (pair) {
     const int ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
     return b_mn ? launch_heads_pair<true>(ma, mb, dst, p, ptiles, stream) : launch_heads_pair<false>(ma, mb, dst, p, ptiles, stream);

@@ -110,13 +110,16 @@ class Attention(nn.Module):
                                                              self.config.rope_variant)}
         return self._rope_cache_full[key]
 
-    def _peer_path(self, qkv: torch.Tensor, sp: int) -> bool:
-        if not (qkv.is_cuda and qkv.dtype == torch.bfloat16):
+    def _symm_ok(self, x: torch.Tensor) -> bool:
+        if not (x.is_cuda and x.dtype == torch.bfloat16):
             return False
         from ...parallel import symm
+        return symm.use_symm()
+
+    def _peer_path(self, qkv: torch.Tensor, sp: int) -> bool:
         from ...parallel.sequence_parallel import ulysses_peer
-        return symm.use_symm() and ulysses_peer.supported(self.num_attention_heads, self.num_key_value_heads, sp,
-                                                          self.head_dim)
+        return self._symm_ok(qkv) and ulysses_peer.supported(self.num_attention_heads, self.num_key_value_heads, sp,
+                                                             self.head_dim)
 
     def forward(self, h: torch.Tensor, B: int | None = None, T_local: int | None = None) -> torch.Tensor:
         """h: `[B*T_local, D]` (or `[B, T_local, D]`) in the compute dtype -> same shape."""
@@ -140,7 +143,7 @@ class Attention(nn.Module):
                 y = F_ops.linear(o.reshape(B * T_local, Hq * hd), self.c_proj.weight)
                 return y.view(shape)
             from ...parallel.sequence_parallel import ulysses_peer
-            if self._peer_path(h, sp) and ulysses_peer.fused_ok(Hq, Hkv, sp, hd, T_local):
+            if self._symm_ok(h) and ulysses_peer.fused_ok(Hq, Hkv, sp, hd, T_local):      # incl. Hkv < sp (replicated KV heads)
                 cos_f, sin_f = self._rope_full(T_local * sp, h.device)
                 y = ulysses_peer.attention_block(h, self._qkv_weight, self.c_proj.weight, Hq, Hkv, hd, B, T_local,
                                                  self._rope_fp16(T_local, h.device), cos_f, sin_f, id(self), group)

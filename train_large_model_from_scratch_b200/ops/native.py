@@ -55,7 +55,7 @@ _SIGS = {
     "tlm_get_deterministic": (_I, []),
     "tlm_gemm_set_pair": (_I, [_I]),
     "tlm_gemm": (_I, [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _I, _I, _I, _P]),
-    "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
+    "tlm_gemm_heads": (_I, [_P, _P, _I, _I, _I, _LL, _LL, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
     "tlm_gemm_swiglu": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
     "tlm_gemm_swiglu_bwd": (_I, [_P, _P, _P, _P, _I, _I, _I, _LL, _LL, _P]),
     "tlm_gemm_swiglu_grouped": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _P]),
@@ -273,12 +273,14 @@ def rope_table_fp16(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
 
 def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: int, batch: int, rows_per_batch: int,
                dst_rows: int, dst_heads: int, row_off: int, n_q: int, n_kv: int, q_l: int, kv_l: int, hd: int,
-               n_rot: int, cs: torch.Tensor | None) -> None:
+               n_rot: int, cs: torch.Tensor | None, kv_rep: int = 1) -> None:
     """Projection GEMM with the head-scatter epilogue (`csrc/gemm.cu`, `tlm_gemm_heads`):
     `x [batch*rows_per_batch, K]` times `w` (`[N, K]`, or `[K, N]` when `b_mn`), N = (n_q + 2 n_kv) * hd;
     head h of row (b, t) -> RoPE (heads < n_rot, table `cs` from `rope_table_fp16`) ->
     `dst[owner(h)][b, row_off + t, slot(h), :]`.
-    `dst_ptrs` is a ctypes array of `n_dst` device addresses (this rank's own tensor or peers' buffers)."""
+    `dst_ptrs` is a ctypes array of `n_dst` device addresses (this rank's own tensor or peers' buffers).
+    `kv_rep > 1` (fewer KV heads than destinations): k / v head j goes to the `kv_rep` destinations
+    `j * kv_rep .. j * kv_rep + kv_rep - 1`, slots `q_l` and `q_l + 1`."""
     M, K, lda = _rows(x)
     if b_mn:
         K2, N, ldb = _rows(w)
@@ -288,7 +290,7 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, b_mn: bool, dst_ptrs, n_dst: in
     assert cs is None or (cs.dtype == torch.float16 and cs.shape == (rows_per_batch, hd, 2) and cs.is_contiguous())
     _check(lib().tlm_gemm_heads(x.data_ptr(), w.data_ptr(), M, N, K, lda, ldb, int(b_mn), dst_ptrs, n_dst, batch,
                                 rows_per_batch, dst_rows, dst_heads, row_off, n_q, n_kv, q_l, kv_l, hd, n_rot,
-                                _ptr(cs), _stream()), "gemm_heads")
+                                _ptr(cs), int(kv_rep), _stream()), "gemm_heads")
 
 
 def swiglu_epilogue_ok(I: int) -> bool:

@@ -202,19 +202,25 @@ class _UlyssesAttention(torch.autograd.Function):
                 leave tensor memory) get the transposed RoPE and are stored head->seq into the sequence owners'
                 packed gradient buffer, which feeds the QKV weight- and data-gradient GEMMs.
 
-    No stand-alone scatter kernel is left; each exchange ends with a flag barrier."""
+    No stand-alone scatter kernel is left; each exchange ends with a flag barrier.
+
+    Fewer KV heads than ranks (`n_kv < sp`, `sp % n_kv == 0`): KV head j is replicated to the `sp / n_kv` ranks that
+    own its query heads (the QKV epilogue stores its tile once per owner), every rank attends with one local KV
+    head, and the partial dK / dV of the replicas come back into separate slots of the packed gradient buffer
+    (`n_q + 2 sp` heads), where the sequence owner sums them before the QKV gradient GEMMs."""
 
     @staticmethod
     def forward(ctx, h, w_qkv, w_out, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, layer_key, group):
         from ...ops import attention_cuda
         st = PeerState.get(group)
         sp, me = st.sp, st.me
-        _, q_l, kv_l = ulysses.head_plan(n_q, n_kv, sp)
+        kv_rep = sp // n_kv if n_kv < sp else 1
+        q_l, kv_l = n_q // sp, (1 if kv_rep > 1 else n_kv // sp)
         hpr = q_l + 2 * kv_l
         T_full = sp * T_l
         ex_qkv = st.buffer((layer_key, "qkv"), (B, T_full, hpr, hd), h.device)
         native.gemm_heads(h, w_qkv, False, ex_qkv.peer.ptr_array, sp, B, T_l, T_full, hpr, me * T_l, n_q, n_kv,
-                          q_l, kv_l, hd, n_q + n_kv, cs_l)
+                          q_l, kv_l, hd, n_q + n_kv, cs_l, kv_rep)
         st.barrier()
         qkv_l = ex_qkv.tensor
         ex_o = st.buffer((layer_key, "o"), (B, T_l, n_q, hd), h.device)
@@ -242,12 +248,20 @@ class _UlyssesAttention(torch.autograd.Function):
         native.gemm_heads(dy, w_out, True, ex_do.peer.ptr_array, sp, B, T_l, T_full, q_l, me * T_l, n_q, 0, q_l, 1,
                           hd, 0, None)
         st.barrier()
-        Ht = n_q + 2 * n_kv
+        kv_rep = sp // n_kv if n_kv < sp else 1
+        n_kv_slots = sp if kv_rep > 1 else n_kv           # replicated KV heads: one dK and one dV slot per source rank
+        Ht = n_q + 2 * n_kv_slots
         ex_d = st.buffer((layer_key, "dqkv"), (B, T_l, Ht, hd), dy.device)
         attention_cuda.bwd_scatter(ex_do.tensor, qkv_l, o, lse, q_l, kv_l, (cos_f, sin_f), ex_d.peer.ptr_array, sp, T_l, Ht,
-                                   me * q_l, n_q + me * kv_l, n_q + n_kv + me * kv_l)
+                                   me * q_l, n_q + me * kv_l, n_q + n_kv_slots + me * kv_l)
         st.barrier()
-        d2 = ex_d.tensor.view(B * T_l, -1)
+        if kv_rep > 1:
+            # rank j * kv_rep + c holds replica c of KV head j: slots of one head are adjacent, sum them in fp32
+            d = ex_d.tensor
+            dkv = d[:, :, n_q:].reshape(B, T_l, 2 * n_kv, kv_rep, hd).float().sum(3).to(d.dtype)
+            d2 = torch.cat([d[:, :, :n_q], dkv], dim=2).view(B * T_l, -1)
+        else:
+            d2 = ex_d.tensor.view(B * T_l, -1)
         native.gemm_tn_accum(d2, h, _main_grad(w_qkv))
         dh = native.gemm_nn(d2, w_qkv) if ctx.needs_input_grad[0] else None
         return (dh,) + (None,) * 12
@@ -262,7 +276,8 @@ def attention_block(h, w_qkv, w_out, n_q, n_kv, hd, B, T_l, cs_l, cos_f, sin_f, 
 def fused_ok(n_q: int, n_kv: int, sp: int, hd: int, T_l: int) -> bool:
     """Shapes for which the exchanges ride on the GEMM epilogues."""
     import os
-    return (supported(n_q, n_kv, sp, hd) and native.heads_epilogue_ok(hd, T_l, sp)
+    heads_ok = n_q % sp == 0 and (n_kv % sp == 0 or (sp % n_kv == 0 and (n_q // n_kv) % (sp // n_kv) == 0))
+    return (heads_ok and native.heads_epilogue_ok(hd, T_l, sp)
             and os.environ.get("TLM_SP_FUSED", "1") != "0")       # 0: keep the stand-alone scatter kernels
 
 
