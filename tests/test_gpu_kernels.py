@@ -184,6 +184,27 @@ def test_gemm_heads_scatter_plan(nat, gemm_mode):
         assert float(bufs[r][:, :me * T_l].abs().max()) == 0.0            # rows of the other source stay untouched
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_gemm_heads_replicates_kv_heads_to_their_owners(nat, gemm_mode, hd):
+    """Fewer KV heads than destinations (8 query heads, 2 KV heads, 4 destinations, all local buffers here): q heads go to
+    their owner, KV head j is stored to destinations 2 j and 2 j + 1 in the slots behind their q heads; no RoPE."""
+    import ctypes
+    Hq, Hkv, B, T_l, sp, me = 8, 2, 2, 128, 4, 2
+    q_l, rep = Hq // sp, sp // Hkv
+    x, w = _rand(B * T_l, 192, seed=35), _rand((Hq + 2 * Hkv) * hd, 192, scale=0.05, seed=36)
+    bufs = [torch.zeros(B, sp * T_l, q_l + 2, hd, dtype=torch.bfloat16, device="cuda") for _ in range(sp)]
+    dst = (ctypes.c_void_p * sp)(*[b.data_ptr() for b in bufs])
+    nat.gemm_heads(x, w, False, dst, sp, B, T_l, sp * T_l, q_l + 2, me * T_l, Hq, Hkv, q_l, 1, hd, 0, None, rep)
+    nat.raise_on_device_status()
+    ref = (x.float() @ w.float().t()).view(B, T_l, Hq + 2 * Hkv, hd)
+    for r in range(sp):
+        got = bufs[r][:, me * T_l:(me + 1) * T_l]
+        want = torch.cat([ref[:, :, r * q_l:(r + 1) * q_l], ref[:, :, Hq + r // rep:Hq + r // rep + 1],
+                          ref[:, :, Hq + Hkv + r // rep:Hq + Hkv + r // rep + 1]], dim=2)
+        assert _rel_err(got, want) < 6e-3, r
+        assert float(bufs[r][:, :me * T_l].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("M,I,K", [(200, 128, 64), (512, 384, 256), (4096, 1024, 512)])
 def test_gemm_swiglu_epilogues(nat, gemm_mode, M, I, K):
     """gate|up GEMM that also emits act, and the down-projection dgrad that emits d(gate|up), against the
