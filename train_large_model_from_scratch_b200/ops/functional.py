@@ -121,7 +121,7 @@ class _Linear(torch.autograd.Function):
         mg = _main_grad(w)
         dy = dy.contiguous()
         if _use_native(x, w):
-            native.gemm_tn_accum(dy, x, mg, side_ok=True)       # mg[N,K] += dy[M,N]^T @ x[M,K]
+            native.gemm_tn_accum(dy, x, mg)                     # mg[N,K] += dy[M,N]^T @ x[M,K]
             dx = native.gemm_nn(dy, w) if ctx.needs_input_grad[0] else None
         else:
             mg.add_((dy.float().t() @ x.float()))
@@ -188,7 +188,7 @@ class _QKVProject(torch.autograd.Function):
         w = ctx.weight
         d = native.rope_qk(d_rot.contiguous(), cos, sin, ctx.n_rot, True)      # in place: the gradient is ours
         d2 = d.view(h.shape[0], -1)
-        native.gemm_tn_accum(d2, h, _main_grad(w), side_ok=True)
+        native.gemm_tn_accum(d2, h, _main_grad(w))
         dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
         return dh, None, None, None, None, None, None, None, None, None
 
@@ -218,7 +218,7 @@ class _QKVAttention(torch.autograd.Function):
         w = ctx.weight
         d = native.flash_attn_bwd(do.contiguous(), qkv, o, lse, n_q, n_kv, True, rope=(cos, sin))
         d2 = d.view(h.shape[0], -1)
-        native.gemm_tn_accum(d2, h, _main_grad(w), side_ok=True)
+        native.gemm_tn_accum(d2, h, _main_grad(w))
         dh = native.gemm_nn(d2, w) if ctx.needs_input_grad[0] else None
         return dh, None, None, None, None, None, None, None, None, None
 
@@ -350,9 +350,9 @@ class _SwiGLUMLP(torch.autograd.Function):
         x, gu, act = ctx.saved_tensors
         w_gu, w_down = ctx.w_gu, ctx.w_down
         dy = dy.contiguous()
-        native.gemm_tn_accum(dy, act, _main_grad(w_down), side_ok=True)
+        native.gemm_tn_accum(dy, act, _main_grad(w_down))
         dgu = native.gemm_swiglu_bwd(dy, w_down, gu)
-        native.gemm_tn_accum(dgu, x, _main_grad(w_gu), side_ok=True)
+        native.gemm_tn_accum(dgu, x, _main_grad(w_gu))
         dx = native.gemm_nn(dgu, w_gu) if ctx.needs_input_grad[0] else None
         return dx, None, None
 

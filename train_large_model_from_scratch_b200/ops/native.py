@@ -247,50 +247,15 @@ def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
-# Weight-gradient side stream (experiment, off by default: TLM_WGRAD_STREAM=1, one GPU only). Nothing in the backward
-# pass reads a weight gradient, so the layers' weight-gradient GEMMs can run on a second stream beside the kernels of the
-# following layers (the memory-bound ones fit next to a GEMM's CTAs); the optimizer step joins the stream. The operands
-# are kept alive until the join, so no allocator stream bookkeeping is needed and the fork / join is recordable.
-_WGRAD = {"stream": None, "keep": []}
-
-
-def _wgrad_side_stream():
-    if os.environ.get("TLM_WGRAD_STREAM", "0") != "1":
-        return None
-    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
-        return None                          # the bucket reductions under the backward pass would need the join as well
-    if _WGRAD["stream"] is None:
-        _WGRAD["stream"] = torch.cuda.Stream()
-    return _WGRAD["stream"]
-
-
-def join_wgrad_stream() -> None:
-    """Make the current stream wait for the weight-gradient GEMMs queued on the side stream (call before anything reads
-    or clears the gradient buffer)."""
-    side = _WGRAD["stream"]
-    if side is not None and _WGRAD["keep"]:
-        torch.cuda.current_stream().wait_stream(side)
-        _WGRAD["keep"].clear()
-
-
-def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor, side_ok: bool = False) -> None:
+def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor) -> None:
     """acc[N,K] (fp32) += dy[M,N]^T @ x[M,K]: the weight-gradient GEMM, both
-    operands MN-major, accumulated into the fp32 gradient buffer. `side_ok`: this gradient is touched by nothing
-    else before the optimizer step, so the GEMM may go to the weight-gradient side stream when that is enabled."""
+    operands MN-major, accumulated into the fp32 gradient buffer."""
     if dy.shape[1] % 8:                      # output rows beyond acc.shape[0] are masked by the kernel (M = N rows)
         dy = _pad8(dy, 1)
     M, N, lda = _rows(dy)
     M2, K, ldb = _rows(x)
     N = acc.shape[0]
     assert M == M2 and acc.dtype == torch.float32 and acc.shape[1] == K
-    side = _wgrad_side_stream() if side_ok else None
-    if side is not None:
-        side.wait_stream(torch.cuda.current_stream())
-        _WGRAD["keep"].append((dy, x))
-        with torch.cuda.stream(side):
-            _check(lib().tlm_gemm(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), N, K, M, lda, ldb, acc.stride(0),
-                                  1, 1, EPI_F32_ACC, _stream()), "gemm_tn_accum")
-        return
     _check(lib().tlm_gemm(dy.data_ptr(), x.data_ptr(), acc.data_ptr(), N, K, M, lda, ldb, acc.stride(0),
                           1, 1, EPI_F32_ACC, _stream()), "gemm_tn_accum")
 

@@ -246,8 +246,6 @@ class FusedAdamW:
         g = self.param_groups[0]
         inv = 1.0 / self.grad_divisor
         norm_sq = None
-        if native.available():
-            native.join_wgrad_stream()           # weight-gradient GEMMs on the side stream (when enabled)
         if self._comm is not None:
             self._comm.join()                    # bucket reductions started during backward
         for s in self.shards:
