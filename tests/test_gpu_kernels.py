@@ -149,7 +149,8 @@ def test_rope(nat, hd, variant):
 
 
 @pytest.mark.parametrize("hd,Hq,Hkv,B,T,K", [(64, 4, 2, 2, 96, 192), (128, 2, 1, 1, 160, 256), (64, 16, 8, 1, 256, 1024),
-                                              (64, 3, 1, 2, 32, 64)])
+                                              (64, 3, 1, 2, 32, 64), (32, 8, 2, 2, 96, 192), (32, 32, 4, 1, 256, 1024),
+                                              (32, 3, 1, 1, 64, 64)])
 def test_gemm_heads_rope_epilogue(nat, gemm_mode, hd, Hq, Hkv, B, T, K):
     """QKV projection whose epilogue rotates q/k heads and writes the packed tensor, against GEMM -> RoPE in fp32."""
     import ctypes

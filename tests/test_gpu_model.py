@@ -16,10 +16,12 @@ def _build(device, dtype, **over):
     return GPT(ModelConfig(**kw), device=device, compute_dtype=dtype)
 
 
-def test_dense_model_matches_cpu_oracle():
+@pytest.mark.parametrize("heads", [(4, 2), (8, 2)])          # head dim 64, and 32 (the shipped 0.25B model's)
+def test_dense_model_matches_cpu_oracle(heads):
     from train_large_model_from_scratch_b200.ops import native
-    gpu = _build("cuda", torch.bfloat16)
-    cpu = _build("cpu", torch.float32)
+    over = dict(num_attention_heads=heads[0], num_key_value_heads=heads[1])
+    gpu = _build("cuda", torch.bfloat16, **over)
+    cpu = _build("cpu", torch.float32, **over)
     cpu.dense_buf.params.copy_(gpu.dense_buf.params.float().cpu())       # same (bf16-rounded) weights
     g = torch.Generator().manual_seed(0)
     data = torch.randint(0, 4096, (2, 257), generator=g)

@@ -471,6 +471,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         const int heads_per_tile = BN / hd;
         uint32_t cs_lo[32], cs_hi[32];                       // hd 64: the row's whole table, shared by the tile's heads
         if (hd == 64 && rows_ok && t.n0 / hd < p.n_rot) { load_cs(cs_lo, 0); load_cs(cs_hi, 32); }
+        if (hd == 32 && rows_ok && t.n0 / hd < p.n_rot) load_cs(cs_lo, 0);
 #pragma unroll 1
         for (int hh = 0; hh < heads_per_tile; ++hh) {
           const int head = t.n0 / hd + hh;
@@ -484,7 +485,40 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           else if (head < p.Hq + p.Hkv) { const int k = head - p.Hq; dest = k / p.kv_l; slot = p.q_l + (k - dest * p.kv_l); }
           else { const int v = head - p.Hq - p.Hkv; dest = v / p.kv_l; slot = p.q_l + p.kv_l + (v - dest * p.kv_l); }
           const bool rot = head < p.n_rot;
-          if (hd == 64) {
+          if (hd == 32) {
+            // Heads of 32 columns: one TMEM load per head; the head fills the left half of a 64-column staging tile and
+            // is stored with the same 64-wide box, whose right half lies outside the 32-wide head dimension of the
+            // destination and is clipped by TMA.
+            const int bsel = hh & 1;
+            uint32_t r0[32];
+            tmem_ld32(taddr + hh * 32, r0);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            tmem_ld_wait();
+            if (live) {
+              if (rot) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {                    // pairs (i, i + 16) with their own table entries
+                  const float2 l = __half22float2(*reinterpret_cast<const __half2*>(&cs_lo[i]));
+                  const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&cs_lo[i + 16]));
+                  const float a = __uint_as_float(r0[i]), b = __uint_as_float(r0[i + 16]);
+                  r0[i] = __float_as_uint(a * l.x - b * l.y);
+                  r0[i + 16] = __float_as_uint(b * h.x + a * h.y);
+                }
+              }
+              stage32(r0, ebuf + bsel * EPI_BUF_BYTES, 0);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (live)
+                for (int c = 0; c < copies; ++c)
+                  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                               ::"l"((uint64_t)(dst_maps + dest + c)), "r"(ebuf_s + bsel * EPI_BUF_BYTES), "r"(0), "r"(slot),
+                                 "r"(p.row_off + t0), "r"(bi) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          } else if (hd == 64) {
             const int bsel = hh & 1;
             uint32_t r0[32], r1[32];
             tmem_ld32(taddr + hh * 64, r0);
@@ -1120,13 +1154,13 @@ TLM_API int tlm_gemm_set_pair(int mode) {
 //   N = (Hq + 2 Hkv) * hd;  dst_ptrs[r]: bf16 [batch, dst_rows, dst_heads, hd] on rank r (peer-mapped
 //   addresses are fine: the stores are TMA tile stores without multicast);  cs: fp16 (cos, sin) pairs
 //   [rows_per_batch, hd, 2] for the heads below n_rot.
-// Requirements: hd in {64, 128}, rows_per_batch % 32 == 0, n_dst <= 8, Hq % q_l == 0, Hkv % kv_l == 0.
+// Requirements: hd in {32, 64, 128}, rows_per_batch % 32 == 0, n_dst <= 8, Hq % q_l == 0, Hkv % kv_l == 0.
 TLM_API int tlm_gemm_heads(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
                            void* const* dst_ptrs, int n_dst, int batch, int rows_per_batch, int dst_rows, int dst_heads,
                            int row_off, int Hq, int Hkv, int q_l, int kv_l, int hd, int n_rot, const void* cs,
                            int kv_rep, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((hd != 64 && hd != 128) || rows_per_batch % 32 != 0 || n_dst < 1 || n_dst > MAX_HEAD_DST) return -4;
+  if ((hd != 32 && hd != 64 && hd != 128) || rows_per_batch % 32 != 0 || n_dst < 1 || n_dst > MAX_HEAD_DST) return -4;
   if (M != batch * rows_per_batch || N != (Hq + 2 * Hkv) * hd || q_l <= 0 || Hq % q_l != 0) return -5;
   if (kv_rep < 1) kv_rep = 1;
   if (kv_rep > 1) {                     // replicated KV heads: every destination holds exactly one k and one v head

@@ -262,7 +262,8 @@ def gemm_tn_accum(dy: torch.Tensor, x: torch.Tensor, acc: torch.Tensor) -> None:
 
 def heads_epilogue_ok(hd: int, rows_per_batch: int, n_dst: int = 1) -> bool:
     """Shapes the head-scatter GEMM epilogue supports."""
-    return hd in (64, 128) and rows_per_batch % 32 == 0 and 1 <= n_dst <= 8
+    # head dim 32 only without an exchange (one destination): the attention kernels' scatter forms take 64 / 128
+    return (hd in (64, 128) or (hd == 32 and n_dst == 1)) and rows_per_batch % 32 == 0 and 1 <= n_dst <= 8
 
 
 def rope_table_fp16(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
