@@ -295,6 +295,9 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": "baseline/_ref is missing (reference tree not installed)"} \
             if rank == 0 else None
     sys.path[:] = [REF_DIR] + [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    if world > 1 and "TORCHINDUCTOR_COMPILE_THREADS" not in os.environ:
+        # every rank compiles the same model: share the host's cores between the ranks' compiler worker pools
+        os.environ["TORCHINDUCTOR_COMPILE_THREADS"] = str(max(1, min(8, (os.cpu_count() or 8) // world)))
     import torch
     if not torch.cuda.is_available():
         return {"impl": "reference", "unavailable": "the reference requires CUDA (model/gpt.py:42)"} if rank == 0 else None
