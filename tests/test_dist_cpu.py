@@ -173,3 +173,19 @@ def test_bucket_plan_and_shard_pieces():
         s.put_local(full, s.master)
         assert torch.equal(full[covered.bool() & (full != 0)], init[covered.bool() & (full != 0)])
     assert bool((covered == 1).all())
+
+
+def test_bucket_plan_never_exceeds_the_flag_array():
+    """The "parameters ready" flag array has room for 16 buckets per flat buffer: with many layers and a small bucket
+    target the plan merges layers evenly instead of making more groups (dense: bucket 0 + at most 15 groups)."""
+    import torch
+    from train_large_model_from_scratch_b200.models import GPT
+    from train_large_model_from_scratch_b200.training.config import ModelConfig
+    cfg = ModelConfig(num_layer=40, hidden_size=32, num_attention_heads=2, num_key_value_heads=1, intermediate_size=64,
+                      vocab_size=128, block_size=32)
+    model = GPT(cfg, device="cpu", compute_dtype=torch.float32, shard_world=2)
+    cuts, groups = model.plan_buckets(target_bytes=1)                        # would be one group per layer
+    assert len(groups[0]) <= 16 and groups[0][0] == 0 and groups[0] == list(range(len(groups[0])))
+    assert len(cuts[0]) == len(groups[0]) - 1 and cuts[0] == sorted(set(cuts[0]))
+    starts = sorted(model._group_of_block)
+    assert starts[0] == 0 and max(b - a for a, b in zip(starts, starts[1:] + [40])) <= 3     # 40 layers in <= 15 groups
